@@ -1,0 +1,57 @@
+// Library-level entry points: version, error strings, tuning knobs.
+#include "common.cuh"
+#include <string.h>
+
+namespace cb {
+thread_local int g_last_cuda_error = 0;
+extern int g_softmax_threads, g_softmax_ctas_per_sm;
+extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_ctas_per_sm;
+extern int g_nll_gpref, g_nll_ctas_per_sm;
+extern int g_rope_threads, g_rope_ctas_per_sm;
+extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
+}  // namespace cb
+
+extern "C" {
+
+int cacti_b200_version(void) { return 100; }   // 0.1.0
+
+const char* cacti_b200_error_string(int code) {
+  switch (code) {
+    case CACTI_B200_OK: return "ok";
+    case CACTI_B200_ERR_INVALID_VALUE: return "invalid value";
+    case CACTI_B200_ERR_DTYPE: return "unsupported dtype";
+    case CACTI_B200_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case CACTI_B200_ERR_LAUNCH: return "CUDA launch failed";
+    case CACTI_B200_ERR_SHAPE: return "unsupported shape";
+    case CACTI_B200_ERR_INDEX_RANGE: return "index out of range in device data";
+    case CACTI_B200_ERR_NO_DEVICE: return "no sm_100 device";
+    default: return "unknown error";
+  }
+}
+
+int cacti_b200_last_cuda_error(void) { return cb::g_last_cuda_error; }
+
+// Launch-shape knobs for measurement sweeps; not part of the thunk contract.  Returns 0, or
+// CACTI_B200_ERR_INVALID_VALUE for an unknown name or a value outside the knob's range.
+int cacti_b200_tune(const char* name, int value) {
+  using namespace cb;
+  struct Knob { const char* name; int* p; int lo, hi; };
+  const Knob knobs[] = {
+      {"softmax_threads", &g_softmax_threads, 32, 512},   {"softmax_ctas_per_sm", &g_softmax_ctas_per_sm, 1, 32},
+      {"rmsnorm_threads", &g_rmsnorm_threads, 32, 512},   {"rmsnorm_gpref", &g_rmsnorm_gpref, 32, 512},
+      {"rmsnorm_ctas_per_sm", &g_rmsnorm_ctas_per_sm, 1, 8},
+      {"nll_gpref", &g_nll_gpref, 32, 512},               {"nll_ctas_per_sm", &g_nll_ctas_per_sm, 1, 32},
+      {"rope_threads", &g_rope_threads, 32, 256},         {"rope_ctas_per_sm", &g_rope_ctas_per_sm, 1, 64},
+      {"swiglu_threads", &g_swiglu_threads, 32, 256},     {"swiglu_ctas_per_sm", &g_swiglu_ctas_per_sm, 1, 64},
+  };
+  if (!name) return CACTI_B200_ERR_INVALID_VALUE;
+  for (const Knob& k : knobs) {
+    if (strcmp(k.name, name) == 0) {
+      if (value < k.lo || value > k.hi || (k.lo == 32 && value % 32)) return CACTI_B200_ERR_INVALID_VALUE;
+      *k.p = value;
+      return CACTI_B200_OK;
+    }
+  }
+  return CACTI_B200_ERR_INVALID_VALUE;
+}
+}

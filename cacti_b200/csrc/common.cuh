@@ -1,0 +1,223 @@
+// Shared device/host helpers for the sm_100a thunk kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/cacti_b200.h"
+
+namespace cb {
+
+constexpr int kNumSMs = 148;          // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+extern thread_local int g_last_cuda_error;
+
+inline int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return CACTI_B200_ERR_LAUNCH; }
+  return CACTI_B200_OK;
+}
+
+inline bool aligned16(uint64_t p) { return (p & 15u) == 0; }
+
+// ---- element traits ------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static constexpr int VEC = 4;                   // elements per 16-byte vector
+  static __device__ __forceinline__ float to_f32(float v) { return v; }
+  static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Elem<__half> {
+  static constexpr int VEC = 8;
+  static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static constexpr int VEC = 8;
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Round an f32 value to T and back: the rounding point of a primitive thunk whose output cell is T.
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+  return Elem<T>::to_f32(Elem<T>::from_f32(v));
+}
+
+// ---- 16-byte vectors -------------------------------------------------------------------
+// Streaming loads/stores: every activation is touched once, so bypass L1 allocation and mark
+// the lines evict-first in L2.
+__device__ __forceinline__ uint4 ld_stream(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_stream(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+__device__ __forceinline__ uint4 ld_keep(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+template <typename T> __device__ __forceinline__ void unpack(const uint4& v, float (&f)[Elem<T>::VEC]);
+template <> __device__ __forceinline__ void unpack<float>(const uint4& v, float (&f)[4]) {
+  f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+  f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack<__half>(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x; f[2 * i + 1] = t.y;
+  }
+}
+template <> __device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {      // bf16 -> f32 is a 16-bit shift
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <typename T> __device__ __forceinline__ uint4 pack(const float (&f)[Elem<T>::VEC]);
+template <> __device__ __forceinline__ uint4 pack<float>(const float (&f)[4]) {
+  return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <> __device__ __forceinline__ uint4 pack<__half>(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <> __device__ __forceinline__ uint4 pack<__nv_bfloat16>(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// out = T(f32(old) + f32(T(v))): Accumulate mode adds in the output dtype after the new value
+// has itself been rounded to that dtype.
+template <typename T>
+__device__ __forceinline__ uint4 pack_accumulate(const float (&f)[Elem<T>::VEC], const uint4& old) {
+  float o[Elem<T>::VEC], r[Elem<T>::VEC];
+  unpack<T>(old, o);
+#pragma unroll
+  for (int i = 0; i < Elem<T>::VEC; ++i) r[i] = o[i] + round_to<T>(f[i]);
+  return pack<T>(r);
+}
+
+// ---- row groups --------------------------------------------------------------------------
+// A row is processed by a group of G threads (G a multiple of 32).  G == 32: the group is a warp
+// and reductions are shuffles only.  G > 32: warps exchange through shared memory and meet on a
+// named barrier that belongs to the group, so several groups share one CTA without blocking
+// each other.  All threads of the group get the same, order-fixed result.
+constexpr int kMaxGroupsPerCta = 15;             // named barriers 1..15 (0 is __syncthreads)
+constexpr int kMaxWarpsPerGroup = 32;
+
+struct GroupCtx {
+  int G;            // threads per group
+  int gid;          // group index inside the CTA
+  int lane;         // thread index inside the group
+  int nwarps;       // warps per group
+  int phase;        // alternates the shared slot so one barrier per reduction is enough
+  float* red;       // shared: [2][groups][kMaxWarpsPerGroup][2]
+};
+
+__device__ __forceinline__ void group_barrier(const GroupCtx& g) {
+  if (g.G == 32) __syncwarp();
+  else asm volatile("bar.sync %0, %1;" ::"r"(g.gid + 1), "r"(g.G) : "memory");
+}
+
+__device__ __forceinline__ size_t group_red_floats(int groups) { return (size_t)2 * groups * kMaxWarpsPerGroup * 2; }
+
+__device__ __forceinline__ GroupCtx make_group(int G, float* red_smem) {
+  GroupCtx g;
+  g.G = G; g.gid = threadIdx.x / G; g.lane = threadIdx.x % G; g.nwarps = G >> 5; g.phase = 0; g.red = red_smem;
+  return g;
+}
+
+struct SumOp { static __device__ __forceinline__ float f(float a, float b) { return a + b; } static __device__ __forceinline__ float id() { return 0.f; } };
+struct MaxOp { static __device__ __forceinline__ float f(float a, float b) { return fmaxf(a, b); } static __device__ __forceinline__ float id() { return -INFINITY; } };
+
+template <typename Op> __device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = Op::f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Reduce two values at once (a and b use the same Op).
+template <typename Op> __device__ __forceinline__ void group_reduce2(GroupCtx& g, float& a, float& b) {
+  a = warp_reduce<Op>(a);
+  b = warp_reduce<Op>(b);
+  if (g.G == 32) return;
+  const int groups = blockDim.x / g.G;
+  float* slot = g.red + ((size_t)(g.phase * groups + g.gid) * kMaxWarpsPerGroup) * 2;
+  const int w = g.lane >> 5;
+  if ((g.lane & 31) == 0) { slot[2 * w] = a; slot[2 * w + 1] = b; }
+  group_barrier(g);
+  float ra = Op::id(), rb = Op::id();
+  for (int i = 0; i < g.nwarps; ++i) { ra = Op::f(ra, slot[2 * i]); rb = Op::f(rb, slot[2 * i + 1]); }
+  a = ra; b = rb;
+  g.phase ^= 1;
+}
+template <typename Op> __device__ __forceinline__ float group_reduce(GroupCtx& g, float a) {
+  float b = Op::id();
+  group_reduce2<Op>(g, a, b);
+  return a;
+}
+
+// ---- block reduction for the element-wise fallback kernels (whole CTA = one row) -----------
+template <typename Op> __device__ __forceinline__ float block_reduce(float v, float* smem /* >= 33 floats */) {
+  v = warp_reduce<Op>(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();                       // protect smem from the previous use
+  if ((threadIdx.x & 31) == 0) smem[w] = v;
+  __syncthreads();
+  float r = Op::id();
+  for (int i = 0; i < nw; ++i) r = Op::f(r, smem[i]);
+  return r;
+}
+
+// exp in f32.  16-bit storage: ex2.approx (relative error ~1e-6, far below the storage
+// rounding).  f32 storage: the accurate library exp, so fp32 results stay within 1e-5 relative.
+template <typename T> __device__ __forceinline__ float exp_for(float x) { return __expf(x); }
+template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
+
+template <typename F> inline int dispatch_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case CACTI_B200_R_32F:  return f(float{});
+    case CACTI_B200_R_16F:  return f(__half{});
+    case CACTI_B200_R_16BF: return f(__nv_bfloat16{});
+    default: return CACTI_B200_ERR_DTYPE;
+  }
+}
+
+// Pick (threads per row group, 16-byte vectors per thread) for a row of `nvec` vectors.
+// Rows of up to 32*nv_max vectors go to one warp (shuffle-only reductions, several rows per CTA).
+// Longer rows go to a multi-warp group: the fewest vectors per thread that keeps the group at
+// or below g_pref threads, else nv_max vectors per thread and up to 512 threads.
+struct GroupPlan { int G; int NV; int groups; bool ok; };
+inline GroupPlan plan_group(int64_t nvec, int nv_max, int g_pref, int target_threads) {
+  GroupPlan p{32, 1, 1, false};
+  if (nvec <= 0) return p;
+  for (int nv = 1; nv <= nv_max; nv *= 2) {
+    if (nvec <= 32LL * nv) {
+      p.G = 32; p.NV = nv; p.groups = target_threads / 32; if (p.groups < 1) p.groups = 1; p.ok = true;
+      return p;
+    }
+  }
+  for (int nv = 1; nv <= nv_max; nv *= 2) {
+    int64_t g = ((nvec + nv - 1) / nv + 31) / 32 * 32;
+    const int64_t cap = (nv == nv_max) ? 512 : g_pref;
+    if (g <= cap) {
+      p.G = (int)g; p.NV = nv;
+      p.groups = target_threads / p.G; if (p.groups < 1) p.groups = 1;
+      if (p.groups > kMaxGroupsPerCta) p.groups = kMaxGroupsPerCta;
+      p.ok = true;
+      return p;
+    }
+  }
+  return p;
+}
+
+}  // namespace cb

@@ -1,0 +1,325 @@
+// K1: RMSNorm forward / backward / fused forward+backward.
+//
+// Replaces the reference's rms_norm closure (src/librarium/llama.rs:442-451): cast -> square ->
+// inner_mean -> add eps -> sqrt -> broadcast div -> broadcast mul -> lossy cast, eight primitive
+// thunks forward and about fourteen backward, each a separate Futhark program.  Here one kernel
+// reads x (and dy) once, keeps the row in registers, and writes y (and dx) once; the two row sums
+// the fused form needs (sum x^2 and sum gamma*dy*x) are reduced together.
+//
+// dgamma is a sum over rows.  Each CTA walks its rows with every thread owning fixed columns, so
+// the per-thread dgamma terms accumulate in registers; at the end the CTA folds its row groups
+// through shared memory and writes one f32 partial row.  A second small kernel adds the partials
+// in a fixed order.  No floating-point atomics: results are run-to-run identical, as the
+// reference's cuBLAS setup also demands (cacti_gpu_cu_ffi/src/lib.rs:749).
+#include "common.cuh"
+
+namespace cb {
+
+int g_rmsnorm_threads = 512;      // target threads per CTA on the vector path
+int g_rmsnorm_gpref = 256;        // preferred threads per row group
+int g_rmsnorm_ctas_per_sm = 2;
+
+constexpr int kRmsMaxPartials = kNumSMs * 8;
+
+template <typename T, int NV, bool FWD, bool BWD>
+__global__ void __launch_bounds__(512)
+rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
+                    const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
+                    float eps, int64_t rows, int cols, int G, int beta_dx) {
+  extern __shared__ float smem[];
+  constexpr int VEC = Elem<T>::VEC;
+  const int groups = blockDim.x / G;
+  float* red = smem;                                              // group reductions
+  float* colacc = smem + (size_t)2 * groups * kMaxWarpsPerGroup * 2;  // [cols] dgamma fold
+  GroupCtx g = make_group(G, red);
+  const float inv_cols = 1.f / (float)cols;
+
+  // Register budget: with NV <= 2 gamma stays in registers and rows are double-buffered; with
+  // NV = 4 gamma is re-read per row (it stays in L1) and the next row is not prefetched.
+  constexpr bool LEAN = NV > 2;
+  constexpr int NG = LEAN ? 1 : NV;
+  uint4 graw[NG];       // gamma for this thread's columns, raw
+  float dg[NV][VEC];    // dgamma accumulators
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int col0 = (g.lane + k * G) * VEC;
+    if (!LEAN && col0 < cols) graw[k % NG] = ld_keep(gamma + col0);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) dg[k][e] = 0.f;
+  }
+
+  const int64_t stride = (int64_t)gridDim.x * groups;
+  int64_t row = (int64_t)blockIdx.x * groups + g.gid;
+  // Rows are double-buffered in registers: the loads of the next row are issued before the
+  // current row is reduced, so each thread keeps 2*NV (fwd) or 4*NV (fwd+bwd) 16-byte loads in flight.
+  constexpr int NP = LEAN ? 1 : NV;
+  uint4 xraw[NV], yraw[NV], xnext[NP], ynext[NP];
+#define CB_LOAD_ROW(r_, xr_, yr_)                                         \
+  _Pragma("unroll") for (int k = 0; k < NV; ++k) {                        \
+    const int col0 = (g.lane + k * G) * VEC;                              \
+    if (col0 < cols) {                                                    \
+      xr_[k] = ld_stream(X + (r_) * cols + col0);                         \
+      if (BWD) yr_[k] = ld_stream(dY + (r_) * cols + col0);               \
+    }                                                                     \
+  }
+  if (!LEAN && row < rows) { CB_LOAD_ROW(row, xraw, yraw) }
+  for (; row < rows; row += stride) {
+    if (LEAN) { CB_LOAD_ROW(row, xraw, yraw) }
+    else if (row + stride < rows) { CB_LOAD_ROW(row + stride, xnext, ynext) }
+    // pass 1: ss = sum x^2, c1 = sum gamma*dy*x
+    float ss = 0.f, c1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < cols) {
+        float x[VEC];
+        unpack<T>(xraw[k], x);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss = fmaf(x[e], x[e], ss);
+        if (BWD) {
+          float gy[VEC], gm[VEC];
+          unpack<T>(yraw[k], gy);
+          unpack<T>(LEAN ? ld_keep(gamma + col0) : graw[k % NG], gm);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) c1 = fmaf(gm[e] * gy[e], x[e], c1);
+        }
+      }
+    }
+    group_reduce2<SumOp>(g, ss, c1);
+    const float s = sqrtf(ss * inv_cols + eps);
+    const float coef = BWD ? c1 / (s * s) / (s + s) * inv_cols * 2.f : 0.f;   // c1 / (cols * s^3)
+    // pass 2: outputs
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < cols) {
+        float x[VEC], gm[VEC], t[VEC];
+        unpack<T>(xraw[k], x);
+        unpack<T>(LEAN ? ld_keep(gamma + col0) : graw[k % NG], gm);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) t[e] = x[e] / s;
+        if (FWD) {
+          float y[VEC];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y[e] = gm[e] * t[e];
+          st_stream(Y + row * cols + col0, pack<T>(y));
+        }
+        if (BWD) {
+          float gy[VEC], d[VEC];
+          unpack<T>(yraw[k], gy);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            dg[k][e] = fmaf(gy[e], t[e], dg[k][e]);
+            d[e] = (gm[e] * gy[e]) / s - x[e] * coef;
+          }
+          T* o = dX + row * cols + col0;
+          if (beta_dx) st_stream(o, pack_accumulate<T>(d, ld_stream(o)));
+          else st_stream(o, pack<T>(d));
+        }
+      }
+    }
+    if (!LEAN) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) { xraw[k] = xnext[k % NP]; if (BWD) yraw[k] = ynext[k % NP]; }
+    }
+  }
+#undef CB_LOAD_ROW
+
+  if (BWD) {
+    // fold the CTA's row groups in group order, then one partial row per CTA
+    for (int q = 0; q < groups; ++q) {
+      if (g.gid == q) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int col0 = (g.lane + k * G) * VEC;
+          if (col0 < cols) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+              if (q == 0) colacc[col0 + e] = dg[k][e];
+              else colacc[col0 + e] += dg[k][e];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    float* prow = partial + (size_t)blockIdx.x * cols;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) prow[j] = colacc[j];
+  }
+}
+
+// dgamma[j] (+)= sum_p partial[p][j], p in increasing order within fixed slices.
+template <typename TO>
+__global__ void __launch_bounds__(512)
+rmsnorm_dgamma_finalize_kernel(TO* __restrict__ dgamma, const float* __restrict__ partial, int nparts, int cols,
+                               int beta) {
+  __shared__ float sm[16][33];
+  const int cx = threadIdx.x & 31, sy = threadIdx.x >> 5;     // 32 columns x 16 slices
+  const int j = blockIdx.x * 32 + cx;
+  float acc = 0.f;
+  if (j < cols) for (int p = sy; p < nparts; p += 16) acc += partial[(size_t)p * cols + j];
+  sm[sy][cx] = acc;
+  __syncthreads();
+  if (sy == 0 && j < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) t += sm[i][cx];
+    if (beta) dgamma[j] = Elem<TO>::from_f32(Elem<TO>::to_f32(dgamma[j]) + round_to<TO>(t));
+    else dgamma[j] = Elem<TO>::from_f32(t);
+  }
+}
+
+// Element-wise fallback (any cols / alignment): one CTA per row; 1/s per row goes to the workspace
+// so that a column kernel can form dgamma without atomics.
+template <typename T, bool FWD, bool BWD>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_generic_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ row_s,
+                            const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
+                            float eps, int64_t rows, int64_t cols, int beta_dx) {
+  __shared__ float sm[33];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* x = X + row * cols;
+    float ss = 0.f, c1 = 0.f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+      const float xv = Elem<T>::to_f32(x[j]);
+      ss = fmaf(xv, xv, ss);
+      if (BWD) c1 = fmaf(Elem<T>::to_f32(gamma[j]) * Elem<T>::to_f32(dY[row * cols + j]), xv, c1);
+    }
+    ss = block_reduce<SumOp>(ss, sm);
+    if (BWD) c1 = block_reduce<SumOp>(c1, sm);
+    const float s = sqrtf(ss / (float)cols + eps);
+    const float coef = BWD ? c1 / (s * s) / (s + s) / (float)cols * 2.f : 0.f;
+    if (BWD && threadIdx.x == 0) row_s[row] = s;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+      const float xv = Elem<T>::to_f32(x[j]), gm = Elem<T>::to_f32(gamma[j]);
+      if (FWD) Y[row * cols + j] = Elem<T>::from_f32(gm * (xv / s));
+      if (BWD) {
+        const float d = (gm * Elem<T>::to_f32(dY[row * cols + j])) / s - xv * coef;
+        T* o = dX + row * cols + j;
+        *o = beta_dx ? Elem<T>::from_f32(Elem<T>::to_f32(*o) + round_to<T>(d)) : Elem<T>::from_f32(d);
+      }
+    }
+  }
+}
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_dgamma_generic_kernel(TO* __restrict__ dgamma, const float* __restrict__ row_s, const T* __restrict__ X,
+                              const T* __restrict__ dY, int64_t rows, int64_t cols, int beta) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  float acc = 0.f;
+  for (int64_t i = 0; i < rows; ++i)
+    acc = fmaf(Elem<T>::to_f32(dY[i * cols + j]), Elem<T>::to_f32(X[i * cols + j]) / row_s[i], acc);
+  if (beta) dgamma[j] = Elem<TO>::from_f32(Elem<TO>::to_f32(dgamma[j]) + round_to<TO>(acc));
+  else dgamma[j] = Elem<TO>::from_f32(acc);
+}
+
+static size_t rmsnorm_ws_bytes(int64_t rows, int64_t cols) {
+  size_t a = (size_t)kRmsMaxPartials * (size_t)cols * sizeof(float);
+  size_t b = (size_t)rows * sizeof(float);
+  return (a > b ? a : b) + 256;
+}
+
+template <typename T, typename TO, bool FWD, bool BWD>
+static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, uint64_t gamma, uint64_t dy,
+                          float eps, int64_t rows, int64_t cols, int beta_dx, int beta_dg, uint64_t ws,
+                          cudaStream_t st) {
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int NVMAX = 4;
+  T* Y = reinterpret_cast<T*>(y); T* dX = reinterpret_cast<T*>(dx);
+  const T* X = reinterpret_cast<const T*>(x); const T* Gm = reinterpret_cast<const T*>(gamma);
+  const T* dY = reinterpret_cast<const T*>(dy);
+  TO* dG = reinterpret_cast<TO*>(dgamma);
+  float* wsf = reinterpret_cast<float*>(ws);
+  const bool vec_ok = (cols % VEC == 0) && aligned16(x) && aligned16(gamma) && (!FWD || aligned16(y)) &&
+                      (!BWD || (aligned16(dx) && aligned16(dy))) && cols / VEC <= 512LL * NVMAX &&
+                      (size_t)cols * sizeof(float) <= 160 * 1024;
+  if (vec_ok) {
+    GroupPlan pl = plan_group(cols / VEC, NVMAX, g_rmsnorm_gpref, g_rmsnorm_threads);
+    if (pl.ok) {
+      const int threads = pl.G * pl.groups;
+      const int64_t want = (rows + pl.groups - 1) / pl.groups;
+      int64_t grid = (int64_t)kNumSMs * g_rmsnorm_ctas_per_sm;
+      if (grid > kRmsMaxPartials) grid = kRmsMaxPartials;
+      if (grid > want) grid = want;
+      const size_t smem = ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+#define CB_LAUNCH(NV_)                                                                                      \
+  do {                                                                                                      \
+    auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD>;                                                      \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, beta_dx); \
+  } while (0)
+      switch (pl.NV) {
+        case 1: CB_LAUNCH(1); break;
+        case 2: CB_LAUNCH(2); break;
+        default: CB_LAUNCH(4); break;
+      }
+#undef CB_LAUNCH
+      int rc = check_launch();
+      if (rc || !BWD) return rc;
+      rmsnorm_dgamma_finalize_kernel<TO><<<(unsigned)((cols + 31) / 32), 512, 0, st>>>(dG, wsf, (int)grid,
+                                                                                      (int)cols, beta_dg);
+      return check_launch();
+    }
+  }
+  int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  rmsnorm_rows_generic_kernel<T, FWD, BWD><<<(unsigned)grid, 256, 0, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, cols,
+                                                                           beta_dx);
+  int rc = check_launch();
+  if (rc || !BWD) return rc;
+  rmsnorm_dgamma_generic_kernel<T, TO><<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(dG, wsf, X, dY, rows, cols,
+                                                                                       beta_dg);
+  return check_launch();
+}
+
+static int rmsnorm_entry(bool fwd, bool bwd, uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, uint64_t gamma,
+                         uint64_t dy, float eps, int64_t rows, int64_t cols, int dtype, int dg_dtype, int beta_dx,
+                         int beta_dg, uint64_t ws, size_t ws_bytes, void* stream) {
+  if (rows < 0 || cols < 0 || cols > 0x7fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
+  if ((beta_dx | beta_dg) & ~1) return CACTI_B200_ERR_INVALID_VALUE;
+  if (rows == 0 || cols == 0) return CACTI_B200_OK;   // reference: an empty cell is a no-op
+  if (!x || !gamma || (fwd && !y) || (bwd && (!dx || !dy || !dgamma))) return CACTI_B200_ERR_INVALID_VALUE;
+  if (bwd) {
+    if (dg_dtype != dtype && dg_dtype != CACTI_B200_R_32F) return CACTI_B200_ERR_DTYPE;
+    if (!ws || ws_bytes < rmsnorm_ws_bytes(rows, cols) || (ws & 3)) return CACTI_B200_ERR_WORKSPACE;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+#define CB_GO(TO_)                                                                                                 \
+  (fwd && bwd) ? launch_rmsnorm<T, TO_, true, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st) \
+  : fwd        ? launch_rmsnorm<T, TO_, true, false>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st) \
+               : launch_rmsnorm<T, TO_, false, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st)
+    if (bwd && dg_dtype == CACTI_B200_R_32F) return CB_GO(float);
+    return CB_GO(T);
+#undef CB_GO
+  });
+}
+
+}  // namespace cb
+
+extern "C" {
+size_t cacti_b200_rmsnorm_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows < 0 || cols < 0) return 0;
+  return cb::rmsnorm_ws_bytes(rows, cols);
+}
+int cacti_b200_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr gamma, float eps, int64_t rows,
+                           int64_t cols, int dtype, cacti_b200_stream stream) {
+  return cb::rmsnorm_entry(true, false, y, 0, 0, x, gamma, 0, eps, rows, cols, dtype, dtype, 0, 0, 0, 0, stream);
+}
+int cacti_b200_rmsnorm_bwd(cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr dy, cacti_b200_dptr x,
+                           cacti_b200_dptr gamma, float eps, int64_t rows, int64_t cols, int dtype, int dgamma_dtype,
+                           int beta_dx, int beta_dgamma, cacti_b200_dptr workspace, size_t workspace_bytes,
+                           cacti_b200_stream stream) {
+  return cb::rmsnorm_entry(false, true, 0, dx, dgamma, x, gamma, dy, eps, rows, cols, dtype, dgamma_dtype, beta_dx,
+                           beta_dgamma, workspace, workspace_bytes, stream);
+}
+int cacti_b200_rmsnorm_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr x,
+                               cacti_b200_dptr gamma, cacti_b200_dptr dy, float eps, int64_t rows, int64_t cols,
+                               int dtype, int dgamma_dtype, int beta_dx, int beta_dgamma, cacti_b200_dptr workspace,
+                               size_t workspace_bytes, cacti_b200_stream stream) {
+  return cb::rmsnorm_entry(true, true, y, dx, dgamma, x, gamma, dy, eps, rows, cols, dtype, dgamma_dtype, beta_dx,
+                           beta_dgamma, workspace, workspace_bytes, stream);
+}
+}

@@ -1,0 +1,273 @@
+// K3: rotary position embedding, forward / backward / fused forward+backward, and its tables.
+//
+// Replaces symplectic_embed (src/librarium/llama.rs:463-465): BroadcastMul (x*cos) +
+// InnerSymplecticMap (rotate-half, :975-1049) + BroadcastMul (rot*sin) + Add
+// (src/thunk/op.rs:1480-1535) -- four programs and three full-size temporaries forward, two
+// memcpys, two Futhark-vjp programs and an accumulate backward.  The backward does not depend on
+// x: dx = dy*cos + R(dy*sin), so the fused form streams x and dy in and y and dx out.
+//
+// head_dim 100 makes a head 200 bytes, so heads are not 16-byte aligned; token rows
+// (heads*head_dim elements) are.  Vectors are therefore taken over the flat token row; the
+// rotate-half partner of each 4-byte unit (a half2 / bf162 / float) sits +-head_dim/2 elements
+// away and is fetched with a 4-byte load that hits lines this CTA already streams.
+//
+// f16 follows the reference's f16 arithmetic (both operands f16 => f16 ops, one rounding per
+// primitive, src/thunk/op.rs:2126-2133) using the non-contracting *_rn intrinsics; f32 uses
+// separately rounded f32 ops; bf16 (no reference chain: Futhark has no bf16) computes in f32 and
+// rounds once.
+#include "common.cuh"
+#include <type_traits>
+
+namespace cb {
+
+int g_rope_threads = 256;
+int g_rope_ctas_per_sm = 8;
+
+template <typename T> struct Unit;         // one 4-byte unit
+template <> struct Unit<__half> { static constexpr int UPV = 2; };
+template <> struct Unit<__nv_bfloat16> { static constexpr int UPV = 2; };
+template <> struct Unit<float> { static constexpr int UPV = 1; };
+
+template <typename T> __device__ __forceinline__ uint32_t ldu(const T* p) {      // 4-byte aligned
+  return __ldg(reinterpret_cast<const unsigned int*>(p));
+}
+
+// y = x*c + r*s with r = first ? -xp : xp   (forward)
+// d = g*c + (first ? z : -z), z = gp*sp     (backward)
+template <typename T>
+__device__ __forceinline__ uint32_t rope_unit(uint32_t own, uint32_t partner, uint32_t c, uint32_t s_for_partner_term,
+                                              bool first, bool backward) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 o = *reinterpret_cast<__half2*>(&own), p = *reinterpret_cast<__half2*>(&partner);
+    const __half2 cc = *reinterpret_cast<__half2*>(&c), ss = *reinterpret_cast<__half2*>(&s_for_partner_term);
+    const __half2 a = __hmul2_rn(o, cc);
+    __half2 b;
+    if (!backward) b = __hmul2_rn(first ? __hneg2(p) : p, ss);
+    else { b = __hmul2_rn(p, ss); if (!first) b = __hneg2(b); }
+    const __half2 y = __hadd2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&y);
+  } else if constexpr (std::is_same<T, float>::value) {
+    const float o = __uint_as_float(own), p = __uint_as_float(partner);
+    const float cc = __uint_as_float(c), ss = __uint_as_float(s_for_partner_term);
+    const float a = __fmul_rn(o, cc);
+    float b = __fmul_rn(p, ss);
+    if (first != backward) b = -b;
+    return __float_as_uint(__fadd_rn(a, b));
+  } else {
+    float r[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float o = __uint_as_float(i ? (own & 0xffff0000u) : (own << 16));
+      const float p = __uint_as_float(i ? (partner & 0xffff0000u) : (partner << 16));
+      const float cc = __uint_as_float(i ? (c & 0xffff0000u) : (c << 16));
+      const float ss = __uint_as_float(i ? (s_for_partner_term & 0xffff0000u) : (s_for_partner_term << 16));
+      const float b = p * ss;
+      r[i] = fmaf(o, cc, (first != backward) ? -b : b);
+    }
+    __nv_bfloat162 y = __floats2bfloat162_rn(r[0], r[1]);
+    return *reinterpret_cast<const uint32_t*>(&y);
+  }
+}
+
+// Accumulate mode: out = old + new in T.
+template <typename T> __device__ __forceinline__ uint32_t add_unit(uint32_t old, uint32_t v) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 y = __hadd2_rn(*reinterpret_cast<__half2*>(&old), *reinterpret_cast<__half2*>(&v));
+    return *reinterpret_cast<const uint32_t*>(&y);
+  } else if constexpr (std::is_same<T, float>::value) {
+    return __float_as_uint(__fadd_rn(__uint_as_float(old), __uint_as_float(v)));
+  } else {
+    __nv_bfloat162 y = __floats2bfloat162_rn(__uint_as_float(old << 16) + __uint_as_float(v << 16),
+                                              __uint_as_float(old & 0xffff0000u) + __uint_as_float(v & 0xffff0000u));
+    return *reinterpret_cast<const uint32_t*>(&y);
+  }
+}
+
+template <typename T, bool FWD, bool BWD>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, const T* __restrict__ dY,
+                const T* __restrict__ cosT, const T* __restrict__ sinT, int64_t nvec, int vpr /* vectors per token row */,
+                int hd, int64_t pos_mod, int64_t pos_off, int beta) {
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int UPV = Unit<T>::UPV;
+  constexpr int NU = 4;                       // units per vector
+  const int half = hd >> 1;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tok = v / vpr;
+    const int r = (int)(v - tok * vpr) * VEC;           // element offset inside the token row
+    const int64_t e0 = v * VEC;                          // flat element index
+    const int64_t pos = (tok + pos_off) % pos_mod;
+    const T* ct = cosT + pos * hd;
+    const T* stb = sinT + pos * hd;
+    uint4 xo, go;
+    if (FWD) xo = ld_stream(X + e0);
+    if (BWD) go = ld_stream(dY + e0);
+    int j = r % hd;
+    uint32_t yo[NU], dout[NU];
+    const uint32_t xw[NU] = {xo.x, xo.y, xo.z, xo.w};
+    const uint32_t gw[NU] = {go.x, go.y, go.z, go.w};
+#pragma unroll
+    for (int p = 0; p < NU; ++p) {
+      if (j >= hd) j -= hd;
+      const bool first = j < half;
+      const int jp = first ? j + half : j - half;        // partner index inside the head
+      const int64_t ep = e0 + p * UPV + (first ? half : -half);
+      const uint32_t c = ldu(ct + j);
+      if (FWD) yo[p] = rope_unit<T>(xw[p], ldu(X + ep), c, ldu(stb + j), first, false);
+      if (BWD) dout[p] = rope_unit<T>(gw[p], ldu(dY + ep), c, ldu(stb + jp), first, true);
+      j += UPV;
+    }
+    if (FWD) st_stream(Y + e0, make_uint4(yo[0], yo[1], yo[2], yo[3]));
+    if (BWD) {
+      if (beta) {
+        const uint4 o = ld_stream(dX + e0);
+        dout[0] = add_unit<T>(o.x, dout[0]); dout[1] = add_unit<T>(o.y, dout[1]);
+        dout[2] = add_unit<T>(o.z, dout[2]); dout[3] = add_unit<T>(o.w, dout[3]);
+      }
+      st_stream(dX + e0, make_uint4(dout[0], dout[1], dout[2], dout[3]));
+    }
+  }
+}
+
+// Element-wise fallback for shapes/alignments the vector kernel does not take (head_dim not a
+// multiple of 4 for 16-bit types, token rows not a multiple of 16 bytes, unaligned views).
+template <typename T> __device__ __forceinline__ T rope_scalar(T own, T partner, T c, T s, bool first, bool backward) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const float b = __bfloat162float(partner) * __bfloat162float(s);
+    return __float2bfloat16_rn(fmaf(__bfloat162float(own), __bfloat162float(c), (first != backward) ? -b : b));
+  } else {
+    const float a = round_to<T>(Elem<T>::to_f32(own) * Elem<T>::to_f32(c));     // exact product, one rounding
+    float b = round_to<T>(Elem<T>::to_f32(partner) * Elem<T>::to_f32(s));
+    if (first != backward) b = -b;
+    return Elem<T>::from_f32(__fadd_rn(a, b));
+  }
+}
+
+template <typename T, bool FWD, bool BWD>
+__global__ void __launch_bounds__(256)
+rope_generic_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, const T* __restrict__ dY,
+                    const T* __restrict__ cosT, const T* __restrict__ sinT, int64_t n, int64_t row_len, int hd,
+                    int64_t pos_mod, int64_t pos_off, int beta) {
+  const int half = hd >> 1;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tok = e / row_len;
+    const int j = (int)((e - tok * row_len) % hd);
+    const int64_t pos = (tok + pos_off) % pos_mod;
+    const bool first = j < half;
+    const int jp = first ? j + half : j - half;
+    const int64_t ep = e + (jp - j);
+    const T c = cosT[pos * hd + j];
+    if (FWD) Y[e] = rope_scalar<T>(X[e], X[ep], c, sinT[pos * hd + j], first, false);
+    if (BWD) {
+      T d = rope_scalar<T>(dY[e], dY[ep], c, sinT[pos * hd + jp], first, true);
+      if (beta) d = Elem<T>::from_f32(Elem<T>::to_f32(dX[e]) + Elem<T>::to_f32(d));
+      dX[e] = d;
+    }
+  }
+}
+
+template <typename T>
+__global__ void rope_tables_kernel(T* __restrict__ cosT, T* __restrict__ sinT, int64_t seq, int hd, float theta,
+                                   float exp_scale) {
+  const int half = hd >> 1;
+  const int64_t n = seq * half;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t p = t / half;
+    const int i = (int)(t - p * half);
+    const float e = __fmul_rn((float)i, exp_scale);      // f32(i) * (-2/hd)
+    const float w = powf(theta, e);
+    const float phi = __fmul_rn((float)p, w);
+    const T c = Elem<T>::from_f32(cosf(phi)), s = Elem<T>::from_f32(sinf(phi));
+    cosT[p * hd + i] = c; cosT[p * hd + i + half] = c;
+    sinT[p * hd + i] = s; sinT[p * hd + i + half] = s;
+  }
+}
+
+template <typename T, bool FWD, bool BWD>
+static int launch_rope(uint64_t y, uint64_t dx, uint64_t x, uint64_t dy, uint64_t c, uint64_t s, int64_t tokens,
+                       int64_t heads, int64_t hd, int64_t pos_mod, int64_t pos_off, int beta, cudaStream_t st) {
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int UPV = Unit<T>::UPV;
+  T* Y = reinterpret_cast<T*>(y); T* dX = reinterpret_cast<T*>(dx);
+  const T* X = reinterpret_cast<const T*>(x); const T* dY = reinterpret_cast<const T*>(dy);
+  const T* C = reinterpret_cast<const T*>(c); const T* S = reinterpret_cast<const T*>(s);
+  const int64_t row_len = heads * hd, n = tokens * row_len;
+  const bool vec_ok = (row_len % VEC == 0) && (hd % (2 * UPV) == 0) && hd >= VEC && (c % 4 == 0) && (s % 4 == 0) &&
+                      (!FWD || (aligned16(x) && aligned16(y))) && (!BWD || (aligned16(dy) && aligned16(dx))) &&
+                      row_len / VEC <= 0x7fffffffLL;
+  const int threads = g_rope_threads;
+  if (vec_ok) {
+    const int64_t nvec = n / VEC;
+    int64_t grid = (nvec + threads - 1) / threads;
+    const int64_t cap = (int64_t)kNumSMs * g_rope_ctas_per_sm;
+    if (grid > cap) grid = cap;
+    rope_vec_kernel<T, FWD, BWD><<<(unsigned)grid, threads, 0, st>>>(Y, dX, X, dY, C, S, nvec, (int)(row_len / VEC),
+                                                                    (int)hd, pos_mod, pos_off, beta);
+    return check_launch();
+  }
+  int64_t grid = (n + threads - 1) / threads;
+  const int64_t cap = (int64_t)kNumSMs * 16;
+  if (grid > cap) grid = cap;
+  rope_generic_kernel<T, FWD, BWD><<<(unsigned)grid, threads, 0, st>>>(Y, dX, X, dY, C, S, n, row_len, (int)hd,
+                                                                      pos_mod, pos_off, beta);
+  return check_launch();
+}
+
+static int rope_entry(bool fwd, bool bwd, uint64_t y, uint64_t dx, uint64_t x, uint64_t dy, uint64_t c, uint64_t s,
+                      int64_t tokens, int64_t heads, int64_t hd, int64_t pos_mod, int64_t pos_off, int dtype, int beta,
+                      void* stream) {
+  if (tokens < 0 || heads < 0 || hd < 0 || hd > 0x3fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
+  if (beta & ~1) return CACTI_B200_ERR_INVALID_VALUE;
+  if (tokens == 0 || heads == 0 || hd == 0) return CACTI_B200_OK;
+  if (hd & 1) return CACTI_B200_ERR_SHAPE;     // rotate-half splits the head in two equal parts
+  if (pos_mod <= 0 || pos_off < 0) return CACTI_B200_ERR_INVALID_VALUE;
+  if (!c || !s || (fwd && (!x || !y)) || (bwd && (!dy || !dx))) return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    if (fwd && bwd) return launch_rope<T, true, true>(y, dx, x, dy, c, s, tokens, heads, hd, pos_mod, pos_off, beta, st);
+    if (fwd) return launch_rope<T, true, false>(y, dx, x, dy, c, s, tokens, heads, hd, pos_mod, pos_off, beta, st);
+    return launch_rope<T, false, true>(y, dx, x, dy, c, s, tokens, heads, hd, pos_mod, pos_off, beta, st);
+  });
+}
+
+}  // namespace cb
+
+extern "C" {
+int cacti_b200_rope_tables(cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t seq, int64_t head_dim, float theta,
+                           int dtype, cacti_b200_stream stream) {
+  using namespace cb;
+  if (seq < 0 || head_dim < 0 || head_dim > 0x3fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
+  if (seq == 0 || head_dim == 0) return CACTI_B200_OK;
+  if (head_dim & 1) return CACTI_B200_ERR_SHAPE;
+  if (!cos || !sin) return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const float exp_scale = -2.0f / (float)head_dim;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const int64_t n = seq * (head_dim / 2);
+    int64_t grid = (n + 255) / 256;
+    if (grid > kNumSMs * 8) grid = kNumSMs * 8;
+    rope_tables_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<T*>(cos), reinterpret_cast<T*>(sin), seq,
+                                                         (int)head_dim, theta, exp_scale);
+    return check_launch();
+  });
+}
+int cacti_b200_rope_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t tokens,
+                        int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off, int dtype,
+                        cacti_b200_stream stream) {
+  return cb::rope_entry(true, false, y, 0, x, 0, cos, sin, tokens, heads, head_dim, pos_mod, pos_off, dtype, 0, stream);
+}
+int cacti_b200_rope_bwd(cacti_b200_dptr dx, cacti_b200_dptr dy, cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t tokens,
+                        int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off, int dtype, int beta_dx,
+                        cacti_b200_stream stream) {
+  return cb::rope_entry(false, true, 0, dx, 0, dy, cos, sin, tokens, heads, head_dim, pos_mod, pos_off, dtype, beta_dx,
+                        stream);
+}
+int cacti_b200_rope_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr x, cacti_b200_dptr dy,
+                            cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t tokens, int64_t heads, int64_t head_dim,
+                            int64_t pos_mod, int64_t pos_off, int dtype, int beta_dx, cacti_b200_stream stream) {
+  return cb::rope_entry(true, true, y, dx, x, dy, cos, sin, tokens, heads, head_dim, pos_mod, pos_off, dtype, beta_dx,
+                        stream);
+}
+}

@@ -1,0 +1,240 @@
+// K2: masked row softmax, forward / backward / fused forward+backward.
+//
+// Replaces, per row of a [.., cols] tensor, the reference chain
+//   cast(f32) -> block_tri_elem_affine (causal mask) -> inner_softmax -> lossy_cast
+// (src/librarium/llama.rs:502-505, src/thunk/op.rs:4189-4278, :3257-3383) and the adjoint
+//   inner_softmax_post_adj over a recomputed softmax + mask adjoint + lossy cast
+// (src/thunk/op.rs:3376-3382, :3386-3457, :4265-4276).
+//
+// Fast path: one row per group of G threads, the row's 16-byte vectors held raw in registers
+// (S and dP), three register passes (max, sum of exp, outputs).  Every input byte is read from
+// HBM once, every output byte written once; masked inputs are never read.  All loads of a row
+// are issued before the first use so a warp keeps NV*2 128-bit loads per lane in flight.
+#include "common.cuh"
+#include <type_traits>
+
+namespace cb {
+
+int g_softmax_threads = 256;   // threads per CTA on the warp-per-row path (tunable)
+int g_softmax_ctas_per_sm = 8; // grid = SMs * this (capped by the row count)
+
+__device__ __forceinline__ int active_cols(int64_t row, int cols, int mask_mode,
+                                           int64_t q_div, int64_t q_mod, int64_t q_off) {
+  if (mask_mode != CACTI_B200_MASK_CAUSAL) return cols;
+  int64_t q = (row / q_div) % q_mod + q_off;
+  if (q < 0) return 0;
+  return (q + 1 < (int64_t)cols) ? (int)(q + 1) : cols;
+}
+
+template <typename T, int NV, bool FWD, bool BWD>
+__global__ void __launch_bounds__(512)
+softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__ S, const T* __restrict__ dP,
+                    int64_t rows, int cols, int G, int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
+                    int beta) {
+  extern __shared__ float red[];
+  constexpr int VEC = Elem<T>::VEC;
+  GroupCtx g = make_group(G, red);
+  const int groups = blockDim.x / G;
+
+  for (int64_t row = (int64_t)blockIdx.x * groups + g.gid; row < rows; row += (int64_t)gridDim.x * groups) {
+    const int active = active_cols(row, cols, mask_mode, q_div, q_mod, q_off);
+    const T* srow = S + row * cols;
+    const T* grow = BWD ? dP + row * cols : nullptr;
+    uint4 sraw[NV], graw[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < active) {
+        sraw[k] = ld_stream(srow + col0);
+        if (BWD) graw[k] = ld_stream(grow + col0);
+      }
+    }
+    // pass 1: row maximum
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < active) {
+        float a[VEC];
+        unpack<T>(sraw[k], a);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) if (col0 + e < active) m = fmaxf(m, a[e]);
+      }
+    }
+    m = group_reduce<MaxOp>(g, m);
+    // pass 2: Z = sum exp(a - m); c' = sum exp(a - m) * g  (c = c'/Z)
+    float z = 0.f, cg = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < active) {
+        float a[VEC], gv[VEC];
+        unpack<T>(sraw[k], a);
+        if (BWD) unpack<T>(graw[k], gv);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          if (col0 + e < active) {
+            const float ex = exp_for<T>(a[e] - m);
+            z += ex;
+            if (BWD) cg = fmaf(ex, gv[e], cg);
+          }
+        }
+      }
+    }
+    group_reduce2<SumOp>(g, z, cg);
+    // An all-masked row has max = -inf and exp(-inf - -inf) = NaN in the reference chain.
+    const bool dead = (active <= 0);
+    const float rz = 1.f / z;
+    const float c = cg * rz;            // sum_j y_j g_j
+    T* prow = FWD ? P + row * cols : nullptr;
+    T* drow = BWD ? dS + row * cols : nullptr;
+    // pass 3: outputs
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < cols) {
+        float y[VEC], d[VEC];
+        if (col0 < active) {
+          float a[VEC], gv[VEC];
+          unpack<T>(sraw[k], a);
+          if (BWD) unpack<T>(graw[k], gv);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            if (col0 + e < active) {
+              const float ex = exp_for<T>(a[e] - m);
+              y[e] = std::is_same<T, float>::value ? ex / z : ex * rz;
+              if (BWD) d[e] = y[e] * gv[e] - c * y[e];
+            } else { y[e] = 0.f; d[e] = 0.f; }
+          }
+        } else {
+          const float fill = dead ? __int_as_float(0x7fc00000) : 0.f;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) { y[e] = fill; d[e] = fill; }
+        }
+        if (FWD) st_stream(prow + col0, pack<T>(y));
+        if (BWD) {
+          if (beta) st_stream(drow + col0, pack_accumulate<T>(d, ld_stream(drow + col0)));
+          else st_stream(drow + col0, pack<T>(d));
+        }
+      }
+    }
+  }
+}
+
+// Element-wise fallback: any cols, any element-aligned pointers.  One CTA per row, rows re-read
+// from global memory (L1/L2) in each pass.
+template <typename T, bool FWD, bool BWD>
+__global__ void __launch_bounds__(256)
+softmax_rows_generic_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__ S, const T* __restrict__ dP,
+                            int64_t rows, int64_t cols, int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
+                            int beta) {
+  __shared__ float sm[33];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    int64_t active = cols;
+    if (mask_mode == CACTI_B200_MASK_CAUSAL) {
+      int64_t q = (row / q_div) % q_mod + q_off;
+      active = q < 0 ? 0 : (q + 1 < cols ? q + 1 : cols);
+    }
+    const T* srow = S + row * cols;
+    float m = -INFINITY;
+    for (int64_t j = threadIdx.x; j < active; j += blockDim.x) m = fmaxf(m, Elem<T>::to_f32(srow[j]));
+    m = block_reduce<MaxOp>(m, sm);
+    float z = 0.f, cg = 0.f;
+    for (int64_t j = threadIdx.x; j < active; j += blockDim.x) {
+      const float ex = exp_for<T>(Elem<T>::to_f32(srow[j]) - m);
+      z += ex;
+      if (BWD) cg = fmaf(ex, Elem<T>::to_f32(dP[row * cols + j]), cg);
+    }
+    z = block_reduce<SumOp>(z, sm);
+    if (BWD) cg = block_reduce<SumOp>(cg, sm);
+    const float rz = 1.f / z, c = cg * rz;
+    const float fill = active <= 0 ? __int_as_float(0x7fc00000) : 0.f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+      float y = fill, d = fill;
+      if (j < active) {
+        const float ex = exp_for<T>(Elem<T>::to_f32(srow[j]) - m);
+        y = std::is_same<T, float>::value ? ex / z : ex * rz;
+        if (BWD) d = y * Elem<T>::to_f32(dP[row * cols + j]) - c * y;
+      }
+      if (FWD) P[row * cols + j] = Elem<T>::from_f32(y);
+      if (BWD) {
+        T* o = dS + row * cols + j;
+        *o = beta ? Elem<T>::from_f32(Elem<T>::to_f32(*o) + round_to<T>(d)) : Elem<T>::from_f32(d);
+      }
+    }
+  }
+}
+
+template <typename T, bool FWD, bool BWD>
+static int launch_softmax(uint64_t p, uint64_t ds, uint64_t s, uint64_t dp, int64_t rows, int64_t cols,
+                          int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off, int beta, cudaStream_t st) {
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int NVMAX = 8;
+  T* P = reinterpret_cast<T*>(p); T* dS = reinterpret_cast<T*>(ds);
+  const T* S = reinterpret_cast<const T*>(s); const T* dP = reinterpret_cast<const T*>(dp);
+  const bool vec_ok = (cols % VEC == 0) && aligned16(s) && (!FWD || aligned16(p)) &&
+                      (!BWD || (aligned16(ds) && aligned16(dp))) && cols / VEC <= 512LL * NVMAX;
+  if (vec_ok) {
+    GroupPlan pl = plan_group(cols / VEC, NVMAX, 128, g_softmax_threads);
+    if (pl.ok) {
+      const int threads = pl.G * pl.groups;
+      const int64_t want = (rows + pl.groups - 1) / pl.groups;
+      int64_t grid = (int64_t)kNumSMs * g_softmax_ctas_per_sm;
+      if (grid > want) grid = want;
+      const size_t smem = (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
+#define CB_LAUNCH(NV_)                                                                               \
+  softmax_rows_kernel<T, NV_, FWD, BWD><<<(unsigned)grid, threads, smem, st>>>(                      \
+      P, dS, S, dP, rows, (int)cols, pl.G, mask_mode, q_div, q_mod, q_off, beta)
+      switch (pl.NV) {
+        case 1: CB_LAUNCH(1); break;
+        case 2: CB_LAUNCH(2); break;
+        case 4: CB_LAUNCH(4); break;
+        default: CB_LAUNCH(8); break;
+      }
+#undef CB_LAUNCH
+      return check_launch();
+    }
+  }
+  int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  softmax_rows_generic_kernel<T, FWD, BWD><<<(unsigned)grid, 256, 0, st>>>(P, dS, S, dP, rows, cols, mask_mode,
+                                                                           q_div, q_mod, q_off, beta);
+  return check_launch();
+}
+
+static int softmax_entry(bool fwd, bool bwd, uint64_t p, uint64_t ds, uint64_t s, uint64_t dp, int64_t rows,
+                         int64_t cols, int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off, int dtype,
+                         int beta, void* stream) {
+  if (rows < 0 || cols < 0 || cols > 0x7fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
+  if (mask_mode != CACTI_B200_MASK_NONE && mask_mode != CACTI_B200_MASK_CAUSAL) return CACTI_B200_ERR_INVALID_VALUE;
+  if (mask_mode == CACTI_B200_MASK_CAUSAL && (q_div <= 0 || q_mod <= 0)) return CACTI_B200_ERR_INVALID_VALUE;
+  if (beta != 0 && beta != 1) return CACTI_B200_ERR_INVALID_VALUE;
+  if (rows == 0 || cols == 0) return CACTI_B200_OK;
+  if (!s || (fwd && !p) || (bwd && (!ds || !dp))) return CACTI_B200_ERR_INVALID_VALUE;
+  if (mask_mode == CACTI_B200_MASK_NONE) { q_div = 1; q_mod = 1; q_off = 0; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    if (fwd && bwd) return launch_softmax<T, true, true>(p, ds, s, dp, rows, cols, mask_mode, q_div, q_mod, q_off, beta, st);
+    if (fwd) return launch_softmax<T, true, false>(p, ds, s, dp, rows, cols, mask_mode, q_div, q_mod, q_off, beta, st);
+    return launch_softmax<T, false, true>(p, ds, s, dp, rows, cols, mask_mode, q_div, q_mod, q_off, beta, st);
+  });
+}
+
+}  // namespace cb
+
+extern "C" {
+int cacti_b200_softmax_fwd(cacti_b200_dptr p, cacti_b200_dptr s, int64_t rows, int64_t cols, int mask_mode,
+                           int64_t q_div, int64_t q_mod, int64_t q_off, int dtype, cacti_b200_stream stream) {
+  return cb::softmax_entry(true, false, p, 0, s, 0, rows, cols, mask_mode, q_div, q_mod, q_off, dtype, 0, stream);
+}
+int cacti_b200_softmax_bwd(cacti_b200_dptr ds, cacti_b200_dptr s, cacti_b200_dptr dp, int64_t rows, int64_t cols,
+                           int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off, int dtype, int beta_ds,
+                           cacti_b200_stream stream) {
+  return cb::softmax_entry(false, true, 0, ds, s, dp, rows, cols, mask_mode, q_div, q_mod, q_off, dtype, beta_ds, stream);
+}
+int cacti_b200_softmax_fwd_bwd(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b200_dptr s, cacti_b200_dptr dp,
+                               int64_t rows, int64_t cols, int mask_mode, int64_t q_div, int64_t q_mod,
+                               int64_t q_off, int dtype, int beta_ds, cacti_b200_stream stream) {
+  return cb::softmax_entry(true, true, p, ds, s, dp, rows, cols, mask_mode, q_div, q_mod, q_off, dtype, beta_ds, stream);
+}
+}

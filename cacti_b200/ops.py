@@ -1,0 +1,221 @@
+"""Torch-tensor front end of the C ABI: argument marshalling only, no arithmetic.
+
+Every function takes CUDA tensors (torch owns the memory and the stream), passes raw pointers to
+libcacti_b200.so and raises CactiB200Error on a non-zero return code.  Function names follow the
+C ABI, which follows the reference ops: rms_norm (src/librarium/llama.rs:442-451), inner_softmax
+(src/op.rs trait MathUnaryOps), symplectic_embed (llama.rs:463-465), standard_silu * up
+(llama.rs:526-527), inner_softmax_categorical_nll (src/op.rs:1223-1231), outer_select
+(src/op.rs:1207-1220).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import capi
+from .capi import MASK_CAUSAL, MASK_NONE, R_16BF, R_16F, R_16U, R_32F, R_32I, check, lib
+
+_DT = {torch.float32: R_32F, torch.float16: R_16F, torch.bfloat16: R_16BF}
+_IDX = {torch.int32: R_32I, torch.uint16: R_16U, torch.int16: R_16U}
+
+
+def _dt(t: torch.Tensor) -> int:
+    return _DT[t.dtype]
+
+
+def _ptr(t) -> int:
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise ValueError("cacti_b200 takes device tensors only (there is no CPU path)")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ws(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# ---- K1 ---------------------------------------------------------------------------------------
+def rmsnorm_workspace(rows: int, cols: int, device) -> torch.Tensor:
+    return _ws(lib().cacti_b200_rmsnorm_workspace_bytes(rows, cols), device)
+
+
+def rmsnorm_fwd(x, gamma, eps, y=None):
+    rows, cols = x.shape
+    y = torch.empty_like(x) if y is None else y
+    check(lib().cacti_b200_rmsnorm_fwd(_ptr(y), _ptr(x), _ptr(gamma), eps, rows, cols, _dt(x), _stream()), "rmsnorm_fwd")
+    return y
+
+
+def rmsnorm_bwd(x, gamma, dy, eps, dx=None, dgamma=None, beta_dx=0, beta_dgamma=0, dgamma_dtype=None, workspace=None):
+    rows, cols = x.shape
+    dx = torch.empty_like(x) if dx is None else dx
+    if dgamma is None:
+        dgamma = torch.empty(cols, dtype=dgamma_dtype or x.dtype, device=x.device)
+    ws = rmsnorm_workspace(rows, cols, x.device) if workspace is None else workspace
+    check(lib().cacti_b200_rmsnorm_bwd(_ptr(dx), _ptr(dgamma), _ptr(dy), _ptr(x), _ptr(gamma), eps, rows, cols, _dt(x),
+                                       _dt(dgamma), beta_dx, beta_dgamma, _ptr(ws), ws.numel(), _stream()), "rmsnorm_bwd")
+    return dx, dgamma
+
+
+def rmsnorm_fwd_bwd(x, gamma, dy, eps, y=None, dx=None, dgamma=None, beta_dx=0, beta_dgamma=0, dgamma_dtype=None,
+                    workspace=None):
+    rows, cols = x.shape
+    y = torch.empty_like(x) if y is None else y
+    dx = torch.empty_like(x) if dx is None else dx
+    if dgamma is None:
+        dgamma = torch.empty(cols, dtype=dgamma_dtype or x.dtype, device=x.device)
+    ws = rmsnorm_workspace(rows, cols, x.device) if workspace is None else workspace
+    check(lib().cacti_b200_rmsnorm_fwd_bwd(_ptr(y), _ptr(dx), _ptr(dgamma), _ptr(x), _ptr(gamma), _ptr(dy), eps, rows,
+                                           cols, _dt(x), _dt(dgamma), beta_dx, beta_dgamma, _ptr(ws), ws.numel(),
+                                           _stream()), "rmsnorm_fwd_bwd")
+    return y, dx, dgamma
+
+
+# ---- K2 ---------------------------------------------------------------------------------------
+def _mask_args(mask):
+    """mask: None or (q_div, q_mod, q_off)."""
+    if mask is None:
+        return MASK_NONE, 1, 1, 0
+    q_div, q_mod, q_off = mask
+    return MASK_CAUSAL, q_div, q_mod, q_off
+
+
+def softmax_fwd(s, mask=None, p=None):
+    rows, cols = s.shape
+    p = torch.empty_like(s) if p is None else p
+    m = _mask_args(mask)
+    check(lib().cacti_b200_softmax_fwd(_ptr(p), _ptr(s), rows, cols, *m, _dt(s), _stream()), "softmax_fwd")
+    return p
+
+
+def softmax_bwd(s, dp, mask=None, ds=None, beta=0):
+    rows, cols = s.shape
+    ds = torch.empty_like(s) if ds is None else ds
+    m = _mask_args(mask)
+    check(lib().cacti_b200_softmax_bwd(_ptr(ds), _ptr(s), _ptr(dp), rows, cols, *m, _dt(s), beta, _stream()), "softmax_bwd")
+    return ds
+
+
+def softmax_fwd_bwd(s, dp, mask=None, p=None, ds=None, beta=0):
+    rows, cols = s.shape
+    p = torch.empty_like(s) if p is None else p
+    ds = torch.empty_like(s) if ds is None else ds
+    m = _mask_args(mask)
+    check(lib().cacti_b200_softmax_fwd_bwd(_ptr(p), _ptr(ds), _ptr(s), _ptr(dp), rows, cols, *m, _dt(s), beta, _stream()),
+          "softmax_fwd_bwd")
+    return p, ds
+
+
+# ---- K3 ---------------------------------------------------------------------------------------
+def rope_tables(seq, head_dim, theta=10000.0, dtype=torch.float16, device="cuda"):
+    cos = torch.empty(seq, head_dim, dtype=dtype, device=device)
+    sin = torch.empty_like(cos)
+    check(lib().cacti_b200_rope_tables(_ptr(cos), _ptr(sin), seq, head_dim, theta, _DT[dtype], _stream()), "rope_tables")
+    return cos, sin
+
+
+def rope_fwd(x, cos, sin, pos_off=0, y=None):
+    tokens, heads, hd = x.shape
+    y = torch.empty_like(x) if y is None else y
+    check(lib().cacti_b200_rope_fwd(_ptr(y), _ptr(x), _ptr(cos), _ptr(sin), tokens, heads, hd, cos.shape[0], pos_off,
+                                    _dt(x), _stream()), "rope_fwd")
+    return y
+
+
+def rope_bwd(dy, cos, sin, pos_off=0, dx=None, beta=0):
+    tokens, heads, hd = dy.shape
+    dx = torch.empty_like(dy) if dx is None else dx
+    check(lib().cacti_b200_rope_bwd(_ptr(dx), _ptr(dy), _ptr(cos), _ptr(sin), tokens, heads, hd, cos.shape[0], pos_off,
+                                    _dt(dy), beta, _stream()), "rope_bwd")
+    return dx
+
+
+def rope_fwd_bwd(x, dy, cos, sin, pos_off=0, y=None, dx=None, beta=0):
+    tokens, heads, hd = x.shape
+    y = torch.empty_like(x) if y is None else y
+    dx = torch.empty_like(x) if dx is None else dx
+    check(lib().cacti_b200_rope_fwd_bwd(_ptr(y), _ptr(dx), _ptr(x), _ptr(dy), _ptr(cos), _ptr(sin), tokens, heads, hd,
+                                        cos.shape[0], pos_off, _dt(x), beta, _stream()), "rope_fwd_bwd")
+    return y, dx
+
+
+# ---- K4 ---------------------------------------------------------------------------------------
+def swiglu_fwd(gate, up, h=None):
+    h = torch.empty_like(gate) if h is None else h
+    check(lib().cacti_b200_swiglu_fwd(_ptr(h), _ptr(gate), _ptr(up), gate.numel(), _dt(gate), _stream()), "swiglu_fwd")
+    return h
+
+
+def swiglu_bwd(gate, up, dh, dgate=None, dup=None, beta_dgate=0, beta_dup=0):
+    dgate = torch.empty_like(gate) if dgate is None else dgate
+    dup = torch.empty_like(gate) if dup is None else dup
+    check(lib().cacti_b200_swiglu_bwd(_ptr(dgate), _ptr(dup), _ptr(gate), _ptr(up), _ptr(dh), gate.numel(), _dt(gate),
+                                      beta_dgate, beta_dup, _stream()), "swiglu_bwd")
+    return dgate, dup
+
+
+def swiglu_fwd_bwd(gate, up, dh, h=None, dgate=None, dup=None, beta_dgate=0, beta_dup=0):
+    h = torch.empty_like(gate) if h is None else h
+    dgate = torch.empty_like(gate) if dgate is None else dgate
+    dup = torch.empty_like(gate) if dup is None else dup
+    check(lib().cacti_b200_swiglu_fwd_bwd(_ptr(h), _ptr(dgate), _ptr(dup), _ptr(gate), _ptr(up), _ptr(dh), gate.numel(),
+                                          _dt(gate), beta_dgate, beta_dup, _stream()), "swiglu_fwd_bwd")
+    return h, dgate, dup
+
+
+# ---- K5 ---------------------------------------------------------------------------------------
+def softmax_nll_fwd_bwd(logits, targets, w=None, w_scalar=1.0, want_grad=True, want_sum=True, want_rows=True,
+                        dlogits=None, beta=0, status=None):
+    """Returns (loss_sum f32[1] | None, loss_rows f32[rows] | None, dlogits | None, status u32[1])."""
+    rows, vocab = logits.shape
+    dev = logits.device
+    loss_sum = torch.empty(1, dtype=torch.float32, device=dev) if want_sum else None
+    loss_rows = torch.empty(rows, dtype=torch.float32, device=dev) if want_rows else None
+    if want_grad and dlogits is None:
+        dlogits = torch.empty_like(logits)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    ws = _ws(lib().cacti_b200_softmax_nll_workspace_bytes(rows), dev)
+    check(lib().cacti_b200_softmax_nll_fwd_bwd(_ptr(loss_sum), _ptr(loss_rows), _ptr(dlogits) if want_grad else 0,
+                                               _ptr(logits), _ptr(targets), _IDX[targets.dtype], _ptr(w), w_scalar, rows,
+                                               vocab, _dt(logits), beta, _ptr(status), _ptr(ws), ws.numel(), _stream()),
+          "softmax_nll_fwd_bwd")
+    return loss_sum, loss_rows, (dlogits if want_grad else None), status
+
+
+# ---- K6 ---------------------------------------------------------------------------------------
+def gather_rows(table, tokens, out=None, status=None):
+    vocab, cols = table.shape
+    n = tokens.numel()
+    out = torch.empty(n, cols, dtype=table.dtype, device=table.device) if out is None else out
+    status = torch.zeros(1, dtype=torch.int32, device=table.device) if status is None else status
+    check(lib().cacti_b200_gather_rows(_ptr(out), _ptr(table), _ptr(tokens), _IDX[tokens.dtype], n, vocab, cols,
+                                       _dt(table), _ptr(status), _stream()), "gather_rows")
+    return out, status
+
+
+def scatter_add_rows(dy, tokens, vocab, dtable=None, beta=0, status=None):
+    n, cols = dy.shape
+    dev = dy.device
+    dtable = torch.empty(vocab, cols, dtype=dy.dtype, device=dev) if dtable is None else dtable
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    ws = _ws(lib().cacti_b200_scatter_add_rows_workspace_bytes(n, vocab), dev)
+    check(lib().cacti_b200_scatter_add_rows(_ptr(dtable), _ptr(dy), _ptr(tokens), _IDX[tokens.dtype], n, vocab, cols,
+                                            _dt(dy), beta, _ptr(ws), ws.numel(), _ptr(status), _stream()),
+          "scatter_add_rows")
+    return dtable, status
+
+
+# ---- K7 ---------------------------------------------------------------------------------------
+def accumulate(dst, src):
+    check(lib().cacti_b200_accumulate(_ptr(dst), _ptr(src), dst.numel(), _dt(dst), _stream()), "accumulate")
+    return dst
+
+
+def add(a, b, out=None):
+    out = torch.empty_like(a) if out is None else out
+    check(lib().cacti_b200_add(_ptr(out), _ptr(a), _ptr(b), a.numel(), _dt(a), _stream()), "add")
+    return out

@@ -1,0 +1,202 @@
+/* cacti_b200.h -- C ABI of libcacti_b200.so: hand-written sm_100a kernels that replace
+ * the Futhark-generated forward/backward thunks (and the cuBLAS GEMM thunks) of cacti.
+ *
+ * The ABI follows the conventions of cacti's own FFI crate so that a new symbol
+ * table can sit beside the existing ones (cacti_gpu_cu_ffi/src/bindings.rs:378-504):
+ *   - every function returns int: 0 = success, anything else is an error code
+ *     (cacti_gpu_cu_ffi/src/lib.rs:96-105 maps non-zero to Err(code));
+ *   - device pointers are 64-bit integers (CUdeviceptr, cacti_gpu_cu_ffi/src/types.rs:22-25);
+ *   - streams are raw CUstream handles (types.rs:78), NULL = the legacy default stream
+ *     the reference runs on (src/pctx/nvgpu.rs:263);
+ *   - element types use cudaDataType_t codes (types.rs:97-102).
+ * No function allocates, frees or synchronises (except where a comment says so);
+ * outputs and workspaces are caller-allocated, as for the reference's GEMM thunks
+ * (src/thunk/op.rs:4574-4578).  One control thread per device context, as in the
+ * reference (src/ctx.rs:21-29).  No function aborts the process or traps the device:
+ * a bad argument is a return code, a bad index inside device data is a code written
+ * to a caller-supplied status word.
+ *
+ * Modes: the reference runs a thunk as Apply (fresh output), Accumulate (out += f(args),
+ * an elementwise add in the output's dtype, src/thunk/mod.rs:1691-1733) or Initialize
+ * (src/thunk/mod.rs:347-351).  Here every gradient output takes `beta`: 0 = Apply,
+ * 1 = Accumulate, with the new value rounded to the output dtype before the add.
+ *
+ * Layout: packed row-major, reductions over the innermost dimension
+ * (src/cell/mod.rs:1913-1926).  Arguments may be views at an arbitrary element
+ * offset (src/cell/mod.rs:2111-2122): a kernel checks 16-byte alignment at run time
+ * and falls back to an element-wise path, so any element-aligned pointer is legal.
+ */
+#ifndef CACTI_B200_H_
+#define CACTI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint64_t cacti_b200_dptr;     /* CUdeviceptr */
+typedef void*    cacti_b200_stream;   /* CUstream    */
+
+/* return codes */
+enum {
+  CACTI_B200_OK                = 0,
+  CACTI_B200_ERR_INVALID_VALUE = 1,  /* null pointer, negative size, size overflow      */
+  CACTI_B200_ERR_DTYPE         = 2,  /* dtype code not supported by this entry point    */
+  CACTI_B200_ERR_WORKSPACE     = 3,  /* workspace missing or smaller than *_workspace_bytes */
+  CACTI_B200_ERR_LAUNCH        = 4,  /* the CUDA runtime refused a launch; see cacti_b200_last_cuda_error */
+  CACTI_B200_ERR_SHAPE         = 5,  /* shape outside what the entry point supports     */
+  CACTI_B200_ERR_INDEX_RANGE   = 6,  /* written to a status word: token/target index out of range */
+  CACTI_B200_ERR_NO_DEVICE     = 7   /* current device is not an sm_100 part            */
+};
+
+/* element types: cudaDataType_t codes (cacti_gpu_cu_ffi/src/types.rs:97-102) */
+enum {
+  CACTI_B200_R_32F  = 0,
+  CACTI_B200_R_16F  = 2,
+  CACTI_B200_R_16BF = 14,
+  CACTI_B200_R_32I  = 10,   /* index type: int32 targets/tokens */
+  CACTI_B200_R_16U  = 22    /* index type: uint16 tokens (src/librarium/llama.rs:383-384) */
+};
+
+/* mask_mode of the row softmax */
+enum {
+  CACTI_B200_MASK_NONE   = 0,
+  CACTI_B200_MASK_CAUSAL = 1   /* column c of row r is masked when c > q_pos(r) */
+};
+
+int         cacti_b200_version(void);               /* 10000*major + 100*minor + patch */
+const char* cacti_b200_error_string(int code);
+int         cacti_b200_last_cuda_error(void);       /* cudaError_t of the last failed launch on this thread */
+/* Launch-shape knobs ("softmax_threads", "rmsnorm_ctas_per_sm", ...) for measurement sweeps.  No counterpart
+ * in the reference; results do not depend on them. */
+int         cacti_b200_tune(const char* name, int value);
+
+/* ---- K1 RMSNorm -----------------------------------------------------------------
+ * Replaces the 8-thunk chain of src/librarium/llama.rs:442-451
+ * (Cast src/thunk/op.rs:621, Square :2522, InnerMean :3150, AddScalar :1395, Sqrt :2609,
+ * BroadcastDiv :2358, BroadcastMul :2058, lossy Cast) and its adjoint chain.
+ *   y  = T(f32(gamma) * f32(x) / sqrt(mean(f32(x)^2) + eps))                [rows, cols]
+ *   dx = T(gamma*dy/s - x * sum_j(gamma_j dy_j x_j) / (cols * s^3))
+ *   dgamma_j = sum_rows dy_ij * x_ij / s_i, written in `dgamma_dtype`
+ *              (dtype, or CACTI_B200_R_32F for a partial that a collective reduces).
+ * Statistics are recomputed in the backward; the fused form reads x and dy once.
+ * The workspace holds per-CTA column partials (deterministic two-stage reduction,
+ * no floating-point atomics). */
+size_t cacti_b200_rmsnorm_workspace_bytes(int64_t rows, int64_t cols);
+int cacti_b200_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr gamma, float eps,
+                           int64_t rows, int64_t cols, int dtype, cacti_b200_stream stream);
+int cacti_b200_rmsnorm_bwd(cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr dy,
+                           cacti_b200_dptr x, cacti_b200_dptr gamma, float eps,
+                           int64_t rows, int64_t cols, int dtype, int dgamma_dtype,
+                           int beta_dx, int beta_dgamma,
+                           cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
+int cacti_b200_rmsnorm_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr dgamma,
+                               cacti_b200_dptr x, cacti_b200_dptr gamma, cacti_b200_dptr dy, float eps,
+                               int64_t rows, int64_t cols, int dtype, int dgamma_dtype,
+                               int beta_dx, int beta_dgamma,
+                               cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
+
+/* ---- K2 masked row softmax --------------------------------------------------------
+ * Replaces cast + BlockTriElemAffine (src/thunk/op.rs:4189-4278) + InnerSoftmax (:3257-3383)
+ * + lossy cast (src/librarium/llama.rs:502-505), and the adjoint InnerSoftmaxPostAdj
+ * (:3386-3457) with its recomputed softmax (:3376-3382) and the mask adjoint (:4265-4276).
+ *   P  = T(softmax_row(mask(f32(S))));  dS = T(mask'(u - (sum u) y)), u = y*f32(dP)
+ * q_pos(r) = (r / q_div) % q_mod + q_off.  The reference layout [B,Sq,H,Sk] has
+ * q_div = H, q_mod = Sq; a [B,H,Sq,Sk] layout has q_div = 1, q_mod = Sq.
+ * Masked inputs are not read; masked outputs are written as exact zeros. */
+int cacti_b200_softmax_fwd(cacti_b200_dptr p, cacti_b200_dptr s, int64_t rows, int64_t cols,
+                           int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
+                           int dtype, cacti_b200_stream stream);
+int cacti_b200_softmax_bwd(cacti_b200_dptr ds, cacti_b200_dptr s, cacti_b200_dptr dp,
+                           int64_t rows, int64_t cols,
+                           int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
+                           int dtype, int beta_ds, cacti_b200_stream stream);
+int cacti_b200_softmax_fwd_bwd(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b200_dptr s, cacti_b200_dptr dp,
+                               int64_t rows, int64_t cols,
+                               int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
+                               int dtype, int beta_ds, cacti_b200_stream stream);
+
+/* ---- K3 RoPE -----------------------------------------------------------------------
+ * Replaces symplectic_embed (src/librarium/llama.rs:463-465): BroadcastMul + InnerSymplecticMap
+ * (:975-1049) + BroadcastMul + Add (src/thunk/op.rs:1480-1535), and their adjoints.
+ *   y = x*cos + rot(x)*sin, rot(x) = [-x[hd/2:], x[:hd/2]];  dx = dy*cos + R(dy*sin)
+ * x: [tokens, heads, head_dim]; cos, sin: [pos_mod, head_dim]; position of a token row t
+ * is (t + pos_off) % pos_mod.  f16 follows the reference's f16 arithmetic (one rounding
+ * per primitive); f32 and bf16 compute in f32 and round once.
+ * rope_tables fills cos/sin as init_constants does (src/librarium/llama.rs:389-411). */
+int cacti_b200_rope_tables(cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t seq, int64_t head_dim,
+                           float theta, int dtype, cacti_b200_stream stream);
+int cacti_b200_rope_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr cos, cacti_b200_dptr sin,
+                        int64_t tokens, int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off,
+                        int dtype, cacti_b200_stream stream);
+int cacti_b200_rope_bwd(cacti_b200_dptr dx, cacti_b200_dptr dy, cacti_b200_dptr cos, cacti_b200_dptr sin,
+                        int64_t tokens, int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off,
+                        int dtype, int beta_dx, cacti_b200_stream stream);
+int cacti_b200_rope_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr x, cacti_b200_dptr dy,
+                            cacti_b200_dptr cos, cacti_b200_dptr sin,
+                            int64_t tokens, int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off,
+                            int dtype, int beta_dx, cacti_b200_stream stream);
+
+/* ---- K4 SwiGLU -----------------------------------------------------------------------
+ * Replaces StandardSilu (src/thunk/op.rs:2867-2910) + Mul (:2001-2056) of
+ * src/librarium/llama.rs:526-527 and their adjoints (Logistic :2821-2865 recomputed).
+ *   h = silu(g)*u;  du = silu(g)*dh;  dg = (dh*u) * (y*(1-t)+t), y = silu(g), t = sigmoid(g)
+ * n = number of elements.  f16 keeps the reference's per-primitive f16 rounding. */
+int cacti_b200_swiglu_fwd(cacti_b200_dptr h, cacti_b200_dptr gate, cacti_b200_dptr up,
+                          int64_t n, int dtype, cacti_b200_stream stream);
+int cacti_b200_swiglu_bwd(cacti_b200_dptr dgate, cacti_b200_dptr dup,
+                          cacti_b200_dptr gate, cacti_b200_dptr up, cacti_b200_dptr dh,
+                          int64_t n, int dtype, int beta_dgate, int beta_dup, cacti_b200_stream stream);
+int cacti_b200_swiglu_fwd_bwd(cacti_b200_dptr h, cacti_b200_dptr dgate, cacti_b200_dptr dup,
+                              cacti_b200_dptr gate, cacti_b200_dptr up, cacti_b200_dptr dh,
+                              int64_t n, int dtype, int beta_dgate, int beta_dup, cacti_b200_stream stream);
+
+/* ---- K5 softmax cross-entropy ----------------------------------------------------------
+ * Replaces cast + InnerSoftmaxCategoricalNLL (src/thunk/op.rs:3460-3569) and its adjoint
+ * (recomputed InnerSoftmax, InnerOneHot :883-997, Sub :1782, BroadcastMul), call site
+ * src/librarium/llama.rs:542-545.
+ *   loss_i = -log softmax(f32(x_i))[k_i];  dlogits = T(w_i * (softmax(x_i) - onehot(k_i)))
+ * w_i = w_rows[i] when w_rows != 0, else w_scalar.  loss_sum (optional, f32[1]) receives
+ * sum_i w_i*loss_i, reduced in a fixed order; loss_rows (optional, f32[rows]) the per-row
+ * losses.  When loss_sum is requested and loss_rows is 0, `workspace` must hold
+ * cacti_b200_softmax_nll_workspace_bytes(rows) bytes.  target_dtype: R_32I or R_16U.
+ * A target outside [0, vocab) (the reference asserts, src/thunk/op.rs:3538) writes
+ * CACTI_B200_ERR_INDEX_RANGE to *status (u32, optional), the row's loss becomes NaN and its
+ * gradient omits the one-hot term; nothing traps. */
+size_t cacti_b200_softmax_nll_workspace_bytes(int64_t rows);
+int cacti_b200_softmax_nll_fwd_bwd(cacti_b200_dptr loss_sum, cacti_b200_dptr loss_rows, cacti_b200_dptr dlogits,
+                                   cacti_b200_dptr logits, cacti_b200_dptr targets, int target_dtype,
+                                   cacti_b200_dptr w_rows, float w_scalar,
+                                   int64_t rows, int64_t vocab, int dtype, int beta_dlogits,
+                                   cacti_b200_dptr status, cacti_b200_dptr workspace, size_t workspace_bytes,
+                                   cacti_b200_stream stream);
+/* forward only: dlogits = 0 skips the gradient */
+
+/* ---- K6 embedding gather / scatter-add ----------------------------------------------------
+ * gather replaces OuterSelect (src/thunk/op.rs:1229-1314): out[i,:] = table[tok[i],:], a bit-exact copy.
+ * scatter_add is its adjoint (a Futhark vjp in the reference): dtable[v,:] (+)= sum_{i: tok[i]=v} dy[i,:],
+ * summed in f32 in token order and rounded once; beta = 0 also zero-fills untouched rows.
+ * Out-of-range tokens are reported through *status and skipped. */
+int cacti_b200_gather_rows(cacti_b200_dptr out, cacti_b200_dptr table, cacti_b200_dptr tokens, int token_dtype,
+                           int64_t n_tokens, int64_t vocab, int64_t cols, int dtype,
+                           cacti_b200_dptr status, cacti_b200_stream stream);
+size_t cacti_b200_scatter_add_rows_workspace_bytes(int64_t n_tokens, int64_t vocab);
+int cacti_b200_scatter_add_rows(cacti_b200_dptr dtable, cacti_b200_dptr dy, cacti_b200_dptr tokens, int token_dtype,
+                                int64_t n_tokens, int64_t vocab, int64_t cols, int dtype, int beta,
+                                cacti_b200_dptr workspace, size_t workspace_bytes,
+                                cacti_b200_dptr status, cacti_b200_stream stream);
+
+/* ---- K7 add / accumulate ------------------------------------------------------------------
+ * accumulate replaces the NVRTC kernels accumulate_1d_{f32,f16,u16}_idx32
+ * (src/pctx/nvgpu.rs:2598-2668): dst[i] += src[i].  add replaces AddFutThunkSpec
+ * (src/thunk/op.rs:1480-1535, the residual adds of src/librarium/llama.rs:514,533). */
+int cacti_b200_accumulate(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t n, int dtype, cacti_b200_stream stream);
+int cacti_b200_add(cacti_b200_dptr out, cacti_b200_dptr a, cacti_b200_dptr b, int64_t n, int dtype,
+                   cacti_b200_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* CACTI_B200_H_ */
