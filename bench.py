@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the fused forward+backward thunks on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N = 1): BASELINE config 2 -- causal row softmax forward+backward on scores
+[1, 32, 2048, 2048] fp16 (fp32 accumulation), one fused launch per step.  `value` is the algorithmic
+HBM GB/s of that launch with inputs resident in HBM; `e2e` is the same quantity measured through
+the C-ABI call with HOST buffers (pinned H2D of scores and dP, D2H of P and dScores inside the timed
+region, pipelined per (batch, head) block).  Under torchrun (N > 1) every rank runs its own config-2
+sized batch (weak scaling, no data-path collective: softmax rows are independent).
+
+`--impl reference` times the CPU restatement of the reference chain (oracle/ref_chain.c: one OpenMP
+loop per primitive thunk over materialised intermediates, all host threads) on a bounded sample of
+the same workload; the reference itself (Rust + patched Futhark) cannot be built on this image.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HEADS, SEQ = 32, 2048                       # config 2: [1, 32, 2048, 2048]
+ROWS, COLS = HEADS * SEQ, SEQ
+ELEMS = ROWS * COLS
+ALGO_BYTES = 4 * ELEMS * 2                  # S, dP read; P, dS written; dense accounting (masked reads not credited)
+METRIC = "fused fwd+bwd thunk HBM GB/s (causal softmax, config 2)"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one softmax_rows_kernel launch on config 2
+# (profiles/softmax_fwd_bwd_cfg2.md); None until a capture exists.
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid, self.rows, self.proc = uuid, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_cores():
+    """Unique (core, socket) pairs, which is what the reference counts (src/pctx/smp.rs:158-181)."""
+    try:
+        out = subprocess.run(["lscpu", "-p=CORE,SOCKET"], capture_output=True, text=True).stdout
+        cores = {l for l in out.splitlines() if l and not l.startswith("#")}
+        n = len(cores)
+        avail = len(os.sched_getaffinity(0))
+        return max(1, min(n, avail)) if n else avail
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_time(sample_heads, reps, threads):
+    """Seconds per pass of the C restatement over `sample_heads` (batch, head) blocks of config 2."""
+    import numpy as np
+    from oracle import c_oracle as CO
+    from oracle import ref_chain as R
+    CO.set_num_threads(threads)
+    rows = sample_heads * SEQ
+    s = R.normal(0, (rows, COLS), np.float16, 0.1)
+    dp = R.normal(1, (rows, COLS), np.float16)
+    CO.softmax_fwd_bwd(s[:SEQ], dp[:SEQ], (1, SEQ, 0))            # warm-up (page in, spin up the team)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        CO.softmax_fwd_bwd(s, dp, (1, SEQ, 0))
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), rows
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = physical_cores()
+    sample_heads = 4
+    t0 = time.time()
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_reference_time(1, 1, threads)
+    sec, rows = cpu_reference_time(sample_heads, max(1, args.steps), threads)
+    gbs = (4 * rows * COLS * 2) / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3 * (ROWS / rows), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+        "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (BASELINE config 2)",
+                   "rows": ROWS, "cols": COLS},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample_heads} of 32 (batch, head) blocks = {rows} rows per step; "
+                                   "ms_per_step is scaled to the full 65536 rows"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.time() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_thunk(fn, launches, warmup, torch):
+    """Average device time per call of fn over `launches` back-to-back calls (CUDA events on the launch stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / launches * 1e-3
+
+
+def other_thunks(torch, ops, peak):
+    """Device-resident GB/s of the other fused thunks at their BASELINE shapes (explanatory, not the headline)."""
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(1)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device="cuda", generator=gen) * scale).half()
+
+    def report(name, sec, nbytes, launches):
+        out[name] = {"GB/s": round(nbytes / sec / 1e9, 1), "frac_of_peak": round(nbytes / sec / 1e9 / peak, 3),
+                     "us": round(sec * 1e6, 1), "algorithmic_bytes": nbytes, "launches_per_step": launches}
+
+    # K1 RMSNorm fwd+bwd at the config-5 activation shape [16384, 3200] f16
+    x, dy, g = rnd(16384, 3200), rnd(16384, 3200), rnd(3200)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    dg = torch.empty(3200, dtype=torch.float16, device="cuda")
+    ws = ops.rmsnorm_workspace(16384, 3200, x.device)
+    sec = time_thunk(lambda: ops.rmsnorm_fwd_bwd(x, g, dy, 1e-6, y=y, dx=dx, dgamma=dg, workspace=ws), 20, 5, torch)
+    report("rmsnorm_fwd_bwd[16384x3200,f16]", sec, 4 * 16384 * 3200 * 2 + 2 * 3200 * 2, 2)
+    del x, dy, y, dx
+    # K5 softmax-NLL config 3
+    lg = rnd(8192, 32000, scale=2.0)
+    tg = torch.randint(0, 32000, (8192,), device="cuda", dtype=torch.int32, generator=gen)
+    dl = torch.empty_like(lg)
+    sec = time_thunk(lambda: ops.softmax_nll_fwd_bwd(lg, tg, w_scalar=1.0 / 8192, dlogits=dl), 20, 5, torch)
+    report("softmax_nll_fwd_bwd[8192x32000,f16]", sec, 2 * 8192 * 32000 * 2 + 8192 * 4 + 4, 2)
+    del lg, dl
+    # K3 RoPE config 4 (one of Q / K per launch)
+    cos, sin = ops.rope_tables(2048, 100)
+    q, dq = rnd(16384, 32, 100), rnd(16384, 32, 100)
+    yq, dxq = torch.empty_like(q), torch.empty_like(q)
+    sec = time_thunk(lambda: ops.rope_fwd_bwd(q, dq, cos, sin, y=yq, dx=dxq), 20, 5, torch)
+    report("rope_fwd_bwd[16384x32x100,f16]", sec, 4 * 16384 * 3200 * 2, 1)
+    del q, dq, yq, dxq
+    # K4 SwiGLU config 4
+    ga, up, dh = rnd(16384, 8640), rnd(16384, 8640), rnd(16384, 8640)
+    h, dga, dup = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
+    sec = time_thunk(lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup), 20, 5, torch)
+    report("swiglu_fwd_bwd[16384x8640,f16]", sec, 6 * 16384 * 8640 * 2, 1)
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from cacti_b200 import capi, ops
+    capi.lib()                                   # raises when the CUDA library is missing: no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the CPU arm is --impl reference")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peak, peak_kind = measured_peak()
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    s = (torch.randn(ROWS, COLS, device=dev, generator=gen) * 0.1).half()
+    dp = torch.randn(ROWS, COLS, device=dev, generator=gen).half()
+    p, ds = torch.empty_like(s), torch.empty_like(s)
+    mask = (1, SEQ, 0)
+
+    def step():
+        ops.softmax_fwd_bwd(s, dp, mask, p=p, ds=ds)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", "")
+    with ClockSampler(uuid) as clocks:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+        # keep the sampler alive long enough to see the load on short runs
+        if dev_ms < 400:
+            t_end = time.time() + 0.6
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize()
+    t = torch.tensor([dev_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = t.item()
+    ms_step = ms_total / args.steps
+    value = world * ALGO_BYTES / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers through the same call, pipelined per (batch, head) block -------------
+    hs, hdp = s.cpu().pin_memory(), dp.cpu().pin_memory()
+    hp, hds = torch.empty_like(hs).pin_memory(), torch.empty_like(hs).pin_memory()
+    nblk, brow = HEADS, SEQ
+    NBUF = 4
+    bufs = [tuple(torch.empty(brow, COLS, dtype=torch.float16, device=dev) for _ in range(4)) for _ in range(NBUF)]
+    st_in, st_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream()
+
+    def e2e_step():
+        ev_in = [torch.cuda.Event() for _ in range(nblk)]
+        ev_k = [torch.cuda.Event() for _ in range(nblk)]
+        ev_out = [torch.cuda.Event() for _ in range(nblk)]
+        for b in range(nblk):
+            bs, bdp, bp, bds = bufs[b % NBUF]
+            r = slice(b * brow, (b + 1) * brow)
+            with torch.cuda.stream(st_in):
+                if b >= NBUF:
+                    st_in.wait_event(ev_k[b - NBUF])          # inputs of the block that used this slot are consumed
+                bs.copy_(hs[r], non_blocking=True)
+                bdp.copy_(hdp[r], non_blocking=True)
+                ev_in[b].record(st_in)
+            main.wait_event(ev_in[b])
+            if b >= NBUF:
+                main.wait_event(ev_out[b - NBUF])             # outputs of that slot are on the host
+            ops.softmax_fwd_bwd(bs, bdp, mask, p=bp, ds=bds)
+            ev_k[b].record(main)
+            with torch.cuda.stream(st_out):
+                st_out.wait_event(ev_k[b])
+                hp[r].copy_(bp, non_blocking=True)
+                hds[r].copy_(bds, non_blocking=True)
+                ev_out[b].record(st_out)
+        main.wait_stream(st_out)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+    e2e_ok = bool(torch.equal(hp[:SEQ], p[:SEQ].cpu()) and torch.equal(hds[-SEQ:], ds[-SEQ:].cpu()))
+    del hs, hdp, hp, hds, bufs
+
+    line = None
+    if rank == 0:
+        thunks = other_thunks(torch, ops, peak) if not args.no_extra else {}
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            threads = physical_cores()
+            sec, rows = cpu_reference_time(4, 3, threads)
+            cpu = {"value": (4 * rows * COLS * 2) / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                   "sample": f"4 of 32 (batch, head) blocks ({rows} rows), median of 3 passes of oracle/ref_chain.c"}
+        achieved = ALGO_BYTES / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 per GPU (BASELINE config 2)",
+                       "rows": ROWS, "cols": COLS, "mask": "causal, applied in-kernel",
+                       "l2": "working set 1.07 GB per step, far larger than the 126 MB L2; no flush needed"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8TBs": achieved / 8000.0, "peak_kind": peak_kind + " copy bandwidth",
+                         "traffic": NCU_TRAFFIC_BYTES, "algorithmic_bytes": ALGO_BYTES,
+                         "kernel": "softmax_rows_kernel<half,8,fwd,bwd>"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * ALGO_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 2 * ELEMS * 2, "d2h_bytes_per_step": 2 * ELEMS * 2, "verified": e2e_ok},
+            "gpu_launches": args.steps, "clocks": clocks.summary(), "thunks": thunks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-thunk table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
