@@ -4,9 +4,10 @@
 
 namespace cb {
 thread_local int g_last_cuda_error = 0;
-extern int g_softmax_threads, g_softmax_ctas_per_sm;
-extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_ctas_per_sm;
-extern int g_nll_gpref, g_nll_ctas_per_sm;
+__device__ unsigned g_dev_error = 0;
+extern int g_softmax_threads, g_softmax_waves;
+extern int g_rmsnorm_threads, g_rmsnorm_gpref;
+extern int g_nll_gpref;
 extern int g_rope_threads, g_rope_ctas_per_sm;
 extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
 }  // namespace cb
@@ -31,16 +32,26 @@ const char* cacti_b200_error_string(int code) {
 
 int cacti_b200_last_cuda_error(void) { return cb::g_last_cuda_error; }
 
+// Reads (and clears) the sticky device-side error word: 0 = none, 1 = a staged row copy never completed,
+// 2 = a GEMM pipeline wait ran out.  Synchronises the device.
+int cacti_b200_device_error(unsigned* out) {
+  if (!out) return CACTI_B200_ERR_INVALID_VALUE;
+  unsigned v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, cb::g_dev_error, sizeof(v)) != cudaSuccess) return cb::check_launch() ? CACTI_B200_ERR_LAUNCH : CACTI_B200_ERR_LAUNCH;
+  if (v) cudaMemcpyToSymbol(cb::g_dev_error, &zero, sizeof(zero));
+  *out = v;
+  return CACTI_B200_OK;
+}
+
 // Launch-shape knobs for measurement sweeps; not part of the thunk contract.  Returns 0, or
 // CACTI_B200_ERR_INVALID_VALUE for an unknown name or a value outside the knob's range.
 int cacti_b200_tune(const char* name, int value) {
   using namespace cb;
   struct Knob { const char* name; int* p; int lo, hi; };
   const Knob knobs[] = {
-      {"softmax_threads", &g_softmax_threads, 32, 512},   {"softmax_ctas_per_sm", &g_softmax_ctas_per_sm, 1, 32},
+      {"softmax_threads", &g_softmax_threads, 32, 512},   {"softmax_waves", &g_softmax_waves, 1, 64},
       {"rmsnorm_threads", &g_rmsnorm_threads, 32, 512},   {"rmsnorm_gpref", &g_rmsnorm_gpref, 32, 512},
-      {"rmsnorm_ctas_per_sm", &g_rmsnorm_ctas_per_sm, 1, 8},
-      {"nll_gpref", &g_nll_gpref, 32, 512},               {"nll_ctas_per_sm", &g_nll_ctas_per_sm, 1, 32},
+      {"nll_gpref", &g_nll_gpref, 32, 512},
       {"rope_threads", &g_rope_threads, 32, 256},         {"rope_ctas_per_sm", &g_rope_ctas_per_sm, 1, 64},
       {"swiglu_threads", &g_swiglu_threads, 32, 256},     {"swiglu_ctas_per_sm", &g_swiglu_ctas_per_sm, 1, 64},
   };

@@ -166,6 +166,50 @@ template <typename Op> __device__ __forceinline__ float group_reduce(GroupCtx& g
   return a;
 }
 
+// ---- row staging: bulk async copies (TMA, untiled) into shared memory, completed on an mbarrier ----
+// Each row group owns one stage buffer and one mbarrier.  The group's first lane arms the barrier
+// with the byte count and issues cp.async.bulk for the row(s); every lane then waits on the phase
+// bit.  After the group has moved the row from shared memory into registers it meets on its barrier
+// and the next row's copy is issued into the same buffer, so a row is always in flight while the
+// previous one is being reduced.  Sources and sizes must be multiples of 16 bytes.
+// Every wait is bounded: if a copy never completes the kernel records kDevErrStageTimeout in
+// g_dev_error and the group stops; it never spins forever.
+constexpr unsigned kDevErrStageTimeout = 1u;
+constexpr unsigned kDevErrGemmTimeout = 2u;
+extern __device__ unsigned g_dev_error;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Returns false after ~2^22 failed polls (each poll itself blocks for a hardware time slice).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned err_code) {
+  for (unsigned it = 0; it < (1u << 22); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicMax(&g_dev_error, err_code);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---- block reduction for the element-wise fallback kernels (whole CTA = one row) -----------
 template <typename Op> __device__ __forceinline__ float block_reduce(float v, float* smem /* >= 33 floats */) {
   v = warp_reduce<Op>(v);
@@ -196,6 +240,24 @@ template <typename F> inline int dispatch_dtype(int dtype, F&& f) {
 // Rows of up to 32*nv_max vectors go to one warp (shuffle-only reductions, several rows per CTA).
 // Longer rows go to a multi-warp group: the fewest vectors per thread that keeps the group at
 // or below g_pref threads, else nv_max vectors per thread and up to 512 threads.
+constexpr size_t kMaxDynSmem = 200 * 1024;      // of the 227 KB a CTA may use
+
+// CTAs of `kern` that fit on one SM with this block size and dynamic shared memory; also raises the
+// kernel's dynamic shared memory limit when needed.  The answer is cached per (kernel, config).
+template <typename K> inline int resident_ctas(K kern, int threads, size_t smem) {
+  struct Key { const void* k; int t; size_t s; int n; };
+  static thread_local Key cache[32];
+  static thread_local int used = 0;
+  const void* kp = reinterpret_cast<const void*>(kern);
+  for (int i = 0; i < used; ++i)
+    if (cache[i].k == kp && cache[i].t == threads && cache[i].s == smem) return cache[i].n;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) n = 1;
+  if (used < 32) cache[used++] = Key{kp, threads, smem, n};
+  return n;
+}
+
 struct GroupPlan { int G; int NV; int groups; bool ok; };
 inline GroupPlan plan_group(int64_t nvec, int nv_max, int g_pref, int target_threads) {
   GroupPlan p{32, 1, 1, false};

@@ -17,7 +17,6 @@ namespace cb {
 
 int g_rmsnorm_threads = 512;      // target threads per CTA on the vector path
 int g_rmsnorm_gpref = 256;        // preferred threads per row group
-int g_rmsnorm_ctas_per_sm = 2;
 
 constexpr int kRmsMaxPartials = kNumSMs * 8;
 
@@ -26,46 +25,60 @@ __global__ void __launch_bounds__(512)
 rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
                     const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
                     float eps, int64_t rows, int cols, int G, int beta_dx) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
-  float* red = smem;                                              // group reductions
-  float* colacc = smem + (size_t)2 * groups * kMaxWarpsPerGroup * 2;  // [cols] dgamma fold
+  const unsigned row_bytes = (unsigned)cols * sizeof(T);
+  const unsigned stage_bytes = row_bytes * (BWD ? 2 : 1);
+  // shared: [groups] stage buffers (x row, dy row) | mbarriers | reduction slots | dgamma fold [cols]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * stage_bytes);
+  float* red = reinterpret_cast<float*>(bars + groups);
+  float* colacc = red + (size_t)2 * groups * kMaxWarpsPerGroup * 2;
   GroupCtx g = make_group(G, red);
+  unsigned char* stage = smem_raw + (size_t)g.gid * stage_bytes;
+  uint64_t* bar = bars + g.gid;
+  if (g.lane == 0) mbar_init(bar, 1);
+  mbar_fence_init();
+  __syncthreads();
   const float inv_cols = 1.f / (float)cols;
 
-  // Register budget: with NV <= 2 gamma stays in registers and rows are double-buffered; with
-  // NV = 4 gamma is re-read per row (it stays in L1) and the next row is not prefetched.
-  constexpr bool LEAN = NV > 2;
-  constexpr int NG = LEAN ? 1 : NV;
-  uint4 graw[NG];       // gamma for this thread's columns, raw
+  uint4 graw[NV];       // gamma for this thread's columns, raw
   float dg[NV][VEC];    // dgamma accumulators
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
     const int col0 = (g.lane + k * G) * VEC;
-    if (!LEAN && col0 < cols) graw[k % NG] = ld_keep(gamma + col0);
+    if (col0 < cols) graw[k] = ld_keep(gamma + col0);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) dg[k][e] = 0.f;
   }
 
   const int64_t stride = (int64_t)gridDim.x * groups;
   int64_t row = (int64_t)blockIdx.x * groups + g.gid;
-  // Rows are double-buffered in registers: the loads of the next row are issued before the
-  // current row is reduced, so each thread keeps 2*NV (fwd) or 4*NV (fwd+bwd) 16-byte loads in flight.
-  constexpr int NP = LEAN ? 1 : NV;
-  uint4 xraw[NV], yraw[NV], xnext[NP], ynext[NP];
-#define CB_LOAD_ROW(r_, xr_, yr_)                                         \
-  _Pragma("unroll") for (int k = 0; k < NV; ++k) {                        \
-    const int col0 = (g.lane + k * G) * VEC;                              \
-    if (col0 < cols) {                                                    \
-      xr_[k] = ld_stream(X + (r_) * cols + col0);                         \
-      if (BWD) yr_[k] = ld_stream(dY + (r_) * cols + col0);               \
-    }                                                                     \
-  }
-  if (!LEAN && row < rows) { CB_LOAD_ROW(row, xraw, yraw) }
+  unsigned phase = 0;
+  auto issue = [&](int64_t r) {
+    if (g.lane == 0) {
+      mbar_expect_tx(bar, stage_bytes);
+      bulk_g2s(stage, X + r * cols, row_bytes, bar);
+      if (BWD) bulk_g2s(stage + row_bytes, dY + r * cols, row_bytes, bar);
+    }
+  };
+  bool alive = true;
+  if (row < rows) issue(row);
   for (; row < rows; row += stride) {
-    if (LEAN) { CB_LOAD_ROW(row, xraw, yraw) }
-    else if (row + stride < rows) { CB_LOAD_ROW(row + stride, xnext, ynext) }
+    if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) { alive = false; break; }
+    phase ^= 1;
+    uint4 xraw[NV], yraw[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int col0 = (g.lane + k * G) * VEC;
+      if (col0 < cols) {
+        xraw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
+        if (BWD) yraw[k] = *reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T));
+      }
+    }
+    group_barrier(g);                       // stage consumed: the next row may land in it
+    if (row + stride < rows) issue(row + stride);
+
     // pass 1: ss = sum x^2, c1 = sum gamma*dy*x
     float ss = 0.f, c1 = 0.f;
 #pragma unroll
@@ -75,19 +88,21 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
         float x[VEC];
         unpack<T>(xraw[k], x);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) ss = fmaf(x[e], x[e], ss);
+        for (int e = 0; e < VEC; ++e) ss = __fmaf_rn(x[e], x[e], ss);
         if (BWD) {
           float gy[VEC], gm[VEC];
           unpack<T>(yraw[k], gy);
-          unpack<T>(LEAN ? ld_keep(gamma + col0) : graw[k % NG], gm);
+          unpack<T>(graw[k], gm);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) c1 = fmaf(gm[e] * gy[e], x[e], c1);
+          for (int e = 0; e < VEC; ++e) c1 = __fmaf_rn(__fmul_rn(gm[e], gy[e]), x[e], c1);
         }
       }
     }
     group_reduce2<SumOp>(g, ss, c1);
-    const float s = sqrtf(ss * inv_cols + eps);
-    const float coef = BWD ? c1 / (s * s) / (s + s) * inv_cols * 2.f : 0.f;   // c1 / (cols * s^3)
+    const float s = __fsqrt_rn(__fmaf_rn(ss, inv_cols, eps));
+    const float rs = __frcp_rn(s);
+    // c1 / (cols * s^3); explicitly rounded ops so that fwd, bwd and fwd_bwd give the same bits
+    const float coef = BWD ? __fmul_rn(__fmul_rn(__fmul_rn(c1, inv_cols), rs), __fmul_rn(rs, rs)) : 0.f;
     // pass 2: outputs
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -95,13 +110,13 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
       if (col0 < cols) {
         float x[VEC], gm[VEC], t[VEC];
         unpack<T>(xraw[k], x);
-        unpack<T>(LEAN ? ld_keep(gamma + col0) : graw[k % NG], gm);
+        unpack<T>(graw[k], gm);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) t[e] = x[e] / s;
+        for (int e = 0; e < VEC; ++e) t[e] = __fmul_rn(x[e], rs);
         if (FWD) {
           float y[VEC];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) y[e] = gm[e] * t[e];
+          for (int e = 0; e < VEC; ++e) y[e] = __fmul_rn(gm[e], t[e]);
           st_stream(Y + row * cols + col0, pack<T>(y));
         }
         if (BWD) {
@@ -109,8 +124,8 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
           unpack<T>(yraw[k], gy);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            dg[k][e] = fmaf(gy[e], t[e], dg[k][e]);
-            d[e] = (gm[e] * gy[e]) / s - x[e] * coef;
+            dg[k][e] = __fmaf_rn(gy[e], t[e], dg[k][e]);
+            d[e] = __fmaf_rn(__fmul_rn(gm[e], gy[e]), rs, -__fmul_rn(x[e], coef));
           }
           T* o = dX + row * cols + col0;
           if (beta_dx) st_stream(o, pack_accumulate<T>(d, ld_stream(o)));
@@ -118,12 +133,8 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
         }
       }
     }
-    if (!LEAN) {
-#pragma unroll
-      for (int k = 0; k < NV; ++k) { xraw[k] = xnext[k % NP]; if (BWD) yraw[k] = ynext[k % NP]; }
-    }
   }
-#undef CB_LOAD_ROW
+  (void)alive;
 
   if (BWD) {
     // fold the CTA's row groups in group order, then one partial row per CTA
@@ -234,33 +245,37 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
   float* wsf = reinterpret_cast<float*>(ws);
   const bool vec_ok = (cols % VEC == 0) && aligned16(x) && aligned16(gamma) && (!FWD || aligned16(y)) &&
                       (!BWD || (aligned16(dx) && aligned16(dy))) && cols / VEC <= 512LL * NVMAX &&
-                      (size_t)cols * sizeof(float) <= 160 * 1024;
+                      (size_t)cols * sizeof(float) <= 64 * 1024;
   if (vec_ok) {
     GroupPlan pl = plan_group(cols / VEC, NVMAX, g_rmsnorm_gpref, g_rmsnorm_threads);
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      int64_t grid = (int64_t)kNumSMs * g_rmsnorm_ctas_per_sm;
-      if (grid > kRmsMaxPartials) grid = kRmsMaxPartials;
-      if (grid > want) grid = want;
-      const size_t smem = ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+      const size_t stage = (size_t)cols * sizeof(T) * (BWD ? 2 : 1);
+      const size_t smem = pl.groups * stage + pl.groups * sizeof(uint64_t) +
+                          ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+      int64_t grid = 0;
 #define CB_LAUNCH(NV_)                                                                                      \
   do {                                                                                                      \
     auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD>;                                                      \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                                           \
+    if (grid > kRmsMaxPartials) grid = kRmsMaxPartials;                                                     \
+    if (grid > want) grid = want;                                                                           \
     kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, beta_dx); \
   } while (0)
-      switch (pl.NV) {
-        case 1: CB_LAUNCH(1); break;
-        case 2: CB_LAUNCH(2); break;
-        default: CB_LAUNCH(4); break;
-      }
+      if (smem <= kMaxDynSmem) {
+        switch (pl.NV) {
+          case 1: CB_LAUNCH(1); break;
+          case 2: CB_LAUNCH(2); break;
+          default: CB_LAUNCH(4); break;
+        }
 #undef CB_LAUNCH
-      int rc = check_launch();
-      if (rc || !BWD) return rc;
-      rmsnorm_dgamma_finalize_kernel<TO><<<(unsigned)((cols + 31) / 32), 512, 0, st>>>(dG, wsf, (int)grid,
-                                                                                      (int)cols, beta_dg);
-      return check_launch();
+        int rc = check_launch();
+        if (rc || !BWD) return rc;
+        rmsnorm_dgamma_finalize_kernel<TO><<<(unsigned)((cols + 31) / 32), 512, 0, st>>>(dG, wsf, (int)grid,
+                                                                                        (int)cols, beta_dg);
+        return check_launch();
+      }
     }
   }
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;

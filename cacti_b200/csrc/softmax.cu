@@ -16,7 +16,7 @@
 namespace cb {
 
 int g_softmax_threads = 256;   // threads per CTA on the warp-per-row path (tunable)
-int g_softmax_ctas_per_sm = 8; // grid = SMs * this (capped by the row count)
+int g_softmax_waves = 1;       // grid = SMs * resident CTAs * this (capped by the row count)
 
 __device__ __forceinline__ int active_cols(int64_t row, int cols, int mask_mode,
                                            int64_t q_div, int64_t q_mod, int64_t q_off) {
@@ -26,85 +26,129 @@ __device__ __forceinline__ int active_cols(int64_t row, int cols, int mask_mode,
   return (q + 1 < (int64_t)cols) ? (int)(q + 1) : cols;
 }
 
+// -inf / 0 fill of the masked tail of the one vector that straddles the causal boundary, so that the
+// three passes below need no per-element predicate.
+template <typename T>
+__device__ __forceinline__ void mask_tail(uint4& s, uint4& g, int nact, bool bwd) {
+  constexpr int VEC = Elem<T>::VEC;
+  float a[VEC];
+  unpack<T>(s, a);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) if (e >= nact) a[e] = -INFINITY;
+  s = pack<T>(a);
+  if (bwd) {
+    unpack<T>(g, a);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) if (e >= nact) a[e] = 0.f;
+    g = pack<T>(a);
+  }
+}
+
 template <typename T, int NV, bool FWD, bool BWD>
 __global__ void __launch_bounds__(512)
 softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__ S, const T* __restrict__ dP,
                     int64_t rows, int cols, int G, int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off,
                     int beta) {
-  extern __shared__ float red[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
-  GroupCtx g = make_group(G, red);
   const int groups = blockDim.x / G;
+  const unsigned row_bytes = (unsigned)cols * sizeof(T);
+  const unsigned stage_bytes = row_bytes * (BWD ? 2 : 1);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * stage_bytes);
+  float* red = reinterpret_cast<float*>(bars + groups);
+  GroupCtx g = make_group(G, red);
+  unsigned char* stage = smem_raw + (size_t)g.gid * stage_bytes;
+  uint64_t* bar = bars + g.gid;
+  if (g.lane == 0) mbar_init(bar, 1);
+  mbar_fence_init();
+  __syncthreads();
 
-  for (int64_t row = (int64_t)blockIdx.x * groups + g.gid; row < rows; row += (int64_t)gridDim.x * groups) {
-    const int active = active_cols(row, cols, mask_mode, q_div, q_mod, q_off);
-    const T* srow = S + row * cols;
-    const T* grow = BWD ? dP + row * cols : nullptr;
+  const int64_t stride = (int64_t)gridDim.x * groups;
+  int64_t row = (int64_t)blockIdx.x * groups + g.gid;
+  unsigned phase = 0;
+  // lane 0 of the group starts the bulk copies of a row's unmasked prefix; returns its length in columns
+  auto issue = [&](int64_t r) -> int {
+    const int act = active_cols(r, cols, mask_mode, q_div, q_mod, q_off);
+    if (act > 0 && g.lane == 0) {
+      const unsigned bytes = ((unsigned)act * sizeof(T) + 15u) & ~15u;
+      mbar_expect_tx(bar, bytes * (BWD ? 2u : 1u));
+      bulk_g2s(stage, S + r * cols, bytes, bar);
+      if (BWD) bulk_g2s(stage + row_bytes, dP + r * cols, bytes, bar);
+    }
+    return act;
+  };
+  int active = row < rows ? issue(row) : 0;
+  for (; row < rows; row += stride) {
     uint4 sraw[NV], graw[NV];
+    if (active > 0) {
+      if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) return;
+      phase ^= 1;
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < active) {
-        sraw[k] = ld_stream(srow + col0);
-        if (BWD) graw[k] = ld_stream(grow + col0);
+      for (int k = 0; k < NV; ++k) {
+        const int col0 = (g.lane + k * G) * VEC;
+        if (col0 < active) {
+          sraw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
+          if (BWD) graw[k] = *reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T));
+          if (active - col0 < VEC) mask_tail<T>(sraw[k], graw[k], active - col0, BWD);
+        }
       }
     }
+    group_barrier(g);                       // the stage buffer has been consumed by every lane
+    const int cur_active = active;
+    active = (row + stride < rows) ? issue(row + stride) : 0;
+
     // pass 1: row maximum
     float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < active) {
+      if (col0 < cur_active) {
         float a[VEC];
         unpack<T>(sraw[k], a);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) if (col0 + e < active) m = fmaxf(m, a[e]);
+        for (int e = 0; e < VEC; ++e) m = fmaxf(m, a[e]);
       }
     }
     m = group_reduce<MaxOp>(g, m);
-    // pass 2: Z = sum exp(a - m); c' = sum exp(a - m) * g  (c = c'/Z)
+    // pass 2: Z = sum exp(a - m); cg = sum exp(a - m) * g  (sum_j y_j g_j = cg / Z)
     float z = 0.f, cg = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < active) {
+      if (col0 < cur_active) {
         float a[VEC], gv[VEC];
         unpack<T>(sraw[k], a);
         if (BWD) unpack<T>(graw[k], gv);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          if (col0 + e < active) {
-            const float ex = exp_for<T>(a[e] - m);
-            z += ex;
-            if (BWD) cg = fmaf(ex, gv[e], cg);
-          }
+          const float ex = exp_for<T>(a[e] - m);
+          z = __fadd_rn(z, ex);
+          if (BWD) cg = __fmaf_rn(ex, gv[e], cg);
         }
       }
     }
     group_reduce2<SumOp>(g, z, cg);
     // An all-masked row has max = -inf and exp(-inf - -inf) = NaN in the reference chain.
-    const bool dead = (active <= 0);
-    const float rz = 1.f / z;
-    const float c = cg * rz;            // sum_j y_j g_j
+    const bool dead = (cur_active <= 0);
+    const float rz = __frcp_rn(z);
+    const float c = __fmul_rn(cg, rz);
     T* prow = FWD ? P + row * cols : nullptr;
     T* drow = BWD ? dS + row * cols : nullptr;
-    // pass 3: outputs
+    // pass 3: outputs (explicitly rounded ops: every entry point produces the same bits)
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
       if (col0 < cols) {
         float y[VEC], d[VEC];
-        if (col0 < active) {
+        if (col0 < cur_active) {
           float a[VEC], gv[VEC];
           unpack<T>(sraw[k], a);
           if (BWD) unpack<T>(graw[k], gv);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            if (col0 + e < active) {
-              const float ex = exp_for<T>(a[e] - m);
-              y[e] = std::is_same<T, float>::value ? ex / z : ex * rz;
-              if (BWD) d[e] = y[e] * gv[e] - c * y[e];
-            } else { y[e] = 0.f; d[e] = 0.f; }
+            const float ex = exp_for<T>(a[e] - m);
+            y[e] = std::is_same<T, float>::value ? __fdiv_rn(ex, z) : __fmul_rn(ex, rz);
+            if (BWD) d[e] = __fmaf_rn(y[e], gv[e], -__fmul_rn(c, y[e]));
           }
         } else {
           const float fill = dead ? __int_as_float(0x7fc00000) : 0.f;
@@ -178,21 +222,28 @@ static int launch_softmax(uint64_t p, uint64_t ds, uint64_t s, uint64_t dp, int6
     GroupPlan pl = plan_group(cols / VEC, NVMAX, 128, g_softmax_threads);
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
+      const size_t stage = (size_t)cols * sizeof(T) * (BWD ? 2 : 1);
+      const size_t smem = pl.groups * stage + pl.groups * sizeof(uint64_t) +
+                          (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      int64_t grid = (int64_t)kNumSMs * g_softmax_ctas_per_sm;
-      if (grid > want) grid = want;
-      const size_t smem = (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
 #define CB_LAUNCH(NV_)                                                                               \
-  softmax_rows_kernel<T, NV_, FWD, BWD><<<(unsigned)grid, threads, smem, st>>>(                      \
-      P, dS, S, dP, rows, (int)cols, pl.G, mask_mode, q_div, q_mod, q_off, beta)
-      switch (pl.NV) {
-        case 1: CB_LAUNCH(1); break;
-        case 2: CB_LAUNCH(2); break;
-        case 4: CB_LAUNCH(4); break;
-        default: CB_LAUNCH(8); break;
-      }
+  do {                                                                                               \
+    auto kern = softmax_rows_kernel<T, NV_, FWD, BWD>;                                               \
+    int64_t grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem) * g_softmax_waves;          \
+    if (grid > want) grid = want;                                                                    \
+    kern<<<(unsigned)grid, threads, smem, st>>>(P, dS, S, dP, rows, (int)cols, pl.G, mask_mode,      \
+                                                q_div, q_mod, q_off, beta);                          \
+  } while (0)
+      if (smem <= kMaxDynSmem) {
+        switch (pl.NV) {
+          case 1: CB_LAUNCH(1); break;
+          case 2: CB_LAUNCH(2); break;
+          case 4: CB_LAUNCH(4); break;
+          default: CB_LAUNCH(8); break;
+        }
 #undef CB_LAUNCH
-      return check_launch();
+        return check_launch();
+      }
     }
   }
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;

@@ -11,7 +11,6 @@
 namespace cb {
 
 int g_nll_gpref = 512;
-int g_nll_ctas_per_sm = 4;
 
 template <typename TI> __device__ __forceinline__ int64_t load_index(const void* p, int64_t i);
 template <> __device__ __forceinline__ int64_t load_index<int32_t>(const void* p, int64_t i) {
@@ -26,23 +25,41 @@ __global__ void __launch_bounds__(512)
 softmax_nll_rows_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const T* __restrict__ L,
                         const void* __restrict__ targets, const float* __restrict__ w_rows, float w_scalar,
                         int64_t rows, int cols, int G, int beta, unsigned* __restrict__ status) {
-  extern __shared__ float red[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
-  GroupCtx g = make_group(G, red);
   const int groups = blockDim.x / G;
-  for (int64_t row = (int64_t)blockIdx.x * groups + g.gid; row < rows; row += (int64_t)gridDim.x * groups) {
-    const T* lrow = L + row * cols;
+  const unsigned row_bytes = (unsigned)cols * sizeof(T);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * row_bytes);
+  float* red = reinterpret_cast<float*>(bars + groups);
+  GroupCtx g = make_group(G, red);
+  unsigned char* stage = smem_raw + (size_t)g.gid * row_bytes;
+  uint64_t* bar = bars + g.gid;
+  if (g.lane == 0) mbar_init(bar, 1);
+  mbar_fence_init();
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * groups;
+  int64_t row = (int64_t)blockIdx.x * groups + g.gid;
+  unsigned phase = 0;
+  auto issue = [&](int64_t r) {
+    if (g.lane == 0) { mbar_expect_tx(bar, row_bytes); bulk_g2s(stage, L + r * cols, row_bytes, bar); }
+  };
+  if (row < rows) issue(row);
+  for (; row < rows; row += stride) {
+    const int64_t tgt = load_index<TI>(targets, row);
+    const bool tgt_ok = tgt >= 0 && tgt < cols;
+    const float w = w_rows ? w_rows[row] : w_scalar;
+    if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) return;
+    phase ^= 1;
     uint4 raw[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cols) raw[k] = ld_stream(lrow + col0);
+      if (col0 < cols) raw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
     }
-    const int64_t tgt = load_index<TI>(targets, row);
-    const bool tgt_ok = tgt >= 0 && tgt < cols;
-    // the target logit: one extra 2/4-byte read per thread of a line this row already touches
-    const float a_t = tgt_ok ? Elem<T>::to_f32(lrow[tgt]) : 0.f;
-    const float w = w_rows ? w_rows[row] : w_scalar;
+    // the target logit, read from the staged row (the stored bit pattern, converted exactly)
+    const float a_t = tgt_ok ? Elem<T>::to_f32(reinterpret_cast<const T*>(stage)[tgt]) : 0.f;
+    group_barrier(g);
+    if (row + stride < rows) issue(row + stride);
 
     float m = -INFINITY;
 #pragma unroll
@@ -161,21 +178,27 @@ static int launch_nll(float* loss_rows, uint64_t dl, uint64_t l, const void* tar
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      int64_t grid = (int64_t)kNumSMs * g_nll_ctas_per_sm;
-      if (grid > want) grid = want;
-      const size_t smem = (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
+      const size_t smem = pl.groups * ((size_t)cols * sizeof(T) + sizeof(uint64_t)) +
+                          (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
 #define CB_LAUNCH(NV_)                                                                          \
-  softmax_nll_rows_kernel<T, TI, NV_, BWD><<<(unsigned)grid, threads, smem, st>>>(              \
-      loss_rows, dL, L, targets, w_rows, w_scalar, rows, (int)cols, pl.G, beta, status)
-      switch (pl.NV) {
-        case 1: CB_LAUNCH(1); break;
-        case 2: CB_LAUNCH(2); break;
-        case 4: CB_LAUNCH(4); break;
-        case 8: CB_LAUNCH(8); break;
-        default: CB_LAUNCH(16); break;
-      }
+  do {                                                                                          \
+    auto kern = softmax_nll_rows_kernel<T, TI, NV_, BWD>;                                       \
+    int64_t grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                       \
+    if (grid > want) grid = want;                                                               \
+    kern<<<(unsigned)grid, threads, smem, st>>>(loss_rows, dL, L, targets, w_rows, w_scalar,    \
+                                                rows, (int)cols, pl.G, beta, status);           \
+  } while (0)
+      if (smem <= kMaxDynSmem) {
+        switch (pl.NV) {
+          case 1: CB_LAUNCH(1); break;
+          case 2: CB_LAUNCH(2); break;
+          case 4: CB_LAUNCH(4); break;
+          case 8: CB_LAUNCH(8); break;
+          default: CB_LAUNCH(16); break;
+        }
 #undef CB_LAUNCH
-      return check_launch();
+        return check_launch();
+      }
     }
   }
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;

@@ -69,7 +69,10 @@ enum {
 int         cacti_b200_version(void);               /* 10000*major + 100*minor + patch */
 const char* cacti_b200_error_string(int code);
 int         cacti_b200_last_cuda_error(void);       /* cudaError_t of the last failed launch on this thread */
-/* Launch-shape knobs ("softmax_threads", "rmsnorm_ctas_per_sm", ...) for measurement sweeps.  No counterpart
+/* Device-side sticky error word (no counterpart in the reference): every wait inside a kernel is bounded; a
+ * wait that runs out records a code here instead of hanging.  0 = none.  Reading clears it and synchronises. */
+int         cacti_b200_device_error(unsigned* out);
+/* Launch-shape knobs ("softmax_threads", "rmsnorm_gpref", ...) for measurement sweeps.  No counterpart
  * in the reference; results do not depend on them. */
 int         cacti_b200_tune(const char* name, int value);
 

@@ -61,7 +61,9 @@ def test_rmsnorm_shapes(cuda, dtype, rows, cols):
     y, dx, dg = ops.rmsnorm_fwd_bwd(dev(x), dev(gamma), dev(dy), 1e-6)
     ry, rdx, rdg = R.ideal64_rmsnorm(x, gamma, dy, 1e-6)
     assert_close(host(y), ry, kind, "y")
-    assert_close(host(dx), rdx, kind, "dx", floor_frac=1.0 if cols < 8 else None)
+    # dx = gamma*dy/s - x*c is a difference of O(|dy|) terms (for cols = 1 it cancels to ~eps): hold it to the
+    # scale of its terms
+    assert_close(host(dx), rdx, kind, "dx", floor_abs=float(np.abs(dy.astype(np.float64)).max()) if cols < 16 else 0.0)
     assert_close(host(dg), rdg, kind, "dgamma")
     # separate entry points give the same bits as the fused one
     assert torch.equal(ops.rmsnorm_fwd(dev(x), dev(gamma), 1e-6), y)
@@ -81,8 +83,8 @@ def test_rmsnorm_unaligned_view_and_accumulate(cuda):
         old_dg = R.normal(78, (3200,), np.float16)
         dxa, dga = dev(old_dx), dev(old_dg)
         ops.rmsnorm_bwd(xin, g, dyin, a["eps"], dx=dxa, dgamma=dga, beta_dx=1, beta_dgamma=1)
-        assert_close(host(dxa), old_dx + GOLD["c2_dx"], "float16", "dx accumulate")
-        assert_close(host(dga), old_dg + GOLD["c2_dgamma"], "float16", "dgamma accumulate")
+        assert_close(host(dxa), old_dx + GOLD["c2_dx"], "float16", "dx accumulate", floor_frac=1.0)
+        assert_close(host(dga), old_dg + GOLD["c2_dgamma"], "float16", "dgamma accumulate", floor_frac=1.0)
 
 
 def test_rmsnorm_f32_partial_and_bf16(cuda):
@@ -159,7 +161,7 @@ def test_softmax_unaligned_accumulate_bf16_dead_rows(cuda):
         old = R.normal(79, a["s"].shape, np.float16)
         acc = dev(old)
         ops.softmax_bwd(sin_, dpin, a["mask"], ds=acc, beta=1)
-        assert_close(host(acc), old + GOLD["c3_ds"], "float16", "dS accumulate")
+        assert_close(host(acc), old + GOLD["c3_ds"], "float16", "dS accumulate", floor_frac=1.0)
     sb = R.bf16_round(R.normal(32, (9, 512), scale=0.5))
     db = R.bf16_round(R.normal(33, (9, 512)))
     p, ds = ops.softmax_fwd_bwd(dev(sb, bf16=True), dev(db, bf16=True), (1, 9, 100))
@@ -288,8 +290,8 @@ def test_swiglu_shapes(cuda, dtype, n):
     old_g, old_u = R.normal(53, (n,), dtype), R.normal(54, (n,), dtype)
     ag, au = dev(old_g), dev(old_u)
     ops.swiglu_bwd(dev(g), dev(u), dev(dh), dgate=ag, dup=au, beta_dgate=1, beta_dup=1)
-    assert_close(host(ag), old_g + rdg, kind, "dg accumulate")
-    assert_close(host(au), old_u + rdu, kind, "du accumulate")
+    assert_close(host(ag), old_g + rdg, kind, "dg accumulate", floor_frac=1.0)
+    assert_close(host(au), old_u + rdu, kind, "du accumulate", floor_frac=1.0)
 
 
 def test_swiglu_bf16_and_extremes(cuda):
@@ -349,7 +351,7 @@ def test_nll_shapes(cuda, dtype, rows, vocab):
     old = R.normal(62, (rows, vocab), dtype)
     acc = dev(old)
     ops.softmax_nll_fwd_bwd(dev(lg), dev(tg), w_scalar=float(w), dlogits=acc, beta=1)
-    assert_close(host(acc), old + rd, kind, "dlogits accumulate")
+    assert_close(host(acc), old + rd, kind, "dlogits accumulate", floor_frac=1.0)
 
 
 def test_nll_out_of_range_target_sets_status(cuda):
@@ -372,11 +374,15 @@ def test_nll_config3_properties(cuda):
     gen = torch.Generator(device="cuda").manual_seed(0)
     lg = (torch.randn(rows, vocab, device="cuda", generator=gen) * 2).half()
     tg = torch.randint(0, vocab, (rows,), device="cuda", generator=gen, dtype=torch.int32)
+    # property run with w = 1 (with w = 1/8192 most f16 gradient entries are below the f16 subnormal range):
+    # sum_j dlogits_ij = sum y - 1 = 0, and the target entry is the only negative one
+    _, _, d1, st = ops.softmax_nll_fwd_bwd(lg, tg, w_scalar=1.0)
+    assert host(st)[0] == 0
+    assert d1.float().sum(-1).abs().max().item() < 2e-3
+    assert ((d1 < 0).sum(-1) == 1).all() and (d1[torch.arange(rows), tg.long()] < 0).all()
+    del d1
     ls, lr, d, st = ops.softmax_nll_fwd_bwd(lg, tg, w_scalar=1.0 / rows)
     assert host(st)[0] == 0
-    # sum_j dlogits_ij = w (sum y - 1) = 0; the target entry is the only negative one
-    assert d.float().sum(-1).abs().max().item() < 1e-6
-    assert ((d < 0).sum(-1) == 1).all() and (d[torch.arange(rows), tg.long()] < 0).all()
     idx = np.array([0, 1, 4095, 8191])
     rl, rd, _ = R.ref_softmax_nll(host(lg[idx]), host(tg)[idx], np.float32(1.0 / rows))
     assert_close(host(lr[idx]), rl, "float32", "loss sampled rows")
@@ -397,7 +403,7 @@ def test_gather_scatter_golden(cuda, tok_dtype):
     old = R.normal(80, (50, 64), np.float16)
     acc = dev(old)
     ops.scatter_add_rows(dev(a["dy"]), tk, 50, dtable=acc, beta=1)
-    assert_close(host(acc), old + GOLD["c8_dtable"], "float16", "dtable accumulate")
+    assert_close(host(acc), old + GOLD["c8_dtable"], "float16", "dtable accumulate", floor_frac=1.0)
     dt2, _ = ops.scatter_add_rows(dev(a["dy"]), tk, 50)
     assert torch.equal(dt, dt2)          # run-to-run identical
 

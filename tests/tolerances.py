@@ -13,7 +13,7 @@ FLOOR_FRAC = {"float32": 1e-1, "float16": 1e-1, "bfloat16": 1e-1}
 ABS_MIN = {"float32": 1e-30, "float16": 2.0 ** -24, "bfloat16": 1e-30}
 
 
-def assert_close(got, ref, kind, what="", rtol=None, floor_frac=None):
+def assert_close(got, ref, kind, what="", rtol=None, floor_frac=None, floor_abs=0.0):
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
@@ -24,7 +24,7 @@ def assert_close(got, ref, kind, what="", rtol=None, floor_frac=None):
     rtol = RTOL[kind] if rtol is None else rtol
     ff = FLOOR_FRAC[kind] if floor_frac is None else floor_frac
     rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
-    bound = rtol * np.maximum(np.abs(ref), ff * rms) + ABS_MIN[kind]
+    bound = rtol * np.maximum(np.maximum(np.abs(ref), ff * rms), floor_abs) + ABS_MIN[kind]
     err = np.abs(got - ref)
     bad = err > bound
     if bad.any():
