@@ -145,19 +145,21 @@ template <typename Op> __device__ __forceinline__ float warp_reduce(float v) {
   return v;
 }
 
-// Reduce two values at once (a and b use the same Op).
+// Reduce two values at once (a and b use the same Op).  Stage 1: shuffles inside each warp; lane 0
+// of every warp publishes its pair; stage 2 after the group barrier: lane l of every warp picks up
+// warp l's pair and the warp reduces again with shuffles (a group has at most 32 warps).
 template <typename Op> __device__ __forceinline__ void group_reduce2(GroupCtx& g, float& a, float& b) {
   a = warp_reduce<Op>(a);
   b = warp_reduce<Op>(b);
   if (g.G == 32) return;
   const int groups = blockDim.x / g.G;
-  float* slot = g.red + ((size_t)(g.phase * groups + g.gid) * kMaxWarpsPerGroup) * 2;
-  const int w = g.lane >> 5;
-  if ((g.lane & 31) == 0) { slot[2 * w] = a; slot[2 * w + 1] = b; }
+  float2* slot = reinterpret_cast<float2*>(g.red) + (size_t)(g.phase * groups + g.gid) * kMaxWarpsPerGroup;
+  const int w = g.lane >> 5, l = g.lane & 31;
+  if (l == 0) slot[w] = make_float2(a, b);
   group_barrier(g);
-  float ra = Op::id(), rb = Op::id();
-  for (int i = 0; i < g.nwarps; ++i) { ra = Op::f(ra, slot[2 * i]); rb = Op::f(rb, slot[2 * i + 1]); }
-  a = ra; b = rb;
+  float2 v = l < g.nwarps ? slot[l] : make_float2(Op::id(), Op::id());
+  a = warp_reduce<Op>(v.x);
+  b = warp_reduce<Op>(v.y);
   g.phase ^= 1;
 }
 template <typename Op> __device__ __forceinline__ float group_reduce(GroupCtx& g, float a) {
@@ -226,6 +228,12 @@ template <typename Op> __device__ __forceinline__ float block_reduce(float v, fl
 // rounding).  f32 storage: the accurate library exp, so fp32 results stay within 1e-5 relative.
 template <typename T> __device__ __forceinline__ float exp_for(float x) { return __expf(x); }
 template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
+
+__device__ __forceinline__ float exp2f_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <typename F> inline int dispatch_dtype(int dtype, F&& f) {
   switch (dtype) {

@@ -17,6 +17,7 @@ namespace cb {
 
 int g_rmsnorm_threads = 512;      // target threads per CTA on the vector path
 int g_rmsnorm_gpref = 256;        // preferred threads per row group
+int g_rmsnorm_smem_kb = 96;       // shared memory per CTA spent on the row ring
 
 constexpr int kRmsMaxPartials = kNumSMs * 8;
 
@@ -24,20 +25,20 @@ template <typename T, int NV, bool FWD, bool BWD>
 __global__ void __launch_bounds__(512)
 rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
                     const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
-                    float eps, int64_t rows, int cols, int G, int beta_dx) {
+                    float eps, int64_t rows, int cols, int G, int nstages, int beta_dx) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
   const unsigned row_bytes = (unsigned)cols * sizeof(T);
   const unsigned stage_bytes = row_bytes * (BWD ? 2 : 1);
-  // shared: [groups] stage buffers (x row, dy row) | mbarriers | reduction slots | dgamma fold [cols]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * stage_bytes);
-  float* red = reinterpret_cast<float*>(bars + groups);
+  // shared: [groups][nstages] stage buffers (x row, dy row) | mbarriers | reduction slots | dgamma fold [cols]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * stage_bytes);
+  float* red = reinterpret_cast<float*>(bars + groups * nstages);
   float* colacc = red + (size_t)2 * groups * kMaxWarpsPerGroup * 2;
   GroupCtx g = make_group(G, red);
-  unsigned char* stage = smem_raw + (size_t)g.gid * stage_bytes;
-  uint64_t* bar = bars + g.gid;
-  if (g.lane == 0) mbar_init(bar, 1);
+  unsigned char* stage0 = smem_raw + (size_t)g.gid * nstages * stage_bytes;
+  uint64_t* bar0 = bars + g.gid * nstages;
+  if (g.lane < nstages) mbar_init(bar0 + g.lane, 1);
   mbar_fence_init();
   __syncthreads();
   const float inv_cols = 1.f / (float)cols;
@@ -53,20 +54,24 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
   }
 
   const int64_t stride = (int64_t)gridDim.x * groups;
-  int64_t row = (int64_t)blockIdx.x * groups + g.gid;
-  unsigned phase = 0;
-  auto issue = [&](int64_t r) {
+  const int64_t row0 = (int64_t)blockIdx.x * groups + g.gid;
+  // a ring of nstages rows per group keeps (nstages - 1) rows in flight while one is reduced
+  auto issue = [&](int64_t r, int sl) {
     if (g.lane == 0) {
-      mbar_expect_tx(bar, stage_bytes);
-      bulk_g2s(stage, X + r * cols, row_bytes, bar);
-      if (BWD) bulk_g2s(stage + row_bytes, dY + r * cols, row_bytes, bar);
+      unsigned char* dst = stage0 + (size_t)sl * stage_bytes;
+      mbar_expect_tx(bar0 + sl, stage_bytes);
+      bulk_g2s(dst, X + r * cols, row_bytes, bar0 + sl);
+      if (BWD) bulk_g2s(dst + row_bytes, dY + r * cols, row_bytes, bar0 + sl);
     }
   };
+  for (int sl = 0; sl < nstages; ++sl)
+    if (row0 + sl * stride < rows) issue(row0 + sl * stride, sl);
+  int slot = 0;
+  unsigned phase = 0;
   bool alive = true;
-  if (row < rows) issue(row);
-  for (; row < rows; row += stride) {
-    if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) { alive = false; break; }
-    phase ^= 1;
+  for (int64_t row = row0; row < rows; row += stride) {
+    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) { alive = false; break; }
+    const unsigned char* stage = stage0 + (size_t)slot * stage_bytes;
     uint4 xraw[NV], yraw[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -76,11 +81,11 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
         if (BWD) yraw[k] = *reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T));
       }
     }
-    group_barrier(g);                       // stage consumed: the next row may land in it
-    if (row + stride < rows) issue(row + stride);
+    const int cur_slot = slot;
+    if (++slot == nstages) { slot = 0; phase ^= 1; }
 
     // pass 1: ss = sum x^2, c1 = sum gamma*dy*x
-    float ss = 0.f, c1 = 0.f;
+    float sq[4] = {0.f, 0.f, 0.f, 0.f}, cq[4] = {0.f, 0.f, 0.f, 0.f};   // independent chains
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
@@ -88,17 +93,21 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
         float x[VEC];
         unpack<T>(xraw[k], x);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) ss = __fmaf_rn(x[e], x[e], ss);
+        for (int e = 0; e < VEC; ++e) sq[e & 3] = __fmaf_rn(x[e], x[e], sq[e & 3]);
         if (BWD) {
           float gy[VEC], gm[VEC];
           unpack<T>(yraw[k], gy);
           unpack<T>(graw[k], gm);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) c1 = __fmaf_rn(__fmul_rn(gm[e], gy[e]), x[e], c1);
+          for (int e = 0; e < VEC; ++e) cq[e & 3] = __fmaf_rn(__fmul_rn(gm[e], gy[e]), x[e], cq[e & 3]);
         }
       }
     }
-    group_reduce2<SumOp>(g, ss, c1);
+    float ss = __fadd_rn(__fadd_rn(sq[0], sq[1]), __fadd_rn(sq[2], sq[3]));
+    float c1 = __fadd_rn(__fadd_rn(cq[0], cq[1]), __fadd_rn(cq[2], cq[3]));
+    group_reduce2<SumOp>(g, ss, c1);        // its barrier also orders every lane's reads of the stage slot
+    if (G == 32) __syncwarp();
+    if (row + (int64_t)nstages * stride < rows) issue(row + (int64_t)nstages * stride, cur_slot);
     const float s = __fsqrt_rn(__fmaf_rn(ss, inv_cols, eps));
     const float rs = __frcp_rn(s);
     // c1 / (cols * s^3); explicitly rounded ops so that fwd, bwd and fwd_bwd give the same bits
@@ -252,8 +261,14 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
       const size_t stage = (size_t)cols * sizeof(T) * (BWD ? 2 : 1);
-      const size_t smem = pl.groups * stage + pl.groups * sizeof(uint64_t) +
-                          ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+      auto smem_for = [&](int ns) {
+        return pl.groups * ns * (stage + sizeof(uint64_t)) +
+               ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+      };
+      // ring depth: fill about g_rmsnorm_smem_kb of shared memory per CTA, at most 8 rows per group
+      int nstages = 8;
+      while (nstages > 1 && smem_for(nstages) > (size_t)g_rmsnorm_smem_kb * 1024) --nstages;
+      const size_t smem = smem_for(nstages);
       int64_t grid = 0;
 #define CB_LAUNCH(NV_)                                                                                      \
   do {                                                                                                      \
@@ -261,7 +276,7 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
     grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                                           \
     if (grid > kRmsMaxPartials) grid = kRmsMaxPartials;                                                     \
     if (grid > want) grid = want;                                                                           \
-    kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, beta_dx); \
+    kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, nstages, beta_dx); \
   } while (0)
       if (smem <= kMaxDynSmem) {
         switch (pl.NV) {

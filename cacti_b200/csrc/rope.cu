@@ -92,39 +92,53 @@ rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, 
   constexpr int UPV = Unit<T>::UPV;
   constexpr int NU = 4;                       // units per vector
   const int half = hd >> 1;
-  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t tok = v / vpr;
-    const int r = (int)(v - tok * vpr) * VEC;           // element offset inside the token row
-    const int64_t e0 = v * VEC;                          // flat element index
-    const int64_t pos = (tok + pos_off) % pos_mod;
-    const T* ct = cosT + pos * hd;
-    const T* stb = sinT + pos * hd;
-    uint4 xo, go;
-    if (FWD) xo = ld_stream(X + e0);
-    if (BWD) go = ld_stream(dY + e0);
-    int j = r % hd;
-    uint32_t yo[NU], dout[NU];
-    const uint32_t xw[NU] = {xo.x, xo.y, xo.z, xo.w};
-    const uint32_t gw[NU] = {go.x, go.y, go.z, go.w};
+  // UNR vectors per thread per trip (more than one lowered occupancy and measured slower on B200)
+  constexpr int UNR = 1;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += UNR * stride) {
+    uint4 xo[UNR], go[UNR];
 #pragma unroll
-    for (int p = 0; p < NU; ++p) {
-      if (j >= hd) j -= hd;
-      const bool first = j < half;
-      const int jp = first ? j + half : j - half;        // partner index inside the head
-      const int64_t ep = e0 + p * UPV + (first ? half : -half);
-      const uint32_t c = ldu(ct + j);
-      if (FWD) yo[p] = rope_unit<T>(xw[p], ldu(X + ep), c, ldu(stb + j), first, false);
-      if (BWD) dout[p] = rope_unit<T>(gw[p], ldu(dY + ep), c, ldu(stb + jp), first, true);
-      j += UPV;
-    }
-    if (FWD) st_stream(Y + e0, make_uint4(yo[0], yo[1], yo[2], yo[3]));
-    if (BWD) {
-      if (beta) {
-        const uint4 o = ld_stream(dX + e0);
-        dout[0] = add_unit<T>(o.x, dout[0]); dout[1] = add_unit<T>(o.y, dout[1]);
-        dout[2] = add_unit<T>(o.z, dout[2]); dout[3] = add_unit<T>(o.w, dout[3]);
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v < nvec) {
+        if (FWD) xo[u] = ld_stream(X + v * VEC);
+        if (BWD) go[u] = ld_stream(dY + v * VEC);
       }
-      st_stream(dX + e0, make_uint4(dout[0], dout[1], dout[2], dout[3]));
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v >= nvec) break;
+      const int64_t tok = v / vpr;
+      const int r = (int)(v - tok * vpr) * VEC;           // element offset inside the token row
+      const int64_t e0 = v * VEC;                          // flat element index
+      const int64_t pos = (tok + pos_off) % pos_mod;
+      const T* ct = cosT + pos * hd;
+      const T* stb = sinT + pos * hd;
+      int j = r % hd;
+      uint32_t yo[NU], dout[NU];
+      const uint32_t xw[NU] = {xo[u].x, xo[u].y, xo[u].z, xo[u].w};
+      const uint32_t gw[NU] = {go[u].x, go[u].y, go[u].z, go[u].w};
+#pragma unroll
+      for (int p = 0; p < NU; ++p) {
+        if (j >= hd) j -= hd;
+        const bool first = j < half;
+        const int jp = first ? j + half : j - half;        // partner index inside the head
+        const int64_t ep = e0 + p * UPV + (first ? half : -half);
+        const uint32_t c = ldu(ct + j);
+        if (FWD) yo[p] = rope_unit<T>(xw[p], ldu(X + ep), c, ldu(stb + j), first, false);
+        if (BWD) dout[p] = rope_unit<T>(gw[p], ldu(dY + ep), c, ldu(stb + jp), first, true);
+        j += UPV;
+      }
+      if (FWD) st_stream(Y + e0, make_uint4(yo[0], yo[1], yo[2], yo[3]));
+      if (BWD) {
+        if (beta) {
+          const uint4 o = ld_stream(dX + e0);
+          dout[0] = add_unit<T>(o.x, dout[0]); dout[1] = add_unit<T>(o.y, dout[1]);
+          dout[2] = add_unit<T>(o.z, dout[2]); dout[3] = add_unit<T>(o.w, dout[3]);
+        }
+        st_stream(dX + e0, make_uint4(dout[0], dout[1], dout[2], dout[3]));
+      }
     }
   }
 }

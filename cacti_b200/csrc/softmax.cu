@@ -98,7 +98,7 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
     active = (row + stride < rows) ? issue(row + stride) : 0;
 
     // pass 1: row maximum
-    float m = -INFINITY;
+    float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
@@ -106,12 +106,12 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
         float a[VEC];
         unpack<T>(sraw[k], a);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) m = fmaxf(m, a[e]);
+        for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[e]);
       }
     }
-    m = group_reduce<MaxOp>(g, m);
+    float m = group_reduce<MaxOp>(g, fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])));
     // pass 2: Z = sum exp(a - m); cg = sum exp(a - m) * g  (sum_j y_j g_j = cg / Z)
-    float z = 0.f, cg = 0.f;
+    float zq[4] = {0.f, 0.f, 0.f, 0.f}, cq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
@@ -122,11 +122,13 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float ex = exp_for<T>(a[e] - m);
-          z = __fadd_rn(z, ex);
-          if (BWD) cg = __fmaf_rn(ex, gv[e], cg);
+          zq[e & 3] = __fadd_rn(zq[e & 3], ex);
+          if (BWD) cq[e & 3] = __fmaf_rn(ex, gv[e], cq[e & 3]);
         }
       }
     }
+    float z = __fadd_rn(__fadd_rn(zq[0], zq[1]), __fadd_rn(zq[2], zq[3]));
+    float cg = __fadd_rn(__fadd_rn(cq[0], cq[1]), __fadd_rn(cq[2], cq[3]));
     group_reduce2<SumOp>(g, z, cg);
     // An all-masked row has max = -inf and exp(-inf - -inf) = NaN in the reference chain.
     const bool dead = (cur_active <= 0);

@@ -11,6 +11,8 @@
 namespace cb {
 
 int g_nll_gpref = 512;
+int g_nll_stages = 3;
+int g_nll_dbg = 0;
 
 template <typename TI> __device__ __forceinline__ int64_t load_index(const void* p, int64_t i);
 template <> __device__ __forceinline__ int64_t load_index<int32_t>(const void* p, int64_t i) {
@@ -20,91 +22,140 @@ template <> __device__ __forceinline__ int64_t load_index<uint16_t>(const void* 
   return (int64_t) reinterpret_cast<const uint16_t*>(p)[i];
 }
 
+// exp(a - m) as one FFMA and one MUFU: ex2(a*log2e - m*log2e).  Used for 16-bit storage, where its
+// ~1e-6 relative error is far below the storage rounding; f32 storage uses the accurate expf.
+template <typename T> __device__ __forceinline__ float exp_shifted(float a, float m, float neg_m_log2e) {
+  if constexpr (std::is_same<T, float>::value) return expf(a - m);
+  else return exp2f_approx(__fmaf_rn(a, 1.4426950408889634f, neg_m_log2e));
+}
+
+// exp(d) for the (max, sum) combine: d <= 0 or -inf.
+template <typename T> __device__ __forceinline__ float exp_rescale(float d) {
+  if constexpr (std::is_same<T, float>::value) return expf(d);
+  else return exp2f_approx(d * 1.4426950408889634f);
+}
+
 template <typename T, typename TI, int NV, bool BWD>
 __global__ void __launch_bounds__(512)
 softmax_nll_rows_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const T* __restrict__ L,
                         const void* __restrict__ targets, const float* __restrict__ w_rows, float w_scalar,
-                        int64_t rows, int cols, int G, int beta, unsigned* __restrict__ status) {
+                        int64_t rows, int cols, int G, int nstages, int beta, unsigned* __restrict__ status, int dbg) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
   const unsigned row_bytes = (unsigned)cols * sizeof(T);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * row_bytes);
-  float* red = reinterpret_cast<float*>(bars + groups);
+  // shared: [groups][nstages] row buffers | [groups][nstages] mbarriers | reduction slots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * row_bytes);
+  float* red = reinterpret_cast<float*>(bars + groups * nstages);
   GroupCtx g = make_group(G, red);
-  unsigned char* stage = smem_raw + (size_t)g.gid * row_bytes;
-  uint64_t* bar = bars + g.gid;
-  if (g.lane == 0) mbar_init(bar, 1);
+  unsigned char* stage0 = smem_raw + (size_t)g.gid * nstages * row_bytes;
+  uint64_t* bar0 = bars + g.gid * nstages;
+  if (g.lane < nstages) mbar_init(bar0 + g.lane, 1);
   mbar_fence_init();
   __syncthreads();
   const int64_t stride = (int64_t)gridDim.x * groups;
-  int64_t row = (int64_t)blockIdx.x * groups + g.gid;
-  unsigned phase = 0;
-  auto issue = [&](int64_t r) {
-    if (g.lane == 0) { mbar_expect_tx(bar, row_bytes); bulk_g2s(stage, L + r * cols, row_bytes, bar); }
+  const int64_t row0 = (int64_t)blockIdx.x * groups + g.gid;
+  auto issue = [&](int64_t r, int slot) {
+    if (g.lane == 0) {
+      mbar_expect_tx(bar0 + slot, row_bytes);
+      bulk_g2s(stage0 + (size_t)slot * row_bytes, L + r * cols, row_bytes, bar0 + slot);
+    }
   };
-  if (row < rows) issue(row);
-  for (; row < rows; row += stride) {
-    const int64_t tgt = load_index<TI>(targets, row);
+  for (int s = 0; s < nstages; ++s)
+    if (row0 + s * stride < rows) issue(row0 + s * stride, s);
+  int slot = 0;
+  unsigned phase = 0;
+  // The target index and row weight are fetched one row ahead: under a saturated memory system a
+  // dependent global load costs about a microsecond, which would otherwise stall every row.
+  int64_t tgt_next = row0 < rows ? load_index<TI>(targets, row0) : 0;
+  float w_next = (row0 < rows && w_rows) ? w_rows[row0] : w_scalar;
+  for (int64_t row = row0; row < rows; row += stride) {
+    const int64_t tgt = tgt_next;
+    const float w = w_next;
+    if (row + stride < rows) {
+      tgt_next = load_index<TI>(targets, row + stride);
+      if (w_rows) w_next = w_rows[row + stride];
+    }
     const bool tgt_ok = tgt >= 0 && tgt < cols;
-    const float w = w_rows ? w_rows[row] : w_scalar;
-    if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) return;
-    phase ^= 1;
-    uint4 raw[NV];
+    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) return;
+    const unsigned char* stage = stage0 + (size_t)slot * row_bytes;
+    // the row as f32 in registers; it is overwritten by exp(a - m) in pass 2 and scaled in pass 3
+    float a[NV][VEC];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cols) raw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
+      if (col0 < cols) unpack<T>(*reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T)), a[k]);
     }
     // the target logit, read from the staged row (the stored bit pattern, converted exactly)
     const float a_t = tgt_ok ? Elem<T>::to_f32(reinterpret_cast<const T*>(stage)[tgt]) : 0.f;
-    group_barrier(g);
-    if (row + stride < rows) issue(row + stride);
+    const int cur_slot = slot;
+    if (++slot == nstages) { slot = 0; phase ^= 1; }
 
-    float m = -INFINITY;
+    // Warp-local online softmax: each warp reduces its own part of the row against its own maximum
+    // and the warps then combine (max, sum) pairs once.  One group barrier per row, and between two
+    // barriers the warps run independently, so one warp's exp phase overlaps another's loads.
+    // (four independent accumulators per reduction: the dependent chain is a quarter as long)
+    float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cols) {
-        float a[VEC];
-        unpack<T>(raw[k], a);
+      if ((g.lane + k * G) * VEC < cols) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) m = fmaxf(m, a[e]);
+        if (!(dbg & 1)) for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[k][e]);
       }
     }
-    m = group_reduce<MaxOp>(g, m);
-    float z = 0.f;
+    float mw = warp_reduce<MaxOp>(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])));
+    // a warp whose part of the row is empty has mw = -inf; use 0 so that no inf - inf appears
+    const float mw_f = mw == -INFINITY ? 0.f : mw;
+    const float nml = -mw_f * 1.4426950408889634f;
+    float zq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cols) {
-        float a[VEC];
-        unpack<T>(raw[k], a);
+      if ((g.lane + k * G) * VEC < cols) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) z += exp_for<T>(a[e] - m);
+        for (int e = 0; e < VEC; ++e) { if (!(dbg & 2)) a[k][e] = exp_shifted<T>(a[k][e], mw_f, nml); zq[e & 3] += a[k][e]; }
       }
     }
-    z = group_reduce<SumOp>(g, z);
+    float zw = warp_reduce<SumOp>((zq[0] + zq[1]) + (zq[2] + zq[3]));
+    float m = mw, z = zw, rescale = 1.f;
+    if (G > 32) {
+      const int groups_ = blockDim.x / G;
+      float2* sl = reinterpret_cast<float2*>(g.red) + (size_t)(g.phase * groups_ + g.gid) * kMaxWarpsPerGroup;
+      const int wi = g.lane >> 5, l = g.lane & 31;
+      if (l == 0) sl[wi] = make_float2(mw, zw);
+      group_barrier(g);                                  // also: every lane has consumed the stage slot
+      const float2 v = l < g.nwarps ? sl[l] : make_float2(-INFINITY, 0.f);
+      m = warp_reduce<MaxOp>(v.x);
+      const float term = v.y * exp_rescale<T>(v.x == -INFINITY ? -INFINITY : v.x - m);
+      z = warp_reduce<SumOp>(term);
+      rescale = exp_rescale<T>(mw == -INFINITY ? -INFINITY : mw - m);
+      g.phase ^= 1;
+    } else {
+      __syncwarp();
+    }
+    if (row + (int64_t)nstages * stride < rows) issue(row + (int64_t)nstages * stride, cur_slot);
     if (g.lane == 0) {
       if (!tgt_ok && status) atomicMax(status, (unsigned)CACTI_B200_ERR_INDEX_RANGE);
       // -log(y_k) with y_k = exp(a_k - m) / z, formed as in the reference (src/thunk/op.rs:3543)
       if (loss_rows) loss_rows[row] = tgt_ok ? -logf(expf(a_t - m) / z) : __int_as_float(0x7fc00000);
     }
-    if (BWD) {
-      const float rz = 1.f / z;
+    if (BWD && !(dbg & 4)) {
+      // w*(y - onehot) = e*(w/z) - w*onehot: one multiply per element, the target column fixed up
+      const float rz = rescale / z;                      // e was formed against the warp's own maximum
+      const float sc = w * rz;
       T* drow = dL + row * cols;
       const int tcol = tgt_ok ? (int)tgt : -1;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int col0 = (g.lane + k * G) * VEC;
         if (col0 < cols) {
-          float a[VEC], d[VEC];
-          unpack<T>(raw[k], a);
+          float d[VEC];
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            const float ex = exp_for<T>(a[e] - m);
-            const float y = std::is_same<T, float>::value ? ex / z : ex * rz;
-            d[e] = w * (y - ((col0 + e) == tcol ? 1.f : 0.f));
+            d[e] = a[k][e] * sc;
+          }
+          if (tcol >= col0 && tcol < col0 + VEC) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) if (col0 + e == tcol) d[e] = w * (a[k][e] * rz - 1.f);
           }
           if (beta) st_stream(drow + col0, pack_accumulate<T>(d, ld_stream(drow + col0)));
           else st_stream(drow + col0, pack<T>(d));
@@ -178,15 +229,21 @@ static int launch_nll(float* loss_rows, uint64_t dl, uint64_t l, const void* tar
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      const size_t smem = pl.groups * ((size_t)cols * sizeof(T) + sizeof(uint64_t)) +
-                          (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
+      // as many row buffers per group as fit (up to g_nll_stages), so a full row is always in flight
+      int nstages = g_nll_stages;
+      auto smem_for = [&](int ns) {
+        return pl.groups * ns * ((size_t)cols * sizeof(T) + sizeof(uint64_t)) +
+               (size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 * sizeof(float);
+      };
+      while (nstages > 1 && smem_for(nstages) > kMaxDynSmem) --nstages;
+      const size_t smem = smem_for(nstages);
 #define CB_LAUNCH(NV_)                                                                          \
   do {                                                                                          \
     auto kern = softmax_nll_rows_kernel<T, TI, NV_, BWD>;                                       \
     int64_t grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                       \
     if (grid > want) grid = want;                                                               \
     kern<<<(unsigned)grid, threads, smem, st>>>(loss_rows, dL, L, targets, w_rows, w_scalar,    \
-                                                rows, (int)cols, pl.G, beta, status);           \
+                                                rows, (int)cols, pl.G, nstages, beta, status, g_nll_dbg);  \
   } while (0)
       if (smem <= kMaxDynSmem) {
         switch (pl.NV) {
