@@ -1,0 +1,459 @@
+// G1 / G2: dense and block (strided-batched) matmul on the 5th-generation tensor cores.
+//
+// Replaces MatrixMulF16F32GpuThunkImpl (cublasGemmEx, src/thunk/op.rs:4413-4716) and
+// BlockMatrixMulF16F32GpuThunkImpl (cublasGemmBatchedEx over host-built pointer arrays,
+// src/thunk/op.rs:5025-5471): C = f16(alpha * op(A) op(B) + beta * C), 16-bit operands, fp32
+// accumulation, no split-K and no atomics (cacti_gpu_cu_ffi/src/lib.rs:749,766-767), row-major with
+// leading dimensions, all four transpose combinations (src/thunk/op.rs:4336-4365, :4883-4911).
+// The block form addresses block (i, j) by two affine strides per operand, which is what the
+// reference computes on the host for its pointer arrays (src/thunk/op.rs:5174-5189); a stride of 0
+// broadcasts the block.
+//
+// Kernel: one persistent CTA per SM, 192 threads.
+//   warp 0      : TMA producer.  Operand tiles are fetched with cp.async.bulk.tensor (4-D tensor maps:
+//                 inner, outer, block j, block i) into a ring of 128-byte-swizzled shared-memory stages;
+//                 out-of-range rows/columns/K are zero-filled by the TMA unit.
+//   warp 1      : allocates TMEM and issues tcgen05.mma (UMMA 128 x BN x 16, kind::f16) from one thread;
+//                 tcgen05.commit releases shared-memory stages and publishes finished accumulators.
+//   warps 2..5  : epilogue.  tcgen05.ld brings the fp32 accumulator out of TMEM, alpha/beta are applied,
+//                 the result is rounded once to the 16-bit type and stored.
+// Two accumulators (2 x BN of the 512 TMEM columns) let the epilogue of one tile overlap the main
+// loop of the next.  Operands may be K-major or MN-major in memory; the transpose flags only change
+// the tensor-map box and the "major" bits of the descriptors, never the data.  No load uses cluster
+// multicast.  Every wait is bounded; on a timeout the CTA records kDevErrGemmTimeout, drains, frees
+// its TMEM and returns.
+//
+// Operands that TMA cannot address (base or a stride not a multiple of 16 bytes, e.g. head_dim 100
+// slices at 200-byte offsets) are first repacked into the caller's workspace with the inner
+// dimension padded to a multiple of 8 elements; the reference pads the same operands to 16 bytes
+// with a separate thunk before calling cuBLAS (src/op.rs:1454-1482).  Outputs need no alignment.
+#include "common.cuh"
+#include <cuda.h>
+#include <type_traits>
+
+namespace cb {
+
+constexpr int kBM = 128, kBK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  int nb_inner, nb_outer;                 // block grid: j (inner) and i (outer)
+  int tiles_m, tiles_n;
+  int a_j, a_i, b_j, b_i;                 // 1: operand has that block dimension, 0: broadcast
+  long long ldc, c_stride_inner, c_stride_outer;
+  float alpha, beta;
+  uint32_t idesc;
+  int c_align;                            // bytes every output row chunk is aligned to: 16, 8, 4 or 2
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 UMMA): start address, leading / stride byte offsets in
+// 16-byte units, version 1, 128-byte swizzle.
+//   K-major tile  [rows][64 k]: rows are 128 B apart, 8-row groups 1024 B apart (SBO); a 16-wide k step
+//                               advances the start address by 32 B inside the swizzle atom.
+//   MN-major tile [64 k][64 mn] per 8 KB box: k rows are 128 B apart, 8-k groups 1024 B apart (SBO),
+//                               the next 64 mn-columns 8192 B further (LBO); a k step advances 2048 B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo16, uint32_t sbo16) {
+  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | ((lbo16 & 0x3FFFu) << 16);
+  const uint32_t hi = (sbo16 & 0x3FFFu) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
+               const GemmParams p) {
+  constexpr int STAGES = BN == 256 ? 4 : 6;
+  constexpr uint32_t A_BYTES = kBM * kBK * 2, B_BYTES = BN * kBK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nkb = (p.K + kBK - 1) / kBK;
+  const long long tiles_per_block = (long long)p.tiles_m * p.tiles_n;
+  const long long total = tiles_per_block * p.nb_inner * p.nb_outer;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    int s = 0; unsigned ph = 0;
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const int blk = (int)(tile / tiles_per_block);
+      const int r = (int)(tile - (long long)blk * tiles_per_block);
+      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+      const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
+      const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+        unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
+        unsigned char* sb = sa + A_BYTES;
+        mbar_expect_tx(full + s, STAGE_BYTES);
+        if (!A_MN) tma_load_4d(sa, &tmA, full + s, kb * kBK, tm * kBM, aj, ai);
+        else {
+#pragma unroll
+          for (int h = 0; h < kBM / 64; ++h) tma_load_4d(sa + h * 8192, &tmA, full + s, tm * kBM + h * 64, kb * kBK, aj, ai);
+        }
+        if (!B_MN) tma_load_4d(sb, &tmB, full + s, kb * kBK, tn * BN, bjj, bii);
+        else {
+#pragma unroll
+          for (int h = 0; h < BN / 64; ++h) tma_load_4d(sb + h * 8192, &tmB, full + s, tn * BN + h * 64, kb * kBK, bjj, bii);
+        }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    int s = 0; unsigned ph = 0;
+    long long local = 0;
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
+      const int acc = (int)(local & 1);
+      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4) {
+          const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
+          const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
+          tc_mma_f16(tacc, da, db, p.idesc, (kb | k4) ? 1u : 0u);
+        }
+        tc_commit(empty + s);                 // stage free once these MMAs have read it
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+      tc_commit(tfull + acc);                 // accumulator complete
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;                   // TMEM lane quarter this warp may read
+    long long local = 0;
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
+      const int blk = (int)(tile / tiles_per_block);
+      const int r = (int)(tile - (long long)blk * tiles_per_block);
+      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+      const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
+      const int acc = (int)(local & 1);
+      if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
+      tc_fence_after();
+      const int row = tm * kBM + q * 32 + lane;
+      T* crow = C + (long long)bi * p.c_stride_outer + (long long)bj * p.c_stride_inner + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) break;               // warp-uniform
+        uint32_t v[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+        if (row < p.M) {
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = p.alpha * __uint_as_float(v[i]);
+          const int nvalid = p.N - col0 < 32 ? p.N - col0 : 32;
+          T* out = crow + col0;
+          if (p.beta != 0.f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < nvalid) f[i] = fmaf(p.beta, Elem<T>::to_f32(out[i]), f[i]);
+          }
+          if (nvalid == 32 && p.c_align >= 16) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float t8[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) t8[i] = f[g * 8 + i];
+              *reinterpret_cast<uint4*>(out + g * 8) = pack<T>(t8);
+            }
+          } else if (p.c_align >= 8) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (g * 4 + 4 <= nvalid) {
+                uint2 w;
+                if constexpr (std::is_same<T, __half>::value) {
+                  __half2 a = __floats2half2_rn(f[g * 4], f[g * 4 + 1]), b = __floats2half2_rn(f[g * 4 + 2], f[g * 4 + 3]);
+                  w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+                } else {
+                  __nv_bfloat162 a = __floats2bfloat162_rn(f[g * 4], f[g * 4 + 1]), b = __floats2bfloat162_rn(f[g * 4 + 2], f[g * 4 + 3]);
+                  w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+                }
+                *reinterpret_cast<uint2*>(out + g * 4) = w;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (g * 4 + i < nvalid) out[g * 4 + i] = Elem<T>::from_f32(f[g * 4 + i]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < nvalid) out[i] = Elem<T>::from_f32(f[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty + acc);
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// Repack blocks [nbo][nbi] of a stored matrix [rows x cols] (leading dimension ld, block strides so/si)
+// into a dense [nbo*nbi][rows][cols_pad] buffer, zero-filling the padding columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pack_blocks_kernel(T* __restrict__ dst, const T* __restrict__ src, long long rows, long long cols, long long cols_pad,
+                   long long ld, int nbi, long long so, long long si, long long total) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long c = i % cols_pad;
+    const long long t = i / cols_pad;
+    const long long r = t % rows;
+    const long long blk = t / rows;
+    const long long bo = blk / nbi, bi = blk - bo * nbi;
+    T v = Elem<T>::from_f32(0.f);
+    if (c < cols) v = src[bo * so + bi * si + r * ld + c];
+    dst[i] = v;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// One operand as stored: `rows` x `cols` elements, cols contiguous, leading dimension ld, block strides.
+struct Operand {
+  uint64_t ptr; long long rows, cols, ld, stride_inner, stride_outer; int has_j, has_i;
+};
+
+static bool tma_ok(const Operand& o, int nbi, int nbo) {
+  if (o.ptr & 15) return false;
+  if ((o.ld * 2) & 15) return false;
+  if (o.has_j && nbi > 1 && ((o.stride_inner * 2) & 15)) return false;
+  if (o.has_i && nbo > 1 && ((o.stride_outer * 2) & 15)) return false;
+  return true;
+}
+
+static int encode_operand(CUtensorMap* map, const Operand& o, int nbi, int nbo, int box_inner, int box_outer, bool bf16) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return CACTI_B200_ERR_LAUNCH;
+  const cuuint64_t dj = (o.has_j && nbi > 1) ? (cuuint64_t)nbi : 1, di = (o.has_i && nbo > 1) ? (cuuint64_t)nbo : 1;
+  cuuint64_t dims[4] = {(cuuint64_t)o.cols, (cuuint64_t)o.rows, dj, di};
+  const cuuint64_t row_bytes = (cuuint64_t)o.ld * 2;
+  const cuuint64_t dflt = row_bytes * (cuuint64_t)o.rows;      // any legal value for an extent-1 dimension
+  cuuint64_t strides[3] = {row_bytes, dj > 1 ? (cuuint64_t)o.stride_inner * 2 : dflt,
+                           di > 1 ? (cuuint64_t)o.stride_outer * 2 : dflt};
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  reinterpret_cast<void*>(o.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return CACTI_B200_ERR_LAUNCH; }
+  return CACTI_B200_OK;
+}
+
+static size_t packed_bytes(long long rows, long long cols, long long nblk) {
+  const long long cp = (cols + 7) / 8 * 8;
+  return ((size_t)nblk * rows * cp * 2 + 255) / 256 * 256;
+}
+
+int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measurement knob)
+
+template <typename T>
+static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
+                    long long ldc, long long cso, long long csi, int nbi, int nbo, float alpha, float beta,
+                    uint64_t ws, size_t ws_bytes, cudaStream_t st) {
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  size_t ws_off = 0;
+  // repack what TMA cannot address
+  for (Operand* o : {&A, &B}) {
+    if (tma_ok(*o, nbi, nbo)) continue;
+    const long long nblk = (long long)((o->has_j ? nbi : 1)) * (o->has_i ? nbo : 1);
+    const size_t need = packed_bytes(o->rows, o->cols, nblk);
+    if (!ws || (ws & 255) || ws_off + need > ws_bytes) return CACTI_B200_ERR_WORKSPACE;
+    const long long cp = (o->cols + 7) / 8 * 8;
+    const long long total = nblk * o->rows * cp;
+    long long grid = (total + 255) / 256;
+    if (grid > (long long)kNumSMs * 16) grid = (long long)kNumSMs * 16;
+    const int eff_nbi = o->has_j ? nbi : 1;
+    pack_blocks_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<T*>(ws + ws_off),
+                                                         reinterpret_cast<const T*>(o->ptr), o->rows, o->cols, cp, o->ld,
+                                                         eff_nbi, o->has_i ? o->stride_outer : 0,
+                                                         o->has_j ? o->stride_inner : 0, total);
+    int rc = check_launch();
+    if (rc) return rc;
+    o->ptr = ws + ws_off; o->ld = cp;
+    o->stride_inner = o->rows * cp;
+    o->stride_outer = o->rows * cp * eff_nbi;
+    ws_off += need;
+  }
+  const int BN = g_gemm_bn ? g_gemm_bn : (N > 128 ? 256 : 128);
+  CUtensorMap tmA, tmB;
+  // K-major operand: stored [mn][k] -> box {64 k, tile mn}; MN-major: stored [k][mn] -> box {64 mn, 64 k}
+  int rc = encode_operand(&tmA, A, nbi, nbo, 64, a_mn ? 64 : kBM, bf16);
+  if (rc) return rc;
+  rc = encode_operand(&tmB, B, nbi, nbo, 64, b_mn ? 64 : BN, bf16);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.nb_inner = nbi; p.nb_outer = nbo;
+  p.tiles_m = (int)((M + kBM - 1) / kBM); p.tiles_n = (int)((N + BN - 1) / BN);
+  p.a_j = A.has_j && nbi > 1; p.a_i = A.has_i && nbo > 1; p.b_j = B.has_j && nbi > 1; p.b_i = B.has_i && nbo > 1;
+  p.ldc = ldc; p.c_stride_inner = csi; p.c_stride_outer = cso;
+  p.alpha = alpha; p.beta = beta;
+  p.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
+            ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  const uint64_t all = c | (uint64_t)(ldc * 2) | (uint64_t)(nbi > 1 ? csi * 2 : 0) | (uint64_t)(nbo > 1 ? cso * 2 : 0);
+  p.c_align = (all & 15) == 0 ? 16 : (all & 7) == 0 ? 8 : (all & 3) == 0 ? 4 : 2;
+  const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
+  const int grid = (int)(total < kNumSMs ? total : kNumSMs);
+  const int stages = BN == 256 ? 4 : 6;
+  const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 + 256;
+  T* C = reinterpret_cast<T*>(c);
+#define CB_GEMM(BN_, AM_, BM_)                                                                         \
+  do {                                                                                                 \
+    auto kern = gemm_tc_kernel<T, BN_, AM_, BM_>;                                                      \
+    static bool attr_set = false;                                                                      \
+    if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_set = true; } \
+    kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, C, p);                                            \
+  } while (0)
+  if (BN == 256) {
+    if (!a_mn && !b_mn) CB_GEMM(256, false, false); else if (!a_mn && b_mn) CB_GEMM(256, false, true);
+    else if (a_mn && !b_mn) CB_GEMM(256, true, false); else CB_GEMM(256, true, true);
+  } else {
+    if (!a_mn && !b_mn) CB_GEMM(128, false, false); else if (!a_mn && b_mn) CB_GEMM(128, false, true);
+    else if (a_mn && !b_mn) CB_GEMM(128, true, false); else CB_GEMM(128, true, true);
+  }
+#undef CB_GEMM
+  return check_launch();
+}
+
+static int gemm_entry(uint64_t c, uint64_t a, uint64_t b, long long m, long long n, long long k, long long lda,
+                      long long ldb, long long ldc, int ta, int tb, const float* alpha, const float* beta, int nbo, int nbi,
+                      long long sao, long long sai, long long sbo, long long sbi, long long sco, long long sci, int dtype,
+                      uint64_t ws, size_t ws_bytes, void* stream) {
+  if (m < 0 || n < 0 || k < 0 || nbo < 0 || nbi < 0 || !alpha || !beta) return CACTI_B200_ERR_INVALID_VALUE;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
+  if ((ta & ~1) || (tb & ~1)) return CACTI_B200_ERR_INVALID_VALUE;
+  if (dtype != CACTI_B200_R_16F && dtype != CACTI_B200_R_16BF) return CACTI_B200_ERR_DTYPE;
+  if (m == 0 || n == 0 || nbo == 0 || nbi == 0) return CACTI_B200_OK;
+  if (!c || (k > 0 && (!a || !b))) return CACTI_B200_ERR_INVALID_VALUE;
+  // stored shapes: A is [m,k] (ta = 0) or [k,m]; B is [k,n] (tb = 0) or [n,k]
+  const long long a_rows = ta ? k : m, a_cols = ta ? m : k, b_rows = tb ? n : k, b_cols = tb ? k : n;
+  if (lda < a_cols || ldb < b_cols || ldc < n) return CACTI_B200_ERR_INVALID_VALUE;
+  if (k == 0) return CACTI_B200_ERR_SHAPE;      // the reference never stages an empty contraction
+  Operand A{a, a_rows, a_cols, lda, sai, sao, sai != 0, sao != 0};
+  Operand B{b, b_rows, b_cols, ldb, sbi, sbo, sbi != 0, sbo != 0};
+  if (nbi == 1) { A.has_j = B.has_j = 0; }
+  if (nbo == 1) { A.has_i = B.has_i = 0; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // A as [m][k] is K-major; as [k][m] it is MN-major.  B as [n][k] (tb = 1) is K-major; as [k][n] MN-major.
+  const bool a_mn = ta != 0, b_mn = tb == 0;
+  if (dtype == CACTI_B200_R_16F)
+    return gemm_run<__half>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, ws, ws_bytes, st);
+  return gemm_run<__nv_bfloat16>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, ws, ws_bytes, st);
+}
+
+}  // namespace cb
+
+extern "C" {
+
+size_t cacti_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch_outer, int64_t batch_inner) {
+  if (m < 0 || n < 0 || k < 0 || batch_outer < 0 || batch_inner < 0) return 0;
+  const long long nb = (batch_outer ? batch_outer : 1) * (batch_inner ? batch_inner : 1);
+  // worst case: both operands repacked, either orientation
+  auto worst = [&](long long r, long long c) {
+    const size_t x = cb::packed_bytes(r, c, nb), y = cb::packed_bytes(c, r, nb);
+    return x > y ? x : y;
+  };
+  return worst(m, k) + worst(k, n) + 512;
+}
+
+int cacti_b200_gemm(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n, int64_t k, int64_t lda,
+                    int64_t ldb, int64_t ldc, int trans_a, int trans_b, const float* alpha, const float* beta, int dtype,
+                    cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream) {
+  return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, 1, 1, 0, 0, 0, 0, 0, 0, dtype,
+                        workspace, workspace_bytes, stream);
+}
+
+int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n,
+                                    int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                                    const float* alpha, const float* beta, int64_t batch_outer, int64_t batch_inner,
+                                    int64_t stride_a_outer, int64_t stride_a_inner, int64_t stride_b_outer,
+                                    int64_t stride_b_inner, int64_t stride_c_outer, int64_t stride_c_inner, int dtype,
+                                    cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream) {
+  if (batch_outer > 0x7fffffffLL || batch_inner > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
+  return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, (int)batch_outer, (int)batch_inner,
+                        stride_a_outer, stride_a_inner, stride_b_outer, stride_b_inner, stride_c_outer, stride_c_inner,
+                        dtype, workspace, workspace_bytes, stream);
+}
+}

@@ -100,7 +100,7 @@ softmax_nll_rows_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const
     for (int k = 0; k < NV; ++k) {
       if ((g.lane + k * G) * VEC < cols) {
 #pragma unroll
-        if (!(dbg & 1)) for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[k][e]);
+        for (int e = 0; e < VEC; ++e) if (!(dbg & 1)) mq[e & 3] = fmaxf(mq[e & 3], a[k][e]);
       }
     }
     float mw = warp_reduce<MaxOp>(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])));

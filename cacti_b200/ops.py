@@ -219,3 +219,50 @@ def add(a, b, out=None):
     out = torch.empty_like(a) if out is None else out
     check(lib().cacti_b200_add(_ptr(out), _ptr(a), _ptr(b), a.numel(), _dt(a), _stream()), "add")
     return out
+
+
+# ---- G1 / G2 ------------------------------------------------------------------------------------
+import ctypes as _C
+
+
+def _scalars(alpha, beta):
+    return _C.byref(_C.c_float(alpha)), _C.byref(_C.c_float(beta))
+
+
+def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
+    """C = alpha * op(A) op(B) + beta * C on 2-d row-major tensors (any row stride, unit column stride)."""
+    m = a.shape[1] if trans_a else a.shape[0]
+    k = a.shape[0] if trans_a else a.shape[1]
+    n = b.shape[0] if trans_b else b.shape[1]
+    c = torch.empty(m, n, dtype=a.dtype, device=a.device) if c is None else c
+    ws = _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, 1, 1), a.device)
+    al, be = _scalars(alpha, beta)
+    check(lib().cacti_b200_gemm(_ptr(c), _ptr(a), _ptr(b), m, n, k, a.stride(0), b.stride(0), c.stride(0), int(trans_a),
+                                int(trans_b), al, be, _dt(a), _ptr(ws), ws.numel(), _stream()), "gemm")
+    return c
+
+
+def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None):
+    """Block matmul on the reference's 4-d layout [nrow, blk_rows, ncol, blk_cols] (packed); an operand with
+    nrow or ncol equal to 1 is broadcast over that block dimension."""
+    nrow, ncol = max(a.shape[0], b.shape[0]), max(a.shape[2], b.shape[2])
+    m = a.shape[3] if trans_a else a.shape[1]
+    k = a.shape[1] if trans_a else a.shape[3]
+    n = b.shape[1] if trans_b else b.shape[3]
+    c = torch.empty(nrow, m, ncol, n, dtype=a.dtype, device=a.device) if c is None else c
+
+    def strides(t):
+        so = t.shape[1] * t.shape[2] * t.shape[3] if t.shape[0] > 1 else 0
+        si = t.shape[3] if t.shape[2] > 1 else 0
+        return t.shape[2] * t.shape[3], so, si
+
+    lda, sao, sai = strides(a)
+    ldb, sbo, sbi = strides(b)
+    ldc, sco, sci = strides(c)
+    if workspace is None:
+        workspace = _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, nrow, ncol), a.device)
+    al, be = _scalars(alpha, beta)
+    check(lib().cacti_b200_gemm_strided_batched(_ptr(c), _ptr(a), _ptr(b), m, n, k, lda, ldb, ldc, int(trans_a),
+                                                int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci, _dt(a),
+                                                _ptr(workspace), workspace.numel(), _stream()), "block_gemm")
+    return c

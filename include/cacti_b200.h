@@ -199,6 +199,35 @@ int cacti_b200_accumulate(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t n, i
 int cacti_b200_add(cacti_b200_dptr out, cacti_b200_dptr a, cacti_b200_dptr b, int64_t n, int dtype,
                    cacti_b200_stream stream);
 
+/* ---- G1 / G2 matmul and block matmul ------------------------------------------------------------
+ * gemm replaces MatrixMulF16F32GpuThunkImpl -> cublas_gemm (src/thunk/op.rs:4413-4716,
+ * cacti_gpu_cu_ffi/src/lib.rs:727-791); gemm_strided_batched replaces BlockMatrixMulF16F32GpuThunkImpl ->
+ * cublas_gemm_batched (src/thunk/op.rs:5025-5471, lib.rs:793-885).
+ *   C[m,n] = T(alpha * op(A) op(B) + beta * C), 16-bit operands (R_16F or R_16BF), fp32 accumulation.
+ * Row-major storage: A is [m,k] with lda (trans_a = 0) or [k,m] (trans_a = 1); B is [k,n] with ldb
+ * (trans_b = 0) or [n,k] (trans_b = 1); C is [m,n] with ldc.  alpha and beta are host pointers
+ * (lib.rs:748).  The reference's `x.matmul(false, W, true)` (src/librarium/llama.rs:478) is trans_b = 1.
+ * Block form: block (i, j), i < batch_outer, j < batch_inner, starts at base + i*stride_outer +
+ * j*stride_inner (elements); a stride of 0 broadcasts that operand (src/thunk/op.rs:5181-5182).  For
+ * the reference's 4-d layout [nrow, blk_rows, ncol, blk_cols] (src/thunk/op.rs:4936-5022): ld =
+ * ncol*blk_cols, stride_outer = blk_rows*ncol*blk_cols, stride_inner = blk_cols.
+ * Operands whose base or strides are not multiples of 16 bytes are repacked into `workspace`
+ * (cacti_b200_gemm_workspace_bytes; 256-byte aligned); aligned operands need none.  C may have any
+ * element-aligned address and strides. */
+size_t cacti_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch_outer, int64_t batch_inner);
+int cacti_b200_gemm(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n, int64_t k,
+                    int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                    const float* alpha, const float* beta, int dtype,
+                    cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
+int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b,
+                                    int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                                    int trans_a, int trans_b, const float* alpha, const float* beta,
+                                    int64_t batch_outer, int64_t batch_inner,
+                                    int64_t stride_a_outer, int64_t stride_a_inner,
+                                    int64_t stride_b_outer, int64_t stride_b_inner,
+                                    int64_t stride_c_outer, int64_t stride_c_inner, int dtype,
+                                    cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,113 @@
+"""GPU parity tests of the tcgen05 GEMM (dense and block form) against the fp64 oracle.
+
+Tolerance: 2e-3 relative (fp16) measured against max(|ref|, rms): the fp32 accumulation error of a
+dot product scales with sum |a||b|, not with the (possibly cancelled) result.
+"""
+import numpy as np
+import pytest
+import torch
+
+from cacti_b200 import capi, ops
+from oracle import ref_chain as R
+from tests.gpu_util import dev, host
+from tests.tolerances import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _stored(seed, rows, cols, trans, scale=1.0):
+    """Matrix op(X) = rows x cols, stored transposed when trans."""
+    return R.normal(seed, (cols, rows) if trans else (rows, cols), np.float16, scale)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (256, 512, 320), (100, 72, 40), (1, 8, 8),
+                                   (300, 260, 200), (129, 257, 65), (640, 3200, 3200)])
+def test_gemm_dense(cuda, ta, tb, m, n, k):
+    a = _stored(1, m, k, ta)
+    b = _stored(2, k, n, tb, 0.1)
+    c = ops.gemm(dev(a), dev(b), ta, tb, alpha=0.5)
+    ref = R.ref_gemm(a, b, ta, tb, alpha=0.5)
+    assert_close(host(c), ref, "float16", f"gemm {m}x{n}x{k} ta={ta} tb={tb}", floor_frac=1.0)
+    # Accumulate mode (beta = 1), as the reference's Accumulate thunk does (src/thunk/op.rs:5053-5067)
+    old = R.normal(3, (m, n), np.float16)
+    cacc = dev(old)
+    ops.gemm(dev(a), dev(b), ta, tb, alpha=0.5, beta=1.0, c=cacc)
+    assert_close(host(cacc), R.ref_gemm(a, b, ta, tb, alpha=0.5, beta=1.0, c=old), "float16", "gemm beta=1", floor_frac=1.0)
+
+
+def test_gemm_views_and_bf16(cuda):
+    # leading dimensions larger than the row, unaligned base: goes through the repack path
+    big_a = R.normal(4, (200, 331), np.float16)
+    big_b = R.normal(5, (150, 331), np.float16, 0.1)
+    ta_, tb_ = dev(big_a), dev(big_b)
+    a_v, b_v = ta_[:, 3:203], tb_[:, 1:201]            # 200 x 200 and 150 x 200 views, odd offsets
+    c = torch.zeros(200, 160, dtype=torch.float16, device="cuda")[:, 5:155]
+    ops.gemm(a_v, b_v, False, True, c=c)
+    ref = R.ref_gemm(big_a[:, 3:203], big_b[:, 1:201], False, True)
+    assert_close(host(c.contiguous()), ref, "float16", "gemm on views", floor_frac=1.0)
+    a = R.bf16_round(R.normal(6, (256, 192)))
+    b = R.bf16_round(R.normal(7, (320, 192), scale=0.1))
+    c = ops.gemm(dev(a, bf16=True), dev(b, bf16=True), False, True)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T
+    assert_close(host(c), ref, "bfloat16", "bf16 gemm", floor_frac=1.0)
+
+
+@pytest.mark.parametrize("hd", [100, 128, 64])
+def test_block_gemm_attention_shapes(cuda, hd):
+    """The four block matmuls of one attention layer and their adjoints, layout [B, S, H, hd] / [B, Sq, H, Sk]."""
+    bsz, s, h = 2, 256, 3
+    q = R.normal(10, (bsz, s, h, hd), np.float16)
+    k = R.normal(11, (bsz, s, h, hd), np.float16)
+    v = R.normal(12, (bsz, s, h, hd), np.float16)
+    alpha = float(1.0 / np.sqrt(hd))
+    sc = ops.block_gemm(dev(q), dev(k), False, True, alpha=alpha)                 # scores = alpha Q K^T
+    ref_sc = R.ref_block_gemm(q, k, False, True, alpha=alpha)
+    assert sc.shape == (bsz, s, h, s)
+    assert_close(host(sc), ref_sc, "float16", "QK^T", floor_frac=1.0)
+    p = R.normal(13, (bsz, s, h, s), np.float16, 0.05)
+    ctx = ops.block_gemm(dev(p), dev(v), False, False)                            # ctx = P V
+    assert_close(host(ctx), R.ref_block_gemm(p, v, False, False), "float16", "PV", floor_frac=1.0)
+    do = R.normal(14, (bsz, s, h, hd), np.float16)
+    dv = ops.block_gemm(dev(p), dev(do), True, False)                             # dV = P^T dO
+    assert_close(host(dv), R.ref_block_gemm(p, do, True, False), "float16", "P^T dO", floor_frac=1.0)
+    dp = ops.block_gemm(dev(do), dev(v), False, True)                             # dP = dO V^T
+    assert_close(host(dp), R.ref_block_gemm(do, v, False, True), "float16", "dO V^T", floor_frac=1.0)
+    ds = R.normal(15, (bsz, s, h, s), np.float16, 0.05)
+    dq = ops.block_gemm(dev(ds), dev(k), False, False, alpha=alpha)               # dQ = alpha dS K
+    assert_close(host(dq), R.ref_block_gemm(ds, k, False, False, alpha=alpha), "float16", "dS K", floor_frac=1.0)
+    dk = ops.block_gemm(dev(ds), dev(q), True, False, alpha=alpha)                # dK = alpha dS^T Q
+    assert_close(host(dk), R.ref_block_gemm(ds, q, True, False, alpha=alpha), "float16", "dS^T Q", floor_frac=1.0)
+
+
+def test_block_gemm_broadcast_and_accumulate(cuda):
+    a = R.normal(20, (3, 64, 2, 40), np.float16)
+    b1 = R.normal(21, (1, 40, 2, 24), np.float16)      # broadcast over block rows
+    b2 = R.normal(22, (3, 40, 1, 24), np.float16)      # broadcast over block columns
+    for b in (b1, b2):
+        c = ops.block_gemm(dev(a), dev(b))
+        assert_close(host(c), R.ref_block_gemm(a, b), "float16", "broadcast block gemm", floor_frac=1.0)
+    old = R.normal(23, (3, 64, 2, 24), np.float16)
+    cacc = dev(old)
+    ops.block_gemm(dev(a), dev(b1), beta=1.0, c=cacc)
+    assert_close(host(cacc), R.ref_block_gemm(a, b1, beta=1.0, c=old), "float16", "block gemm beta=1", floor_frac=1.0)
+
+
+def test_gemm_argument_errors(cuda):
+    L = capi.lib()
+    import ctypes as C
+    one, zero = C.byref(C.c_float(1.0)), C.byref(C.c_float(0.0))
+    P = 0x1000
+    assert L.cacti_b200_gemm(P, P, P, 8, 8, 8, 8, 8, 8, 0, 1, one, zero, capi.R_32F, 0, 0, None) == capi.ERR_DTYPE
+    assert L.cacti_b200_gemm(P, P, P, 8, 8, 8, 4, 8, 8, 0, 1, one, zero, capi.R_16F, 0, 0, None) == capi.ERR_INVALID_VALUE
+    assert L.cacti_b200_gemm(P, P, P, 0, 8, 8, 8, 8, 8, 0, 1, one, zero, capi.R_16F, 0, 0, None) == capi.OK
+    # misaligned operand without a workspace
+    assert L.cacti_b200_gemm(P, P + 2, P, 8, 8, 8, 8, 8, 8, 0, 1, one, zero, capi.R_16F, 0, 0, None) == capi.ERR_WORKSPACE
+    err = C.c_uint(0)
+    assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+
+
+def test_gemm_deterministic(cuda):
+    a, b = dev(R.normal(30, (512, 640), np.float16)), dev(R.normal(31, (384, 640), np.float16))
+    c1, c2 = ops.gemm(a, b, False, True), ops.gemm(a, b, False, True)
+    assert torch.equal(c1, c2)
