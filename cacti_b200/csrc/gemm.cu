@@ -45,6 +45,8 @@ struct GemmParams {
   float alpha, beta;
   uint32_t idesc;
   int c_align;                            // bytes every output row chunk is aligned to: 16, 8, 4 or 2
+  int c_tma;                              // 1: C is written with TMA stores from a swizzled staging buffer
+  int group_m;                            // tile rasterisation: m-tiles per group (L2 reuse of the B panel)
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
@@ -53,6 +55,11 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -70,6 +77,7 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_
       ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum)
       : "memory");
 }
+// issues the load; the registers are valid after tc_ld_wait()
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -79,8 +87,8 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 UMMA): start address, leading / stride byte offsets in
 // 16-byte units, version 1, 128-byte swizzle.
@@ -94,10 +102,24 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo16, ui
   return ((uint64_t)hi << 32) | lo;
 }
 
+// Tile order inside one block: groups of `group_m` m-tiles; inside a group the m index runs fastest, so
+// the CTAs that run at the same time share a few B (weight) panels and a bounded set of A rows in L2.
+__device__ __forceinline__ void decode_tile(long long tile, long long tiles_per_block, const GemmParams& p, int& blk,
+                                            int& tm, int& tn) {
+  blk = (int)(tile / tiles_per_block);
+  const int r = (int)(tile - (long long)blk * tiles_per_block);
+  const int per_group = p.group_m * p.tiles_n;
+  const int grp = r / per_group, in = r - grp * per_group;
+  const int m0 = grp * p.group_m;
+  const int gm = p.tiles_m - m0 < p.group_m ? p.tiles_m - m0 : p.group_m;
+  tn = in / gm;
+  tm = m0 + (in - tn * gm);
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
-               const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, T* __restrict__ C, const GemmParams p) {
   constexpr int STAGES = BN == 256 ? 4 : 6;
   constexpr uint32_t A_BYTES = kBM * kBK * 2, B_BYTES = BN * kBK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ unsigned char smem_raw[];
@@ -107,6 +129,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  // epilogue staging: per epilogue warp two [32 rows][64 cols] buffers in the 128-byte-swizzled layout of a
+  // TMA box (4 KB each), 1024-byte aligned
+  unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -132,9 +157,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- TMA producer ----------------
     int s = 0; unsigned ph = 0;
     for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const int blk = (int)(tile / tiles_per_block);
-      const int r = (int)(tile - (long long)blk * tiles_per_block);
-      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
       for (int kb = 0; kb < nkb; ++kb) {
@@ -184,14 +208,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;                   // TMEM lane quarter this warp may read
     long long local = 0;
     for (long long tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
-      const int blk = (int)(tile / tiles_per_block);
-      const int r = (int)(tile - (long long)blk * tiles_per_block);
-      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
       tc_fence_after();
       const int row = tm * kBM + q * 32 + lane;
+      if (p.c_tma) {
+        // TMEM -> registers -> swizzled shared staging -> TMA store (clips rows/columns past M, N)
+        // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
+        unsigned char* mybuf = cstage + (size_t)(warp - 2) * 8192;
+        const bool scale = p.alpha != 1.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 128; ++c) {
+          const int col0 = tn * BN + c * 128;
+          if (col0 >= p.N) break;               // warp-uniform
+          uint32_t v[4][32];
+#pragma unroll
+          for (int hh = 0; hh < 4; ++hh)
+            tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
+          // both staging buffers must have been read by the stores of the previous trip
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          tc_ld_wait();
+          if (c == BN / 128 - 1 || col0 + 128 >= p.N) {      // last trip of this tile: the accumulator is free
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty + acc);
+          } else {
+            __syncwarp();
+          }
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            unsigned char* buf = mybuf + hb * 4096;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                float t8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float a = __uint_as_float(v[hb * 2 + hh][g * 8 + i]);
+                  t8[i] = scale ? p.alpha * a : a;
+                }
+                const int chunk = hh * 4 + g;       // 16-byte chunk inside the 128-byte row
+                *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pack<T>(t8);
+              }
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&tmC, mybuf, col0, tm * kBM + q * 32, bj, bi);
+            if (col0 + 64 < p.N) tma_store_4d(&tmC, mybuf + 4096, col0 + 64, tm * kBM + q * 32, bj, bi);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        continue;                               // tempty was released inside the loop
+      } else {
       T* crow = C + (long long)bi * p.c_stride_outer + (long long)bj * p.c_stride_inner + (long long)row * p.ldc;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -199,6 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (col0 >= p.N) break;               // warp-uniform
         uint32_t v[32];
         tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+        tc_ld_wait();
         if (row < p.M) {
           float f[32];
 #pragma unroll
@@ -241,12 +316,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + acc);
     }
   }
 done:
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -257,20 +334,26 @@ done:
 }
 
 // Repack blocks [nbo][nbi] of a stored matrix [rows x cols] (leading dimension ld, block strides so/si)
-// into a dense [nbo*nbi][rows][cols_pad] buffer, zero-filling the padding columns.
+// into a dense [nbo*nbi][rows][cols_pad] buffer, zero-filling the padding columns.  One warp per row;
+// 4-byte units when every row start is 4-byte aligned, else elements.
 template <typename T>
 __global__ void __launch_bounds__(256)
-pack_blocks_kernel(T* __restrict__ dst, const T* __restrict__ src, long long rows, long long cols, long long cols_pad,
-                   long long ld, int nbi, long long so, long long si, long long total) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long c = i % cols_pad;
-    const long long t = i / cols_pad;
-    const long long r = t % rows;
-    const long long blk = t / rows;
-    const long long bo = blk / nbi, bi = blk - bo * nbi;
-    T v = Elem<T>::from_f32(0.f);
-    if (c < cols) v = src[bo * so + bi * si + r * ld + c];
-    dst[i] = v;
+pack_blocks_kernel(T* __restrict__ dst, const T* __restrict__ src, int rows, int cols, int cols_pad, long long ld,
+                   int nbi, long long so, long long si, long long total_rows, int pairs_ok) {
+  const int lane = threadIdx.x & 31;
+  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < total_rows; t += (long long)gridDim.x * 8) {
+    const int r = (int)(t % rows);
+    const int blk = (int)(t / rows);
+    const int bo = blk / nbi, bi = blk - bo * nbi;
+    const T* s = src + bo * so + bi * si + (long long)r * ld;
+    T* d = dst + t * cols_pad;
+    if (pairs_ok) {
+      const uint32_t* s2 = reinterpret_cast<const uint32_t*>(s);
+      uint32_t* d2 = reinterpret_cast<uint32_t*>(d);
+      for (int c = lane; c < cols_pad / 2; c += 32) d2[c] = c < cols / 2 ? __ldg(s2 + c) : 0u;
+    } else {
+      for (int c = lane; c < cols_pad; c += 32) d[c] = c < cols ? s[c] : Elem<T>::from_f32(0.f);
+    }
   }
 }
 
@@ -327,6 +410,7 @@ static size_t packed_bytes(long long rows, long long cols, long long nblk) {
 }
 
 int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measurement knob)
+int g_gemm_group_m = 0;
 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
@@ -341,14 +425,15 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     const size_t need = packed_bytes(o->rows, o->cols, nblk);
     if (!ws || (ws & 255) || ws_off + need > ws_bytes) return CACTI_B200_ERR_WORKSPACE;
     const long long cp = (o->cols + 7) / 8 * 8;
-    const long long total = nblk * o->rows * cp;
-    long long grid = (total + 255) / 256;
-    if (grid > (long long)kNumSMs * 16) grid = (long long)kNumSMs * 16;
+    const long long total_rows = nblk * o->rows;
+    long long grid = (total_rows + 7) / 8;
+    if (grid > (long long)kNumSMs * 32) grid = (long long)kNumSMs * 32;
     const int eff_nbi = o->has_j ? nbi : 1;
+    const long long so_ = o->has_i ? o->stride_outer : 0, si_ = o->has_j ? o->stride_inner : 0;
+    const int pairs_ok = !(o->cols & 1) && !(o->ptr & 3) && !(o->ld & 1) && !(so_ & 1) && !(si_ & 1);
     pack_blocks_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<T*>(ws + ws_off),
-                                                         reinterpret_cast<const T*>(o->ptr), o->rows, o->cols, cp, o->ld,
-                                                         eff_nbi, o->has_i ? o->stride_outer : 0,
-                                                         o->has_j ? o->stride_inner : 0, total);
+                                                         reinterpret_cast<const T*>(o->ptr), (int)o->rows, (int)o->cols,
+                                                         (int)cp, o->ld, eff_nbi, so_, si_, total_rows, pairs_ok);
     int rc = check_launch();
     if (rc) return rc;
     o->ptr = ws + ws_off; o->ld = cp;
@@ -374,17 +459,31 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
             ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   const uint64_t all = c | (uint64_t)(ldc * 2) | (uint64_t)(nbi > 1 ? csi * 2 : 0) | (uint64_t)(nbo > 1 ? cso * 2 : 0);
   p.c_align = (all & 15) == 0 ? 16 : (all & 7) == 0 ? 8 : (all & 3) == 0 ? 4 : 2;
+  // TMA store of C needs a 16-byte aligned base and strides, and no read-modify-write
+  CUtensorMap tmC = tmA;
+  p.c_tma = 0;
+  {
+    Operand Co{c, M, N, ldc, csi, cso, nbi > 1, nbo > 1};
+    if (beta == 0.f && tma_ok(Co, nbi, nbo) && (nbi == 1 || csi != 0) && (nbo == 1 || cso != 0)) {
+      rc = encode_operand(&tmC, Co, nbi, nbo, 64, 32, bf16);
+      if (rc) return rc;
+      p.c_tma = 1;
+    }
+  }
+  // about 16 m-tiles of A (2048 rows) stay hot in L2 while the B panels stream
+  p.group_m = g_gemm_group_m > 0 ? g_gemm_group_m : 16;
+  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
   const int stages = BN == 256 ? 4 : 6;
-  const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 + 256;
+  const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
 #define CB_GEMM(BN_, AM_, BM_)                                                                         \
   do {                                                                                                 \
     auto kern = gemm_tc_kernel<T, BN_, AM_, BM_>;                                                      \
     static bool attr_set = false;                                                                      \
     if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_set = true; } \
-    kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, C, p);                                            \
+    kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, tmC, C, p);                                            \
   } while (0)
   if (BN == 256) {
     if (!a_mn && !b_mn) CB_GEMM(256, false, false); else if (!a_mn && b_mn) CB_GEMM(256, false, true);
