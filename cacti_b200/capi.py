@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("CACTI_B200_LIB", os.path.join(HERE, "lib", "libcacti_
 HEADER = os.path.join(HERE, "..", "include", "cacti_b200.h")
 
 OK, ERR_INVALID_VALUE, ERR_DTYPE, ERR_WORKSPACE, ERR_LAUNCH, ERR_SHAPE, ERR_INDEX_RANGE, ERR_NO_DEVICE = range(8)
+ERR_SCRATCH_LIMIT = 8
 R_32F, R_16F, R_16BF, R_32I, R_16U = 0, 2, 14, 10, 22
 MASK_NONE, MASK_CAUSAL = 0, 1
 
@@ -31,6 +32,7 @@ SIGNATURES = {
     "cacti_b200_rmsnorm_fwd": (_int, [_p, _p, _p, _f32, _i64, _i64, _int, _st]),
     "cacti_b200_rmsnorm_bwd": (_int, [_p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _p, _sz, _st]),
     "cacti_b200_rmsnorm_fwd_bwd": (_int, [_p, _p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _p, _sz, _st]),
+    "cacti_b200_rmsnorm_fwd_bwd_noalloc": (_int, [_p, _p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _st]),
     "cacti_b200_softmax_fwd": (_int, [_p, _p, _i64, _i64, _int, _i64, _i64, _i64, _int, _st]),
     "cacti_b200_softmax_bwd": (_int, [_p, _p, _p, _i64, _i64, _int, _i64, _i64, _i64, _int, _int, _st]),
     "cacti_b200_softmax_fwd_bwd": (_int, [_p, _p, _p, _p, _i64, _i64, _int, _i64, _i64, _i64, _int, _int, _st]),

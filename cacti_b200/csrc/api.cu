@@ -27,6 +27,7 @@ const char* cacti_b200_error_string(int code) {
     case CACTI_B200_ERR_SHAPE: return "unsupported shape";
     case CACTI_B200_ERR_INDEX_RANGE: return "index out of range in device data";
     case CACTI_B200_ERR_NO_DEVICE: return "no sm_100 device";
+    case CACTI_B200_ERR_SCRATCH_LIMIT: return "shape exceeds the scratch array built into this no-allocation entry point";
     default: return "unknown error";
   }
 }

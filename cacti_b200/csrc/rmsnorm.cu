@@ -235,8 +235,8 @@ rmsnorm_dgamma_generic_kernel(TO* __restrict__ dgamma, const float* __restrict__
   else dgamma[j] = Elem<TO>::from_f32(acc);
 }
 
-static size_t rmsnorm_ws_bytes(int64_t rows, int64_t cols) {
-  size_t a = (size_t)kRmsMaxPartials * (size_t)cols * sizeof(float);
+static size_t rmsnorm_ws_bytes(int64_t rows, int64_t cols, int max_partials = kRmsMaxPartials) {
+  size_t a = (size_t)max_partials * (size_t)cols * sizeof(float);
   size_t b = (size_t)rows * sizeof(float);
   return (a > b ? a : b) + 256;
 }
@@ -244,7 +244,7 @@ static size_t rmsnorm_ws_bytes(int64_t rows, int64_t cols) {
 template <typename T, typename TO, bool FWD, bool BWD>
 static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, uint64_t gamma, uint64_t dy,
                           float eps, int64_t rows, int64_t cols, int beta_dx, int beta_dg, uint64_t ws,
-                          cudaStream_t st) {
+                          cudaStream_t st, int max_partials = kRmsMaxPartials) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NVMAX = 4;
   T* Y = reinterpret_cast<T*>(y); T* dX = reinterpret_cast<T*>(dx);
@@ -274,7 +274,7 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
   do {                                                                                                      \
     auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD>;                                                      \
     grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                                           \
-    if (grid > kRmsMaxPartials) grid = kRmsMaxPartials;                                                     \
+    if (grid > max_partials) grid = max_partials;                                                           \
     if (grid > want) grid = want;                                                                           \
     kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, nstages, beta_dx); \
   } while (0)
@@ -305,26 +305,60 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
 
 static int rmsnorm_entry(bool fwd, bool bwd, uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, uint64_t gamma,
                          uint64_t dy, float eps, int64_t rows, int64_t cols, int dtype, int dg_dtype, int beta_dx,
-                         int beta_dg, uint64_t ws, size_t ws_bytes, void* stream) {
+                         int beta_dg, uint64_t ws, size_t ws_bytes, void* stream, int max_partials = kRmsMaxPartials) {
   if (rows < 0 || cols < 0 || cols > 0x7fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
   if ((beta_dx | beta_dg) & ~1) return CACTI_B200_ERR_INVALID_VALUE;
   if (rows == 0 || cols == 0) return CACTI_B200_OK;   // reference: an empty cell is a no-op
   if (!x || !gamma || (fwd && !y) || (bwd && (!dx || !dy || !dgamma))) return CACTI_B200_ERR_INVALID_VALUE;
   if (bwd) {
     if (dg_dtype != dtype && dg_dtype != CACTI_B200_R_32F) return CACTI_B200_ERR_DTYPE;
-    if (!ws || ws_bytes < rmsnorm_ws_bytes(rows, cols) || (ws & 3)) return CACTI_B200_ERR_WORKSPACE;
+    if (!ws || ws_bytes < rmsnorm_ws_bytes(rows, cols, max_partials) || (ws & 3)) return CACTI_B200_ERR_WORKSPACE;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
 #define CB_GO(TO_)                                                                                                 \
-  (fwd && bwd) ? launch_rmsnorm<T, TO_, true, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st) \
-  : fwd        ? launch_rmsnorm<T, TO_, true, false>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st) \
-               : launch_rmsnorm<T, TO_, false, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st)
+  (fwd && bwd) ? launch_rmsnorm<T, TO_, true, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st, max_partials) \
+  : fwd        ? launch_rmsnorm<T, TO_, true, false>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st, max_partials) \
+               : launch_rmsnorm<T, TO_, false, true>(y, dx, dgamma, x, gamma, dy, eps, rows, cols, beta_dx, beta_dg, ws, st, max_partials)
     if (bwd && dg_dtype == CACTI_B200_R_32F) return CB_GO(float);
     return CB_GO(T);
 #undef CB_GO
   });
+}
+
+// ---- entry point that needs no caller workspace --------------------------------------------------
+// The column partials of the dgamma reduction live in this file-scope device array instead of a
+// caller-provided buffer.  Every device that loads the library holds the array (about 4.6 MiB) until
+// the process exits.
+constexpr int kNoAllocMaxCols = 4096;                        // widest row this entry point accepts
+constexpr int kNoAllocMaxPartials = 2 * kNumSMs;             // per-CTA partial rows kept in the array
+constexpr size_t kNoAllocRowLimit = (size_t)kNoAllocMaxPartials * kNoAllocMaxCols;
+constexpr size_t kNoAllocFloats = kNoAllocRowLimit + 64;    // + the slack the workspace check asks for
+static __device__ __align__(256) float g_rmsnorm_scratch[kNoAllocFloats];
+
+// `g_rmsnorm_scratch` in host code is only the host-side handle of the symbol, not an address a kernel
+// can use.  The device address is looked up once per device (with that device current) and cached.
+static int noalloc_scratch(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cache[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    g_last_cuda_error = (int)cudaGetLastError();
+    return CACTI_B200_ERR_LAUNCH;
+  }
+  if (!cache[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_rmsnorm_scratch);
+    if (e != cudaSuccess || !p) {
+      g_last_cuda_error = (int)e;
+      (void)cudaGetLastError();
+      return CACTI_B200_ERR_LAUNCH;
+    }
+    cache[dev] = static_cast<float*>(p);
+  }
+  *out = cache[dev];
+  return CACTI_B200_OK;
 }
 
 }  // namespace cb
@@ -351,5 +385,22 @@ int cacti_b200_rmsnorm_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200
                                size_t workspace_bytes, cacti_b200_stream stream) {
   return cb::rmsnorm_entry(true, true, y, dx, dgamma, x, gamma, dy, eps, rows, cols, dtype, dgamma_dtype, beta_dx,
                            beta_dgamma, workspace, workspace_bytes, stream);
+}
+
+int cacti_b200_rmsnorm_fwd_bwd_noalloc(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr x,
+                                       cacti_b200_dptr gamma, cacti_b200_dptr dy, float eps, int64_t rows, int64_t cols,
+                                       int dtype, int dgamma_dtype, int beta_dx, int beta_dgamma,
+                                       cacti_b200_stream stream) {
+  using namespace cb;
+  if (rows < 0 || cols < 0) return CACTI_B200_ERR_INVALID_VALUE;
+  // limits of the built-in array: the vector path stores 2*148 partial rows of `cols` floats, the
+  // element-wise path one float per row
+  if (cols > kNoAllocMaxCols || (size_t)rows > kNoAllocRowLimit) return CACTI_B200_ERR_SCRATCH_LIMIT;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  return rmsnorm_entry(true, true, y, dx, dgamma, x, gamma, dy, eps, rows, cols, dtype, dgamma_dtype, beta_dx,
+                       beta_dgamma, reinterpret_cast<uint64_t>(scratch), kNoAllocFloats * sizeof(float), stream,
+                       kNoAllocMaxPartials);
 }
 }

@@ -48,7 +48,8 @@ enum {
   CACTI_B200_ERR_LAUNCH        = 4,  /* the CUDA runtime refused a launch; see cacti_b200_last_cuda_error */
   CACTI_B200_ERR_SHAPE         = 5,  /* shape outside what the entry point supports     */
   CACTI_B200_ERR_INDEX_RANGE   = 6,  /* written to a status word: token/target index out of range */
-  CACTI_B200_ERR_NO_DEVICE     = 7   /* current device is not an sm_100 part            */
+  CACTI_B200_ERR_NO_DEVICE     = 7,  /* current device is not an sm_100 part            */
+  CACTI_B200_ERR_SCRATCH_LIMIT = 8   /* shape needs more scratch than a *_noalloc entry point has built in */
 };
 
 /* element types: cudaDataType_t codes (cacti_gpu_cu_ffi/src/types.rs:97-102) */
@@ -100,6 +101,23 @@ int cacti_b200_rmsnorm_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200
                                int64_t rows, int64_t cols, int dtype, int dgamma_dtype,
                                int beta_dx, int beta_dgamma,
                                cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
+
+/* Same computation as cacti_b200_rmsnorm_fwd_bwd for callers that have no workspace to give.  It has no
+ * counterpart in the reference.  It is meant for hosts such as cacti's pctx, which takes almost all device
+ * memory into its own arena at start-up and hands thunks only cells from that arena: when the arena is
+ * exhausted, or at a point where the host must not enter the CUDA allocator, such a caller cannot produce the
+ * workspace the entry point above asks for.  Here the dgamma partials go to an array that is part of the
+ * library image (about 4.6 MiB on every device that loads the library, for the life of the process); the
+ * function itself calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Limits: cols <= 4096 (and rows <= 1212416 for rows that take the element-wise path); larger shapes return
+ * CACTI_B200_ERR_SCRATCH_LIMIT.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call outside any stream capture.
+ * All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race on
+ * it.  Nothing in it has to be cleared between calls; every launch overwrites the part it later reads. */
+int cacti_b200_rmsnorm_fwd_bwd_noalloc(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dptr dgamma,
+                                       cacti_b200_dptr x, cacti_b200_dptr gamma, cacti_b200_dptr dy, float eps,
+                                       int64_t rows, int64_t cols, int dtype, int dgamma_dtype,
+                                       int beta_dx, int beta_dgamma, cacti_b200_stream stream);
 
 /* ---- K2 masked row softmax --------------------------------------------------------
  * Replaces cast + BlockTriElemAffine (src/thunk/op.rs:4189-4278) + InnerSoftmax (:3257-3383)
