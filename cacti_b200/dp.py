@@ -1,0 +1,60 @@
+"""Data-parallel plumbing for the row-sharded path: which sequences a rank owns, and the one exchange step
+(sum of weight gradients across ranks) as bucketed all-reduces through torch.distributed.
+
+The reference is single-GPU (src/pctx/mod.rs:303-311 takes device 0); rows (sequences) are independent in
+every thunk of the path, so ranks need no data-path collective.  Gradient dtype = parameter dtype, as in the
+reference (examples/open_llama_3b_train.rs:161-169).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_sequences(n_seq: int, world: int, rank: int):
+    """Contiguous block of sequences for `rank`: (first, count).  Earlier ranks take the remainder."""
+    base, rem = divmod(n_seq, world)
+    first = rank * base + min(rank, rem)
+    return first, base + (1 if rank < rem else 0)
+
+
+def alloc_bucketed_grads(params):
+    """Gradient tensors shaped like `params`; each layer's gradients are views of one flat buffer (a bucket),
+    and the non-layer parameters share a final bucket.  Returns (grads, buckets)."""
+    def carve(named):
+        total = sum((t.numel() + 127) // 128 * 128 for _, t in named)
+        first = named[0][1]
+        flat = torch.zeros(total, dtype=first.dtype, device=first.device)
+        out, off = {}, 0
+        for k, t in named:
+            out[k] = flat[off:off + t.numel()].view(t.shape)
+            off += (t.numel() + 127) // 128 * 128
+        return out, flat
+
+    grads, buckets = {"layers": []}, []
+    for L in params["layers"]:
+        g, flat = carve(list(L.items()))
+        grads["layers"].append(g)
+        buckets.append(flat)
+    g, flat = carve([(k, v) for k, v in params.items() if k != "layers"])
+    grads.update(g)
+    buckets.append(flat)
+    return grads, buckets
+
+
+class GradReducer:
+    """Launches one asynchronous all-reduce per bucket as soon as the bucket is complete, so the exchange
+    overlaps the rest of the backward pass; `finish()` waits for all of them."""
+
+    def __init__(self, buckets, group=None):
+        self.buckets, self.group, self.pending = buckets, group, []
+        self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+    def reduce_bucket(self, i: int):
+        if self.enabled:
+            self.pending.append(dist.all_reduce(self.buckets[i], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self):
+        for w in self.pending:
+            w.wait()
+        self.pending = []

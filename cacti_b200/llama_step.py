@@ -1,0 +1,187 @@
+"""One OpenLLaMA-shaped training step (forward + backward) issued purely through the C ABI.
+
+This is the workload of BASELINE config 5: the op sequence of `Llama::apply` (src/librarium/llama.rs:420-548)
+and of the adjoints the spine would stage for it (src/spine.rs:447-690), with each group of primitive thunks
+replaced by its fused entry point.  It is host plumbing only: torch owns device memory and streams, every
+arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph, all stated:
+  * the f32 probability tensor `out_lm_prob` and the arg-max (llama.rs:543,546) are not produced;
+  * attention probabilities are recomputed from the saved scores in the backward instead of being kept
+    (one extra softmax pass per layer, 2.1 GB less live memory per layer at B = 8);
+  * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted.
+Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+from .capi import lib
+
+
+@dataclass
+class LlamaShape:
+    layers: int = 26
+    d_model: int = 3200
+    heads: int = 32
+    head_dim: int = 100
+    ffn: int = 8640
+    vocab: int = 32000
+    seq: int = 2048
+    eps: float = 1e-6
+    theta: float = 10000.0
+
+    @staticmethod
+    def open_llama_3b():
+        """LlamaConfig::open_llama_3b, src/librarium/llama.rs:88-105."""
+        return LlamaShape()
+
+
+def init_weights(cfg: LlamaShape, device, seed=0, std=0.02, dtype=torch.float16):
+    """Random-init weights ~ N(0, std^2); norm gains are 1 (a gain ~N(0, 0.02^2) would scale every residual
+    branch by 0.02 and make the step degenerate)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def w(*shape):
+        return (torch.randn(*shape, device=device, generator=g) * std).to(dtype)
+
+    D, F, V = cfg.d_model, cfg.ffn, cfg.vocab
+    P = {"embed": w(V, D), "lm_head": w(V, D), "head_norm": torch.ones(D, device=device, dtype=dtype), "layers": []}
+    for _ in range(cfg.layers):
+        P["layers"].append({"pre_norm": torch.ones(D, device=device, dtype=dtype), "q": w(D, D), "k": w(D, D),
+                            "v": w(D, D), "o": w(D, D), "post_norm": torch.ones(D, device=device, dtype=dtype),
+                            "up": w(F, D), "gate": w(F, D), "down": w(D, F)})
+    return P
+
+
+def zeros_like_params(P):
+    out = {k: torch.zeros_like(v) for k, v in P.items() if k != "layers"}
+    out["layers"] = [{k: torch.zeros_like(v) for k, v in L.items()} for L in P["layers"]]
+    return out
+
+
+def flat_params(P):
+    """(name, tensor) pairs in a fixed order (used for gradient bucketing)."""
+    out = [("embed", P["embed"]), ("lm_head", P["lm_head"]), ("head_norm", P["head_norm"])]
+    for i, L in enumerate(P["layers"]):
+        out += [(f"layers.{i}.{k}", v) for k, v in L.items()]
+    return out
+
+
+class TrainStep:
+    """Forward + backward over `batch` sequences of cfg.seq tokens.  Gradients are written (Apply mode) into
+    `grads`, a structure shaped like the parameters; `on_layer_done(i)` is called after layer i's weight
+    gradients are complete (the hook a data-parallel reducer attaches to)."""
+
+    def __init__(self, cfg: LlamaShape, params, batch: int, loss_tokens: int | None = None):
+        self.cfg, self.P, self.B = cfg, params, batch
+        dev = params["embed"].device
+        self.dev = dev
+        self.T = batch * cfg.seq
+        self.loss_tokens = loss_tokens or self.T           # global token count: the loss is a mean over all ranks
+        self.cos, self.sin = ops.rope_tables(cfg.seq, cfg.head_dim, cfg.theta, params["embed"].dtype, dev)
+        L = lib()
+        S, hd, H = cfg.seq, cfg.head_dim, cfg.heads
+        nb = max(L.cacti_b200_gemm_workspace_bytes(S, S, hd, batch, H), L.cacti_b200_gemm_workspace_bytes(S, hd, S, batch, H),
+                 L.cacti_b200_gemm_workspace_bytes(hd, S, S, batch, H))
+        self.gemm_ws = torch.empty(nb, dtype=torch.uint8, device=dev)
+        self.norm_ws = ops.rmsnorm_workspace(self.T, cfg.d_model, dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.launches = 0
+
+    # -- small helpers (each is exactly one or two C-ABI calls) -----------------------------------------
+    def _mm(self, a, b, ta, tb, c=None, beta=0.0):
+        self.launches += 1
+        return ops.gemm(a, b, ta, tb, beta=beta, c=c)
+
+    def _bmm(self, a, b, ta, tb, alpha=1.0):
+        self.launches += 3
+        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws)
+
+    def forward_backward(self, tokens, targets, grads, on_layer_done=None):
+        cfg, P, B, T = self.cfg, self.P, self.B, self.T
+        S, H, hd, D = cfg.seq, cfg.heads, cfg.head_dim, cfg.d_model
+        alpha = 1.0 / math.sqrt(hd)
+        mask = (H, S, 0)                                  # scores [B, S, H, S]: q_pos = (row / H) % S
+        self.launches = 0
+        x, _ = ops.gather_rows(P["embed"], tokens, status=self.status)
+        self.launches += 1
+        saved = []
+        for Lw in P["layers"]:
+            n1 = ops.rmsnorm_fwd(x, Lw["pre_norm"], cfg.eps)
+            q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
+            k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
+            v = self._mm(n1, Lw["v"], False, True)
+            sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha)        # [B,S,H,S]
+            p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
+            ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False).view(T, D)
+            del p
+            x_mid = ops.add(x, self._mm(ctx, Lw["o"], False, True))
+            n2 = ops.rmsnorm_fwd(x_mid, Lw["post_norm"], cfg.eps)
+            up = self._mm(n2, Lw["up"], False, True)
+            gate = self._mm(n2, Lw["gate"], False, True)
+            h = ops.swiglu_fwd(gate, up)
+            x_out = ops.add(x_mid, self._mm(h, Lw["down"], False, True))
+            self.launches += 9
+            saved.append((x, n1, q, k, v, sc, ctx, x_mid, n2, up, gate, h))
+            x = x_out
+        nf = ops.rmsnorm_fwd(x, P["head_norm"], cfg.eps)
+        logits = self._mm(nf, P["lm_head"], False, True)
+        loss, _, dlogits, _ = ops.softmax_nll_fwd_bwd(logits, targets, w_scalar=1.0 / self.loss_tokens, want_rows=False,
+                                                       status=self.status)
+        self.launches += 3
+        del logits
+        # ---------------------------------------------------------------- backward
+        self._mm(dlogits, nf, True, False, c=grads["lm_head"])
+        dnf = self._mm(dlogits, P["lm_head"], False, False)
+        del dlogits
+        dx, _ = ops.rmsnorm_bwd(x, P["head_norm"], dnf, cfg.eps, dgamma=grads["head_norm"], workspace=self.norm_ws)
+        self.launches += 2
+        for li in range(cfg.layers - 1, -1, -1):
+            Lw, G = P["layers"][li], grads["layers"][li]
+            x_in, n1, q, k, v, sc, ctx, x_mid, n2, up, gate, h = saved.pop()
+            # MLP branch: x_out = x_mid + h Wdown^T
+            self._mm(dx, h, True, False, c=G["down"])
+            dh = self._mm(dx, Lw["down"], False, False)
+            dgate, dup = ops.swiglu_bwd(gate, up, dh)
+            del dh, h
+            self._mm(dup, n2, True, False, c=G["up"])
+            self._mm(dgate, n2, True, False, c=G["gate"])
+            dn2 = self._mm(dup, Lw["up"], False, False)
+            self._mm(dgate, Lw["gate"], False, False, c=dn2, beta=1.0)
+            del dgate, dup, up, gate
+            ops.rmsnorm_bwd(x_mid, Lw["post_norm"], dn2, cfg.eps, dx=dx, dgamma=G["post_norm"], beta_dx=1,
+                            workspace=self.norm_ws)                                  # dx += adjoint through the norm
+            del dn2
+            # attention branch: x_mid = x_in + ctx Wo^T
+            self._mm(dx, ctx, True, False, c=G["o"])
+            dctx = self._mm(dx, Lw["o"], False, False)
+            p = ops.softmax_fwd(sc.view(B * S * H, S), mask)                         # recomputed probabilities
+            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False).view(T, D)       # P^T dctx
+            dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True)                   # dctx V^T
+            del p, dctx
+            ds = ops.softmax_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
+            del dp, sc
+            dq = self._bmm(ds.view(B, S, H, S), k.view(B, S, H, hd), False, False, alpha)              # dS K
+            dk = self._bmm(ds.view(B, S, H, S), q.view(B, S, H, hd), True, False, alpha)               # dS^T Q
+            del ds
+            dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
+            dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)
+            self._mm(dq, n1, True, False, c=G["q"])
+            self._mm(dk, n1, True, False, c=G["k"])
+            self._mm(dv, n1, True, False, c=G["v"])
+            dn1 = self._mm(dq, Lw["q"], False, False)
+            self._mm(dk, Lw["k"], False, False, c=dn1, beta=1.0)
+            self._mm(dv, Lw["v"], False, False, c=dn1, beta=1.0)
+            del dq, dk, dv
+            ops.rmsnorm_bwd(x_in, Lw["pre_norm"], dn1, cfg.eps, dx=dx, dgamma=G["pre_norm"], beta_dx=1,
+                            workspace=self.norm_ws)
+            del dn1
+            self.launches += 12
+            if on_layer_done is not None:
+                on_layer_done(li)
+        ops.scatter_add_rows(dx, tokens, cfg.vocab, dtable=grads["embed"], status=self.status)
+        self.launches += 5
+        return loss

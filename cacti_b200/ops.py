@@ -235,10 +235,13 @@ def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
     k = a.shape[0] if trans_a else a.shape[1]
     n = b.shape[0] if trans_b else b.shape[1]
     c = torch.empty(m, n, dtype=a.dtype, device=a.device) if c is None else c
-    ws = _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, 1, 1), a.device)
+    # a repack workspace is only needed when TMA cannot address an operand (16-byte base and row pitch)
+    aligned = all(t.data_ptr() % 16 == 0 and (t.stride(0) * t.element_size()) % 16 == 0 for t in (a, b))
+    ws = None if aligned else _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, 1, 1), a.device)
     al, be = _scalars(alpha, beta)
     check(lib().cacti_b200_gemm(_ptr(c), _ptr(a), _ptr(b), m, n, k, a.stride(0), b.stride(0), c.stride(0), int(trans_a),
-                                int(trans_b), al, be, _dt(a), _ptr(ws), ws.numel(), _stream()), "gemm")
+                                int(trans_b), al, be, _dt(a), _ptr(ws), ws.numel() if ws is not None else 0, _stream()),
+          "gemm")
     return c
 
 

@@ -1,0 +1,71 @@
+"""World-size-2 gloo test of the data-parallel host logic (sequence sharding, bucketed gradient all-reduce)."""
+import os
+import socket
+import subprocess
+import sys
+
+import torch
+
+from cacti_b200 import dp
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from cacti_b200 import dp
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=int(os.environ["RANK"]), world_size=2)
+rank = dist.get_rank()
+params = {"embed": torch.zeros(7, 5), "head_norm": torch.zeros(5),
+          "layers": [{"q": torch.zeros(5, 5), "pre_norm": torch.zeros(5)} for _ in range(3)]}
+grads, buckets = dp.alloc_bucketed_grads(params)
+assert len(buckets) == 4
+red = dp.GradReducer(buckets)
+assert red.enabled
+for li in (2, 1, 0):                      # backward order
+    grads["layers"][li]["q"].fill_(float(rank + 1) * (li + 1))
+    grads["layers"][li]["pre_norm"].fill_(float(rank + 10))
+    red.reduce_bucket(li)
+grads["embed"].fill_(float(rank)); grads["head_norm"].fill_(1.0)
+red.reduce_bucket(3)
+red.finish()
+for li in range(3):
+    assert torch.all(grads["layers"][li]["q"] == 3.0 * (li + 1)), grads["layers"][li]["q"]
+    assert torch.all(grads["layers"][li]["pre_norm"] == 21.0)
+assert torch.all(grads["embed"] == 1.0) and torch.all(grads["head_norm"] == 2.0)
+first, count = dp.shard_sequences(8, 2, rank)
+t = torch.tensor([first, count]); out = [torch.zeros(2, dtype=torch.long) for _ in range(2)]
+dist.all_gather(out, t)
+assert [o.tolist() for o in out] == [[0, 4], [4, 4]]
+dist.destroy_process_group()
+print("ok", rank)
+'''
+
+
+def test_shard_sequences_covers_everything():
+    for n in (1, 7, 8, 9):
+        for world in (1, 2, 4, 8):
+            got = [dp.shard_sequences(n, world, r) for r in range(world)]
+            assert sum(c for _, c in got) == n
+            pos = 0
+            for first, count in got:
+                assert first == pos
+                pos += count
+
+
+def test_bucketed_grads_are_views_of_the_buckets():
+    params = {"embed": torch.zeros(3, 4), "layers": [{"a": torch.zeros(2, 2), "b": torch.zeros(5)}]}
+    grads, buckets = dp.alloc_bucketed_grads(params)
+    grads["layers"][0]["b"].fill_(2.0)
+    assert buckets[0].sum().item() == 10.0 and grads["layers"][0]["a"].shape == (2, 2)
+    assert dp.GradReducer(buckets).enabled is False        # no process group: a single-GPU run reduces nothing
+
+
+def test_gloo_world2_allreduce():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), PORT=str(port), REPO=repo)
+        procs.append(subprocess.Popen([sys.executable, "-c", WORKER], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"ok {r}" in o, o

@@ -1,0 +1,44 @@
+"""The composed training step (BASELINE config 5 at reduced depth/width) against the composed CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from cacti_b200 import llama_step as LS
+from oracle import llama_oracle, ref_chain as R
+from tests.gpu_util import dev, host
+from tests.tolerances import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _np_params(P):
+    out = {k: host(v) for k, v in P.items() if k != "layers"}
+    out["layers"] = [{k: host(v) for k, v in L.items()} for L in P["layers"]]
+    return out
+
+
+@pytest.mark.parametrize("hd,heads", [(20, 4), (16, 2)])
+def test_reduced_step_matches_oracle(cuda, hd, heads):
+    cfg = LS.LlamaShape(layers=2, d_model=hd * heads, heads=heads, head_dim=hd, ffn=96, vocab=160, seq=32)
+    B = 2
+    P = LS.init_weights(cfg, cuda, seed=0, std=0.08)
+    # non-trivial norm gains so that dgamma and the gain path are exercised
+    for L in P["layers"]:
+        L["pre_norm"].copy_(dev(R.normal(50, (cfg.d_model,), np.float16, 0.1, 1.0)))
+        L["post_norm"].copy_(dev(R.normal(51, (cfg.d_model,), np.float16, 0.1, 1.0)))
+    tok = R.uniform_int(1, B * cfg.seq, cfg.vocab)
+    tgt = R.uniform_int(2, B * cfg.seq, cfg.vocab)
+    grads = LS.zeros_like_params(P)
+    step = LS.TrainStep(cfg, P, B)
+    loss = step.forward_backward(dev(tok), dev(tgt), grads)
+    torch.cuda.synchronize()
+    assert host(step.status)[0] == 0
+    ref_loss, ref_g = llama_oracle.step(_np_params(P), tok, tgt, cfg)
+    assert abs(float(host(loss)[0]) - float(ref_loss)) < 2e-3 * abs(float(ref_loss))
+    # gradients pass through ~40 f16-rounded thunks; hold them to 2 % of the tensor's rms
+    for name in ("lm_head", "head_norm", "embed"):
+        assert_close(host(grads[name]), ref_g[name], "float16", name, rtol=2e-2, floor_frac=1.0)
+    for li in range(cfg.layers):
+        for name, g in grads["layers"][li].items():
+            assert_close(host(g), ref_g["layers"][li][name], "float16", f"layer {li} {name}", rtol=2e-2, floor_frac=1.0)
+    assert step.launches > 0
