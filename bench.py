@@ -39,6 +39,14 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_BYTES = None
 
 
+def measured_tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 def measured_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -203,7 +211,91 @@ def other_thunks(torch, ops, peak):
     h, dga, dup = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
     sec = time_thunk(lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup), 20, 5, torch)
     report("swiglu_fwd_bwd[16384x8640,f16]", sec, 6 * 16384 * 8640 * 2, 1)
+    del ga, up, dh, h, dga, dup
+    # G1 dense matmul: gate projection x[16384,3200] W[8640,3200]^T and its two adjoints (tensor roofline)
+    tpeak = measured_tensor_peak()
+    x, w, dyp = rnd(16384, 3200), rnd(8640, 3200, scale=0.02), rnd(16384, 8640)
+    c = torch.empty(16384, 8640, dtype=torch.float16, device="cuda")
+    dxp = torch.empty(16384, 3200, dtype=torch.float16, device="cuda")
+    dw = torch.empty(8640, 3200, dtype=torch.float16, device="cuda")
+    flops = 2 * 16384 * 8640 * 3200
+    for name, fn in (("gemm_nt y=xW^T", lambda: ops.gemm(x, w, False, True, c=c)),
+                     ("gemm_nn dx=dyW", lambda: ops.gemm(dyp, w, False, False, c=dxp)),
+                     ("gemm_tn dW=dy^Tx", lambda: ops.gemm(dyp, x, True, False, c=dw))):
+        sec = time_thunk(fn, 10, 3, torch)
+        out[name + "[16384x8640x3200,f16]"] = {"TFLOP/s": round(flops / sec / 1e12, 1), "frac_of_measured_burst_peak": round(flops / sec / 1e12 / tpeak, 3),
+                                              "frac_of_nominal_2250": round(flops / sec / 1e12 / 2250.0, 3), "us": round(sec * 1e6, 1), "launches_per_step": 1}
+    del x, w, dyp, c, dxp, dw
+    # G2 block matmul at config 5 (B = 8): HBM-bound by the 2.1 GB score tensor
+    B, S, H, hd = 8, 2048, 32, 100
+    q, k = rnd(B, S, H, hd), rnd(B, S, H, hd)
+    sc = torch.empty(B, S, H, S, dtype=torch.float16, device="cuda")
+    ws = torch.empty(ops.lib().cacti_b200_gemm_workspace_bytes(S, S, hd, B, H), dtype=torch.uint8, device="cuda")
+    sec = time_thunk(lambda: ops.block_gemm(q, k, False, True, alpha=0.1, c=sc, workspace=ws), 5, 3, torch)
+    nbytes = B * H * S * S * 2 + 2 * B * S * H * hd * 2
+    out["block_gemm QK^T[8x2048x32x100]"] = {"TFLOP/s": round(2 * B * H * S * S * hd / sec / 1e12, 1), "GB/s": round(nbytes / sec / 1e9, 1),
+                                             "frac_of_peak": round(nbytes / sec / 1e9 / peak, 3), "us": round(sec * 1e6, 1), "launches_per_step": 3}
+    v = rnd(B, S, H, hd)
+    ctx = torch.empty(B, S, H, hd, dtype=torch.float16, device="cuda")
+    sec = time_thunk(lambda: ops.block_gemm(sc, v, False, False, c=ctx, workspace=ws), 5, 3, torch)
+    out["block_gemm PV[8x2048x32x100]"] = {"TFLOP/s": round(2 * B * H * S * S * hd / sec / 1e12, 1), "GB/s": round(nbytes / sec / 1e9, 1),
+                                           "frac_of_peak": round(nbytes / sec / 1e9 / peak, 3), "us": round(sec * 1e6, 1), "launches_per_step": 2}
     return out
+
+
+def train_step_leg(torch, dist, rank, world, dev, steps):
+    """BASELINE config 5: one OpenLLaMA-3B-shaped forward+backward over 8 sequences of 2048 tokens, the sequences
+    split across the ranks (strong scaling), weight gradients summed with bucketed NCCL all-reduces that overlap
+    the backward pass.  Random-init weights, synthetic token ids."""
+    from cacti_b200 import dp, llama_step as LS
+    cfg = LS.LlamaShape.open_llama_3b()
+    n_seq = 8
+    first, count = dp.shard_sequences(n_seq, world, rank)
+    P = LS.init_weights(cfg, dev, seed=0)
+    grads, buckets = dp.alloc_bucketed_grads(P)
+    red = dp.GradReducer(buckets)
+    step = LS.TrainStep(cfg, P, count, loss_tokens=n_seq * cfg.seq)
+    g = torch.Generator(device=dev).manual_seed(1)
+    tok_all = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g)
+    tgt_all = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g)
+    sl = slice(first * cfg.seq, (first + count) * cfg.seq)
+    h_tok, h_tgt = tok_all[sl].cpu().pin_memory(), tgt_all[sl].cpu().pin_memory()
+    tok, tgt = torch.empty_like(tok_all[sl]), torch.empty_like(tgt_all[sl])
+    nl = cfg.layers
+
+    def one():
+        # end to end: token ids come from pinned host memory, the loss goes back to the host
+        tok.copy_(h_tok, non_blocking=True); tgt.copy_(h_tgt, non_blocking=True)
+        loss = step.forward_backward(tok, tgt, grads, on_layer_done=red.reduce_bucket)
+        red.reduce_bucket(nl)
+        red.finish()
+        if world > 1:
+            dist.all_reduce(loss)
+        return loss.cpu()
+
+    for _ in range(2):
+        one()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss = one()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    return {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (BASELINE config 5)",
+            "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "scaling": "strong", "n_gpus": world,
+            "sequences_per_gpu": count, "loss": float(loss.item()), "gpu_launches_per_step": step.launches,
+            "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+            "h2d_bytes_per_step": 2 * count * cfg.seq * 4, "d2h_bytes_per_step": 4,
+            "note": "no optimizer step (the optimizer thunks are outside this path); gradients of all parameters are produced and all-reduced"}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -306,6 +398,11 @@ def run_ours(args, rank, world, local_rank):
     e2e_ok = bool(torch.equal(hp[:SEQ], p[:SEQ].cpu()) and torch.equal(hds[-SEQ:], ds[-SEQ:].cpu()))
     del hs, hdp, hp, hds, bufs
 
+    train = None
+    if not args.no_train:
+        torch.cuda.empty_cache()
+        train = train_step_leg(torch, dist, rank, world, dev, max(1, min(args.steps, 3)))
+        torch.cuda.empty_cache()
     line = None
     if rank == 0:
         thunks = other_thunks(torch, ops, peak) if not args.no_extra else {}
@@ -330,7 +427,7 @@ def run_ours(args, rank, world, local_rank):
             "cpu_baseline": cpu,
             "e2e": {"value": world * ALGO_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * ELEMS * 2, "d2h_bytes_per_step": 2 * ELEMS * 2, "verified": e2e_ok},
-            "gpu_launches": args.steps, "clocks": clocks.summary(), "thunks": thunks,
+            "gpu_launches": args.steps, "clocks": clocks.summary(), "thunks": thunks, "train_step": train,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -346,6 +443,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the per-thunk table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-train", action="store_true", help="skip the config-5 training-step leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
