@@ -25,7 +25,7 @@
 //
 // Operands that TMA cannot address (base or a stride not a multiple of 16 bytes, e.g. head_dim 100
 // slices at 200-byte offsets) are first repacked into the caller's workspace with the inner
-// dimension padded to a multiple of 8 elements; the reference pads the same operands to 16 bytes
+// dimension zero-padded to a multiple of 64 elements; the reference pads the same operands to 16 bytes
 // with a separate thunk before calling cuBLAS (src/op.rs:1454-1482).  Outputs need no alignment.
 #include "common.cuh"
 #include <cuda.h>
@@ -334,26 +334,23 @@ done:
 }
 
 // Repack blocks [nbo][nbi] of a stored matrix [rows x cols] (leading dimension ld, block strides so/si)
-// into a dense [nbo*nbi][rows][cols_pad] buffer, zero-filling the padding columns.  One warp per row;
-// 4-byte units when every row start is 4-byte aligned, else elements.
-template <typename T>
+// into a dense [nbo*nbi][rows][cols_pad] buffer, zero-filling the padding columns.  One thread per unit of
+// UNIT bytes (8 when every row start is 8-byte aligned and cols % 4 == 0, else 4 or 2); consecutive threads
+// take consecutive units of a row, so both sides are coalesced.
+template <typename U>
 __global__ void __launch_bounds__(256)
-pack_blocks_kernel(T* __restrict__ dst, const T* __restrict__ src, int rows, int cols, int cols_pad, long long ld,
-                   int nbi, long long so, long long si, long long total_rows, int pairs_ok) {
-  const int lane = threadIdx.x & 31;
-  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < total_rows; t += (long long)gridDim.x * 8) {
-    const int r = (int)(t % rows);
-    const int blk = (int)(t / rows);
-    const int bo = blk / nbi, bi = blk - bo * nbi;
-    const T* s = src + bo * so + bi * si + (long long)r * ld;
-    T* d = dst + t * cols_pad;
-    if (pairs_ok) {
-      const uint32_t* s2 = reinterpret_cast<const uint32_t*>(s);
-      uint32_t* d2 = reinterpret_cast<uint32_t*>(d);
-      for (int c = lane; c < cols_pad / 2; c += 32) d2[c] = c < cols / 2 ? __ldg(s2 + c) : 0u;
-    } else {
-      for (int c = lane; c < cols_pad; c += 32) d[c] = c < cols ? s[c] : Elem<T>::from_f32(0.f);
-    }
+pack_blocks_kernel(U* __restrict__ dst, const U* __restrict__ src, unsigned rows, unsigned upr_src /* units per source row */,
+                   unsigned upr_dst, long long ld_units, unsigned nbi, long long so_units, long long si_units,
+                   long long total_units) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_units; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / upr_dst;                      // destination row
+    const unsigned c = (unsigned)(i - t * upr_dst);
+    const unsigned blk = (unsigned)(t / rows);
+    const unsigned r = (unsigned)(t - (long long)blk * rows);
+    const unsigned bo = blk / nbi, bi = blk - bo * nbi;
+    U v{};
+    if (c < upr_src) v = src[bo * so_units + bi * si_units + (long long)r * ld_units + c];
+    dst[i] = v;
   }
 }
 
@@ -376,6 +373,7 @@ static EncodeTiledFn encode_fn() {
 // One operand as stored: `rows` x `cols` elements, cols contiguous, leading dimension ld, block strides.
 struct Operand {
   uint64_t ptr; long long rows, cols, ld, stride_inner, stride_outer; int has_j, has_i;
+  long long map_cols = 0;     // inner extent given to the tensor map (0: cols); > cols for zero-padded repacked operands
 };
 
 static bool tma_ok(const Operand& o, int nbi, int nbo) {
@@ -390,7 +388,7 @@ static int encode_operand(CUtensorMap* map, const Operand& o, int nbi, int nbo, 
   EncodeTiledFn fn = encode_fn();
   if (!fn) return CACTI_B200_ERR_LAUNCH;
   const cuuint64_t dj = (o.has_j && nbi > 1) ? (cuuint64_t)nbi : 1, di = (o.has_i && nbo > 1) ? (cuuint64_t)nbo : 1;
-  cuuint64_t dims[4] = {(cuuint64_t)o.cols, (cuuint64_t)o.rows, dj, di};
+  cuuint64_t dims[4] = {(cuuint64_t)(o.map_cols ? o.map_cols : o.cols), (cuuint64_t)o.rows, dj, di};
   const cuuint64_t row_bytes = (cuuint64_t)o.ld * 2;
   const cuuint64_t dflt = row_bytes * (cuuint64_t)o.rows;      // any legal value for an extent-1 dimension
   cuuint64_t strides[3] = {row_bytes, dj > 1 ? (cuuint64_t)o.stride_inner * 2 : dflt,
@@ -404,8 +402,12 @@ static int encode_operand(CUtensorMap* map, const Operand& o, int nbi, int nbo, 
   return CACTI_B200_OK;
 }
 
+// Repacked operands are padded to a multiple of 64 columns (one 128-byte swizzle span) with zeros, so that no
+// TMA box of theirs is partly out of range: measured on B200, boxes that needed out-of-range fill made the
+// head_dim-100 block matmuls 1.45x slower than the same kernel on head_dim 128.
+static long long packed_cols(long long cols) { return (cols + 63) / 64 * 64; }
 static size_t packed_bytes(long long rows, long long cols, long long nblk) {
-  const long long cp = (cols + 7) / 8 * 8;
+  const long long cp = packed_cols(cols);
   return ((size_t)nblk * rows * cp * 2 + 255) / 256 * 256;
 }
 
@@ -424,19 +426,25 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     const long long nblk = (long long)((o->has_j ? nbi : 1)) * (o->has_i ? nbo : 1);
     const size_t need = packed_bytes(o->rows, o->cols, nblk);
     if (!ws || (ws & 255) || ws_off + need > ws_bytes) return CACTI_B200_ERR_WORKSPACE;
-    const long long cp = (o->cols + 7) / 8 * 8;
-    const long long total_rows = nblk * o->rows;
-    long long grid = (total_rows + 7) / 8;
-    if (grid > (long long)kNumSMs * 32) grid = (long long)kNumSMs * 32;
+    const long long cp = packed_cols(o->cols);
     const int eff_nbi = o->has_j ? nbi : 1;
     const long long so_ = o->has_i ? o->stride_outer : 0, si_ = o->has_j ? o->stride_inner : 0;
-    const int pairs_ok = !(o->cols & 1) && !(o->ptr & 3) && !(o->ld & 1) && !(so_ & 1) && !(si_ & 1);
-    pack_blocks_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<T*>(ws + ws_off),
-                                                         reinterpret_cast<const T*>(o->ptr), (int)o->rows, (int)o->cols,
-                                                         (int)cp, o->ld, eff_nbi, so_, si_, total_rows, pairs_ok);
+    // widest unit (in elements) that divides every offset involved
+    const unsigned long long all = (unsigned long long)(o->ptr / 2) | (unsigned long long)o->ld | (unsigned long long)so_ |
+                                   (unsigned long long)si_ | (unsigned long long)o->cols;
+    const int ue = (all & 3) == 0 ? 4 : (all & 1) == 0 ? 2 : 1;       // elements per unit
+    const long long total_units = nblk * o->rows * (cp / ue);
+    long long grid = (total_units + 255) / 256;
+    if (grid > (long long)kNumSMs * 32) grid = (long long)kNumSMs * 32;
+#define CB_PACK(U_)                                                                                              \
+  pack_blocks_kernel<U_><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<U_*>(ws + ws_off),                     \
+      reinterpret_cast<const U_*>(o->ptr), (unsigned)o->rows, (unsigned)(o->cols / ue), (unsigned)(cp / ue),     \
+      o->ld / ue, (unsigned)eff_nbi, so_ / ue, si_ / ue, total_units)
+    if (ue == 4) CB_PACK(uint2); else if (ue == 2) CB_PACK(uint32_t); else CB_PACK(uint16_t);
+#undef CB_PACK
     int rc = check_launch();
     if (rc) return rc;
-    o->ptr = ws + ws_off; o->ld = cp;
+    o->ptr = ws + ws_off; o->ld = cp; o->map_cols = cp;
     o->stride_inner = o->rows * cp;
     o->stride_outer = o->rows * cp * eff_nbi;
     ws_off += need;

@@ -4,7 +4,7 @@ import torch
 from . import ops
 
 
-def make(case, rnd):
+def make(case, rnd, batch=2):
     if case.startswith("gemm_"):
         m, n, k = 4096, 3200, 3200
         if case == "gemm_nt":          # y = x W^T (forward projection)
@@ -19,7 +19,7 @@ def make(case, rnd):
             a, b = rnd(m, n), rnd(m, k)
             c = torch.empty(n, k, dtype=torch.float16, device="cuda")
             return lambda: ops.gemm(a, b, True, False, c=c)
-    bsz, s, h, hd = 2, 2048, 32, 100
+    bsz, s, h, hd = batch, 2048, 32, 100
     if case == "qk":
         q, kk = rnd(bsz, s, h, hd), rnd(bsz, s, h, hd)
         c = torch.empty(bsz, s, h, s, dtype=torch.float16, device="cuda")

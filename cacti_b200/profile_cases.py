@@ -20,6 +20,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=2, help="sequences for the qk / pv cases")
     a = ap.parse_args()
     gen = torch.Generator(device="cuda").manual_seed(0)
 
@@ -54,7 +55,7 @@ def main():
         fn = lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup)
     elif a.case.startswith("gemm_") or a.case in ("qk", "pv"):
         from . import gemm_cases
-        fn = gemm_cases.make(a.case, rnd)
+        fn = gemm_cases.make(a.case, rnd, a.batch)
     else:
         raise SystemExit(f"unknown case {a.case}")
     for _ in range(a.launches):
