@@ -251,18 +251,28 @@ template <typename F> inline int dispatch_dtype(int dtype, F&& f) {
 constexpr size_t kMaxDynSmem = 200 * 1024;      // of the 227 KB a CTA may use
 
 // CTAs of `kern` that fit on one SM with this block size and dynamic shared memory; also raises the
-// kernel's dynamic shared memory limit when needed.  The answer is cached per (kernel, config).
+// kernel's dynamic shared memory limit when needed (never lowers it).  Cached per (kernel, config).
 template <typename K> inline int resident_ctas(K kern, int threads, size_t smem) {
   struct Key { const void* k; int t; size_t s; int n; };
-  static thread_local Key cache[32];
-  static thread_local int used = 0;
+  struct Lim { const void* k; size_t s; };
+  static thread_local Key cache[64];
+  static thread_local Lim lim[64];
+  static thread_local int used = 0, nlim = 0;
   const void* kp = reinterpret_cast<const void*>(kern);
+  if (smem > 48 * 1024) {
+    int i = 0;
+    for (; i < nlim; ++i) if (lim[i].k == kp) break;
+    if (i == nlim && nlim < 64) lim[nlim++] = Lim{kp, 0};
+    if (i >= 64 || lim[i].s < smem) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (i < 64) lim[i].s = smem;
+    }
+  }
   for (int i = 0; i < used; ++i)
     if (cache[i].k == kp && cache[i].t == threads && cache[i].s == smem) return cache[i].n;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   int n = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) n = 1;
-  if (used < 32) cache[used++] = Key{kp, threads, smem, n};
+  if (used < 64) cache[used++] = Key{kp, threads, smem, n};
   return n;
 }
 

@@ -4,7 +4,8 @@
 
 cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16), softmax_full (config 2), nll (2048 x 32000 f16),
 rmsnorm (16384 x 3200 f16), rope (16384 x 32 x 100 f16), swiglu (4096 x 8640 f16),
-gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200 f16), qk / pv (2 sequences of config 5).
+gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200 f16), qk / pv (--batch sequences of config 5),
+train_step (one config-5 forward+backward over --batch sequences; only for the single-pass launch list).
 Inputs are larger than the 126 MB L2 so DRAM counters are meaningful.
 """
 from __future__ import annotations
@@ -53,6 +54,15 @@ def main():
         ga, up, dh = rnd(4096, 8640), rnd(4096, 8640), rnd(4096, 8640)
         h, dga, dup = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
         fn = lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup)
+    elif a.case == "train_step":
+        from . import dp, llama_step as LS
+        cfg = LS.LlamaShape.open_llama_3b()
+        P = LS.init_weights(cfg, torch.device("cuda"))
+        grads, _ = dp.alloc_bucketed_grads(P)
+        step = LS.TrainStep(cfg, P, a.batch)
+        tok = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
+        tgt = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
+        fn = lambda: step.forward_backward(tok, tgt, grads)
     elif a.case.startswith("gemm_") or a.case in ("qk", "pv"):
         from . import gemm_cases
         fn = gemm_cases.make(a.case, rnd, a.batch)
