@@ -6,7 +6,8 @@ replaced by its fused entry point.  It is host plumbing only: torch owns device 
 arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph, all stated:
   * the f32 probability tensor `out_lm_prob` and the arg-max (llama.rs:543,546) are not produced;
   * attention probabilities are recomputed from the saved scores in the backward instead of being kept
-    (one extra softmax pass per layer, 2.1 GB less live memory per layer at B = 8);
+    (the fused softmax forward+backward entry point yields them together with dS; 2.1 GB less live memory per
+    layer at B = 8);
   * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted.
 Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
 """
@@ -158,12 +159,12 @@ class TrainStep:
             # attention branch: x_mid = x_in + ctx Wo^T
             self._mm(dx, ctx, True, False, c=G["o"])
             dctx = self._mm(dx, Lw["o"], False, False)
-            p = ops.softmax_fwd(sc.view(B * S * H, S), mask)                         # recomputed probabilities
-            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False).view(T, D)       # P^T dctx
             dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True)                   # dctx V^T
-            del p, dctx
-            ds = ops.softmax_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
+            # one fused pass over (S, dP) yields the recomputed probabilities and dS together
+            p, ds = ops.softmax_fwd_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
             del dp, sc
+            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False).view(T, D)       # P^T dctx
+            del p, dctx
             dq = self._bmm(ds.view(B, S, H, S), k.view(B, S, H, hd), False, False, alpha)              # dS K
             dk = self._bmm(ds.view(B, S, H, S), q.view(B, S, H, hd), True, False, alpha)               # dS^T Q
             del ds
@@ -179,7 +180,7 @@ class TrainStep:
             ops.rmsnorm_bwd(x_in, Lw["pre_norm"], dn1, cfg.eps, dx=dx, dgamma=G["pre_norm"], beta_dx=1,
                             workspace=self.norm_ws)
             del dn1
-            self.launches += 12
+            self.launches += 11
             if on_layer_done is not None:
                 on_layer_done(li)
         ops.scatter_add_rows(dx, tokens, cfg.vocab, dtable=grads["embed"], status=self.status)
