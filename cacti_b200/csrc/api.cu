@@ -63,7 +63,7 @@ int cacti_b200_tune(const char* name, int value) {
   for (const Knob& k : knobs) {
     if (strcmp(k.name, name) == 0) {
       if (value < k.lo || value > k.hi || (k.lo == 32 && value % 32)) return CACTI_B200_ERR_INVALID_VALUE;
-      if (k.p == &g_gemm_bn && value != 0 && value != 128 && value != 256) return CACTI_B200_ERR_INVALID_VALUE;
+      if (k.p == &g_gemm_bn && value != 0 && value != 128 && value != 192 && value != 256) return CACTI_B200_ERR_INVALID_VALUE;
       *k.p = value;
       return CACTI_B200_OK;
     }

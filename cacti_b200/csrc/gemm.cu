@@ -120,7 +120,7 @@ template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, T* __restrict__ C, const GemmParams p) {
-  constexpr int STAGES = BN == 256 ? 4 : 6;
+  constexpr int STAGES = BN >= 192 ? 4 : 6;
   constexpr uint32_t A_BYTES = kBM * kBK * 2, B_BYTES = BN * kBK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -220,18 +220,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
         unsigned char* mybuf = cstage + (size_t)(warp - 2) * 8192;
         const bool scale = p.alpha != 1.f;
+        constexpr int TRIPS = (BN + 127) / 128;
 #pragma unroll 1
-        for (int c = 0; c < BN / 128; ++c) {
+        for (int c = 0; c < TRIPS; ++c) {
           const int col0 = tn * BN + c * 128;
           if (col0 >= p.N) break;               // warp-uniform
+          const int ncols = BN - c * 128 < 128 ? BN - c * 128 : 128;      // columns of this tile in this trip (128 or 64)
           uint32_t v[4][32];
 #pragma unroll
           for (int hh = 0; hh < 4; ++hh)
-            tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
+            if (hh * 32 < ncols)
+              tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
           // both staging buffers must have been read by the stores of the previous trip
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           tc_ld_wait();
-          if (c == BN / 128 - 1 || col0 + 128 >= p.N) {      // last trip of this tile: the accumulator is free
+          if (c == TRIPS - 1 || col0 + 128 >= p.N) {         // last trip of this tile: the accumulator is free
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty + acc);
@@ -240,6 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
+            if (hb * 64 >= ncols) break;
             unsigned char* buf = mybuf + hb * 4096;
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
@@ -260,7 +264,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) {
             tma_store_4d(&tmC, mybuf, col0, tm * kBM + q * 32, bj, bi);
-            if (col0 + 64 < p.N) tma_store_4d(&tmC, mybuf + 4096, col0 + 64, tm * kBM + q * 32, bj, bi);
+            if (col0 + 64 < p.N && ncols > 64) tma_store_4d(&tmC, mybuf + 4096, col0 + 64, tm * kBM + q * 32, bj, bi);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
@@ -449,7 +453,20 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     o->stride_outer = o->rows * cp * eff_nbi;
     ws_off += need;
   }
-  const int BN = g_gemm_bn ? g_gemm_bn : (N > 128 ? 256 : 128);
+  // Tile width: the persistent grid runs ceil(tiles / 148) waves; pick the width with the least wave-time
+  // (measured per-flop cost relative to the 256-wide tile: 1.08 for 192, 1.3 for 128).
+  int BN = g_gemm_bn;
+  if (!BN) {
+    if (N <= 128) BN = 128;
+    else {
+      double best = 1e300;
+      for (int bn : {256, 192, 128}) {
+        const long long tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * nbi * nbo;
+        const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * bn * (bn == 128 ? 1.3 : bn == 192 ? 1.08 : 1.0);
+        if (cost < best * 0.999) { best = cost; BN = bn; }
+      }
+    }
+  }
   CUtensorMap tmA, tmB;
   // K-major operand: stored [mn][k] -> box {64 k, tile mn}; MN-major: stored [k][mn] -> box {64 mn, 64 k}
   int rc = encode_operand(&tmA, A, nbi, nbo, 64, a_mn ? 64 : kBM, bf16);
@@ -483,7 +500,7 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
-  const int stages = BN == 256 ? 4 : 6;
+  const int stages = BN >= 192 ? 4 : 6;
   const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
 #define CB_GEMM(BN_, AM_, BM_)                                                                         \
@@ -496,6 +513,9 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   if (BN == 256) {
     if (!a_mn && !b_mn) CB_GEMM(256, false, false); else if (!a_mn && b_mn) CB_GEMM(256, false, true);
     else if (a_mn && !b_mn) CB_GEMM(256, true, false); else CB_GEMM(256, true, true);
+  } else if (BN == 192) {
+    if (!a_mn && !b_mn) CB_GEMM(192, false, false); else if (!a_mn && b_mn) CB_GEMM(192, false, true);
+    else if (a_mn && !b_mn) CB_GEMM(192, true, false); else CB_GEMM(192, true, true);
   } else {
     if (!a_mn && !b_mn) CB_GEMM(128, false, false); else if (!a_mn && b_mn) CB_GEMM(128, false, true);
     else if (a_mn && !b_mn) CB_GEMM(128, true, false); else CB_GEMM(128, true, true);
