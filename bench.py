@@ -212,6 +212,15 @@ def other_thunks(torch, ops, peak):
     sec = time_thunk(lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup), 20, 5, torch)
     report("swiglu_fwd_bwd[16384x8640,f16]", sec, 6 * 16384 * 8640 * 2, 1)
     del ga, up, dh, h, dga, dup
+    # K8 AdamW32 update of one gate-projection-sized parameter block x4 (f32 master/m/v, f16 gradient and copy)
+    n = 4 * 8640 * 3200
+    wm = torch.randn(n, device="cuda", generator=gen)
+    m1, m2 = torch.zeros_like(wm), torch.zeros_like(wm)
+    gg = rnd(n)
+    pc = torch.empty_like(gg)
+    sec = time_thunk(lambda: ops.adamw32_step(wm, m1, m2, gg, 5, param_out=pc), 10, 3, torch)
+    report("adamw32_step[110.6M params]", sec, 28 * n, 1)
+    del wm, m1, m2, gg, pc
     # G1 dense matmul: gate projection x[16384,3200] W[8640,3200]^T and its two adjoints (tensor roofline)
     tpeak = measured_tensor_peak()
     x, w, dyp = rnd(16384, 3200), rnd(8640, 3200, scale=0.02), rnd(16384, 8640)

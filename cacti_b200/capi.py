@@ -50,6 +50,7 @@ SIGNATURES = {
     "cacti_b200_scatter_add_rows": (_int, [_p, _p, _p, _int, _i64, _i64, _i64, _int, _int, _p, _sz, _p, _st]),
     "cacti_b200_accumulate": (_int, [_p, _p, _i64, _int, _st]),
     "cacti_b200_add": (_int, [_p, _p, _p, _i64, _int, _st]),
+    "cacti_b200_adamw32_step": (_int, [_p, _p, _p, _p, _p, _i64, _int, _int, _f32, _f32, _f32, _f32, _f32, _f32, _int, _st]),
     "cacti_b200_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "cacti_b200_gemm": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, C.POINTER(_f32),
                                C.POINTER(_f32), _int, _p, _sz, _st]),

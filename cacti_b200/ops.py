@@ -221,6 +221,14 @@ def add(a, b, out=None):
     return out
 
 
+# ---- K8 ---------------------------------------------------------------------------------------
+def adamw32_step(master, grad1_avg, grad2_avg, grad, iter_nr, lr=1e-3, wd=0.0, a1=0.1, a2=1e-3, eps=1e-8, grad_unscale=1.0,
+                 param_out=None):
+    check(lib().cacti_b200_adamw32_step(_ptr(master), _ptr(grad1_avg), _ptr(grad2_avg), _ptr(param_out), _ptr(grad),
+                                        master.numel(), _dt(grad), _dt(param_out) if param_out is not None else R_16F,
+                                        grad_unscale, lr, wd, a1, a2, eps, iter_nr, _stream()), "adamw32_step")
+
+
 # ---- G1 / G2 ------------------------------------------------------------------------------------
 import ctypes as _C
 

@@ -217,6 +217,22 @@ int cacti_b200_accumulate(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t n, i
 int cacti_b200_add(cacti_b200_dptr out, cacti_b200_dptr a, cacti_b200_dptr b, int64_t n, int dtype,
                    cacti_b200_stream stream);
 
+/* ---- K8 AdamW32 parameter update --------------------------------------------------------------
+ * Replaces the three in-place optimizer thunks AdamW32::step stages per parameter (src/librarium/adamw.rs:46-61):
+ * init_online_average_scale, init_online_average_square_scale and init_online_adamw_update32
+ * (src/op.rs:950-1023; Futhark bodies src/thunk/op.rs:3929-3934, :3991-3998, :4051-4055), plus the lossy cast that
+ * refreshes the 16-bit parameter from its f32 master.
+ *   m <- m + a1*(s*g - m);  v <- v + a2*((s*g)^2 - v);  w <- w - lr*(u*m/(sqrt(v) + e) + wd*w)
+ * u = unbias2/unbias1, e = eps*unbias2, unbias1 = 1-(1-a1)^iter_nr, unbias2 = sqrt(1-(1-a2)^iter_nr) (src/op.rs:985-1012).
+ * master, grad1_avg, grad2_avg: f32[n], updated in place; grad: grad_dtype[n]; param_out: param_dtype[n] or 0.
+ * a1, a2 are the reference's averaging rates (its defaults 0.1 and 0.001 correspond to beta1 0.9, beta2 0.999).
+ * iter_nr <= 0 is CACTI_B200_ERR_INVALID_VALUE (the reference panics).  Results are bit-identical to running the
+ * three f32 programs in sequence. */
+int cacti_b200_adamw32_step(cacti_b200_dptr master, cacti_b200_dptr grad1_avg, cacti_b200_dptr grad2_avg,
+                            cacti_b200_dptr param_out, cacti_b200_dptr grad, int64_t n, int grad_dtype, int param_dtype,
+                            float grad_unscale, float lr, float wd, float a1, float a2, float eps, int iter_nr,
+                            cacti_b200_stream stream);
+
 /* ---- G1 / G2 matmul and block matmul ------------------------------------------------------------
  * gemm replaces MatrixMulF16F32GpuThunkImpl -> cublas_gemm (src/thunk/op.rs:4413-4716,
  * cacti_gpu_cu_ffi/src/lib.rs:727-791); gemm_strided_batched replaces BlockMatrixMulF16F32GpuThunkImpl ->

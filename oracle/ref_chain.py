@@ -361,6 +361,41 @@ def ref_add(a, b):
     return a + b
 
 
+# --------------------------------------------------------------------------- AdamW32 (optimizer thunks)
+def ref_adamw32_step(w, m, v, g, iter_nr, lr=1e-3, wd=0.0, a1=0.1, a2=1e-3, eps=1e-8, grad_unscale=1.0, param_dtype=None):
+    """AdamW32::step (src/librarium/adamw.rs:46-61): three in-place f32 programs, evaluated in order.
+
+    m <- m + a1*(s*f32(g) - m)                      src/thunk/op.rs:3929-3934
+    v <- v + a2*((s*f32(g))*(s*f32(g)) - v)         :3991-3998
+    w <- w + (-lr)*(u*(m/(sqrt(v)+e)) + wd*w)       :4051-4055, scalars as in src/op.rs:985-1012
+    Returns new (w, m, v[, param]) as f32 arrays (param in param_dtype)."""
+    f = F32
+
+    def powi(a, b):          # f32 repeated squaring, as Rust's f32::powi (src/op.rs:990,1000)
+        r = f(1.0)
+        while True:
+            if b & 1:
+                r = f(r * a)
+            b //= 2
+            if b == 0:
+                return r
+            a = f(a * a)
+
+    a1f, a2f = f(a1), f(a2)
+    unbias1 = a1f if iter_nr == 1 else f(f(1.0) - powi(f(1.0) - a1f, iter_nr))
+    unbias2 = np.sqrt(a2f) if iter_nr == 1 else np.sqrt(f(f(1.0) - powi(f(1.0) - a2f, iter_nr)))
+    u = f(unbias2 / unbias1)
+    e = f(f(eps) * unbias2)
+    sg = f(grad_unscale) * g.astype(F32)
+    m2 = m + a1f * (sg - m)
+    v2 = v + a2f * (sg * sg - v)
+    w2 = w + f(-lr) * (u * (m2 / (np.sqrt(v2) + e)) + f(wd) * w)
+    out = (w2.astype(F32), m2.astype(F32), v2.astype(F32))
+    if param_dtype is not None:
+        out = out + (w2.astype(param_dtype),)
+    return out
+
+
 # --------------------------------------------------------------------------- A6/A7 GEMM
 def ref_gemm(a, b, ta=False, tb=False, alpha=1.0, beta=0.0, c=None):
     """C = T(alpha * op(A) op(B) + beta * C), fp64 accumulation then one rounding.
