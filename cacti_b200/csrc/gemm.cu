@@ -417,6 +417,7 @@ static size_t packed_bytes(long long rows, long long cols, long long nblk) {
 
 int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measurement knob)
 int g_gemm_group_m = 0;
+int g_gemm_sms = 0;   // 0: all 148
 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
@@ -499,7 +500,10 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   p.group_m = g_gemm_group_m > 0 ? g_gemm_group_m : 16;
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
-  const int grid = (int)(total < kNumSMs ? total : kNumSMs);
+  // g_gemm_sms < 148 leaves SMs free for a concurrent kernel (the gradient all-reduce): a persistent grid that
+  // cannot be fully resident would otherwise run its last CTAs as a second wave
+  const int sms = g_gemm_sms > 0 && g_gemm_sms < kNumSMs ? g_gemm_sms : kNumSMs;
+  const int grid = (int)(total < sms ? total : sms);
   const int stages = BN >= 192 ? 4 : 6;
   const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
