@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline workload (N = 1): BASELINE config 2 -- causal row softmax forward+backward on scores
+Headline workload (N = 1): benchmark config 2 -- causal row softmax forward+backward on scores
 [1, 32, 2048, 2048] fp16 (fp32 accumulation), one fused launch per step.  `value` is the algorithmic
 HBM GB/s of that launch with inputs resident in HBM; `e2e` is the same quantity measured through
 the C-ABI call with HOST buffers (pinned H2D of scores and dP, D2H of P and dScores inside the timed
@@ -147,7 +147,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3 * (ROWS / rows), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-        "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (BASELINE config 2)",
+        "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (benchmark config 2)",
                    "rows": ROWS, "cols": COLS},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{sample_heads} of 32 (batch, head) blocks = {rows} rows per step; "
@@ -173,7 +173,7 @@ def time_thunk(fn, launches, warmup, torch):
 
 
 def other_thunks(torch, ops, peak):
-    """Device-resident GB/s of the other fused thunks at their BASELINE shapes (explanatory, not the headline)."""
+    """Device-resident GB/s of the other fused thunks at their benchmark shapes (explanatory, not the headline)."""
     out = {}
     gen = torch.Generator(device="cuda").manual_seed(1)
 
@@ -253,7 +253,7 @@ def other_thunks(torch, ops, peak):
 
 
 def train_step_leg(torch, dist, rank, world, dev, steps):
-    """BASELINE config 5: one OpenLLaMA-3B-shaped forward+backward over 8 sequences of 2048 tokens, the sequences
+    """benchmark config 5: one OpenLLaMA-3B-shaped forward+backward over 8 sequences of 2048 tokens, the sequences
     split across the ranks (strong scaling), weight gradients summed with bucketed NCCL all-reduces that overlap
     the backward pass.  Random-init weights, synthetic token ids."""
     from cacti_b200 import dp, llama_step as LS, ops
@@ -305,7 +305,7 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item()
     ops.lib().cacti_b200_tune(b"gemm_sms", 0)
-    return {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (BASELINE config 5)",
+    return {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (benchmark config 5)",
             "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "scaling": "strong", "n_gpus": world,
             "sequences_per_gpu": count, "loss": float(loss.item()), "gpu_launches_per_step": step.launches,
             "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
@@ -432,7 +432,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 per GPU (BASELINE config 2)",
+            "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 per GPU (benchmark config 2)",
                        "rows": ROWS, "cols": COLS, "mask": "causal, applied in-kernel",
                        "l2": "working set 1.07 GB per step, far larger than the 126 MB L2; no flush needed"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -1,6 +1,6 @@
 """One OpenLLaMA-shaped training step (forward + backward) issued purely through the C ABI.
 
-This is the workload of BASELINE config 5: the op sequence of `Llama::apply` (src/librarium/llama.rs:420-548)
+This is the workload of benchmark config 5: the op sequence of `Llama::apply` (src/librarium/llama.rs:420-548)
 and of the adjoints the spine would stage for it (src/spine.rs:447-690), with each group of primitive thunks
 replaced by its fused entry point.  It is host plumbing only: torch owns device memory and streams, every
 arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph, all stated:

@@ -21,7 +21,7 @@ OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden_small.npz
 def inputs(case):
     """Seeded inputs of every golden case (shared with the tests)."""
     s = 1000 * case
-    if case == 1:      # RMSNorm f32, 8 rows of BASELINE config 1
+    if case == 1:      # RMSNorm f32, 8 rows of benchmark config 1
         return dict(x=R.normal(s + 0, (8, 3200)), gamma=R.normal(s + 1, (3200,), scale=0.02, shift=1.0),
                     dy=R.normal(s + 2, (8, 3200)), eps=1e-6)
     if case == 2:      # RMSNorm f16

@@ -1,4 +1,4 @@
-"""The composed training step (BASELINE config 5 at reduced depth/width) against the composed CPU oracle."""
+"""The composed training step (benchmark config 5 at reduced depth/width) against the composed CPU oracle."""
 import numpy as np
 import pytest
 import torch

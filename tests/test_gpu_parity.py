@@ -35,7 +35,7 @@ def test_rmsnorm_golden(cuda, case):
 
 
 def test_rmsnorm_config1_full(cuda):
-    """BASELINE config 1: [256 x 3200] fp32, gamma = 1 + 0.02 N(0,1), eps 1e-6, seed 0."""
+    """benchmark config 1: [256 x 3200] fp32, gamma = 1 + 0.02 N(0,1), eps 1e-6, seed 0."""
     x = R.normal(0, (256, 3200))
     gamma = R.normal(1, (3200,), scale=0.02, shift=1.0)
     dy = R.normal(2, (256, 3200))
@@ -177,7 +177,7 @@ def test_softmax_unaligned_accumulate_bf16_dead_rows(cuda):
 
 
 def test_softmax_config2_properties(cuda):
-    """BASELINE config 2 at full size [1,32,2048,2048] f16: size-independent properties + sampled rows."""
+    """benchmark config 2 at full size [1,32,2048,2048] f16: size-independent properties + sampled rows."""
     rows, cols = 32 * 2048, 2048
     gen = torch.Generator(device="cuda").manual_seed(0)
     s = (torch.randn(rows, cols, device="cuda", generator=gen) * 0.1).half()
@@ -369,7 +369,7 @@ def test_nll_out_of_range_target_sets_status(cuda):
 
 
 def test_nll_config3_properties(cuda):
-    """BASELINE config 3 at full size: [8192 x 32000] f16 logits ~ N(0, 2^2), int32 targets, mean loss."""
+    """benchmark config 3 at full size: [8192 x 32000] f16 logits ~ N(0, 2^2), int32 targets, mean loss."""
     rows, vocab = 8192, 32000
     gen = torch.Generator(device="cuda").manual_seed(0)
     lg = (torch.randn(rows, vocab, device="cuda", generator=gen) * 2).half()
@@ -454,7 +454,7 @@ def test_add_accumulate(cuda, dtype, n):
 
 # ------------------------------------------------------------------------------------------- config 4 at full size
 def test_config4_properties(cuda):
-    """BASELINE config 4: RoPE on [16384 x 32 x 100] f16 and SwiGLU on [16384 x 8640] f16."""
+    """benchmark config 4: RoPE on [16384 x 32 x 100] f16 and SwiGLU on [16384 x 8640] f16."""
     gen = torch.Generator(device="cuda").manual_seed(0)
     tokens, heads, hd, seq = 16384, 32, 100, 2048
     cos, sin = ops.rope_tables(seq, hd)
