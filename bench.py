@@ -281,7 +281,7 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
         # end to end: token ids come from pinned host memory, the loss goes back to the host
         tok.copy_(h_tok, non_blocking=True); tgt.copy_(h_tgt, non_blocking=True)
         loss = step.forward_backward(tok, tgt, grads, on_layer_done=red.reduce_bucket)
-        red.reduce_bucket(nl)
+        red.reduce_bucket(nl + 1)                      # the embedding gradient, complete last
         red.finish()
         if world > 1:
             dist.all_reduce(loss)

@@ -19,8 +19,10 @@ def shard_sequences(n_seq: int, world: int, rank: int):
 
 
 def alloc_bucketed_grads(params):
-    """Gradient tensors shaped like `params`; each layer's gradients are views of one flat buffer (a bucket),
-    and the non-layer parameters share a final bucket.  Returns (grads, buckets)."""
+    """Gradient tensors shaped like `params`; each layer's gradients are views of one flat buffer (a bucket).
+    The output head (`lm_head`, `head_norm`), whose gradients are the first to be complete in the backward pass,
+    gets bucket len(layers); the remaining parameters (the embedding, complete last) bucket len(layers) + 1.
+    Returns (grads, buckets)."""
     def carve(named):
         total = sum((t.numel() + 127) // 128 * 128 for _, t in named)
         first = named[0][1]
@@ -36,9 +38,13 @@ def alloc_bucketed_grads(params):
         g, flat = carve(list(L.items()))
         grads["layers"].append(g)
         buckets.append(flat)
-    g, flat = carve([(k, v) for k, v in params.items() if k != "layers"])
-    grads.update(g)
-    buckets.append(flat)
+    head_keys = [k for k in ("lm_head", "head_norm") if k in params]
+    rest_keys = [k for k in params if k != "layers" and k not in head_keys]
+    for keys in (head_keys, rest_keys):
+        if keys:
+            g, flat = carve([(k, params[k]) for k in keys])
+            grads.update(g)
+            buckets.append(flat)
     return grads, buckets
 
 

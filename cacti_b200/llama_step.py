@@ -74,7 +74,8 @@ def flat_params(P):
 class TrainStep:
     """Forward + backward over `batch` sequences of cfg.seq tokens.  Gradients are written (Apply mode) into
     `grads`, a structure shaped like the parameters; `on_layer_done(i)` is called after layer i's weight
-    gradients are complete (the hook a data-parallel reducer attaches to)."""
+    gradients are complete, and with i = cfg.layers as soon as the output head's gradients are (the hook a
+    data-parallel reducer attaches to; the embedding gradient is complete when the call returns)."""
 
     def __init__(self, cfg: LlamaShape, params, batch: int, loss_tokens: int | None = None):
         self.cfg, self.P, self.B = cfg, params, batch
@@ -140,6 +141,8 @@ class TrainStep:
         del dlogits
         dx, _ = ops.rmsnorm_bwd(x, P["head_norm"], dnf, cfg.eps, dgamma=grads["head_norm"], workspace=self.norm_ws)
         self.launches += 2
+        if on_layer_done is not None:
+            on_layer_done(cfg.layers)
         for li in range(cfg.layers - 1, -1, -1):
             Lw, G = P["layers"][li], grads["layers"][li]
             x_in, n1, q, k, v, sc, ctx, x_mid, n2, up, gate, h = saved.pop()

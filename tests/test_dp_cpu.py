@@ -17,7 +17,7 @@ rank = dist.get_rank()
 params = {"embed": torch.zeros(7, 5), "head_norm": torch.zeros(5),
           "layers": [{"q": torch.zeros(5, 5), "pre_norm": torch.zeros(5)} for _ in range(3)]}
 grads, buckets = dp.alloc_bucketed_grads(params)
-assert len(buckets) == 4
+assert len(buckets) == 5          # 3 layers, the output head, the rest
 red = dp.GradReducer(buckets)
 assert red.enabled
 for li in (2, 1, 0):                      # backward order
@@ -26,6 +26,7 @@ for li in (2, 1, 0):                      # backward order
     red.reduce_bucket(li)
 grads["embed"].fill_(float(rank)); grads["head_norm"].fill_(1.0)
 red.reduce_bucket(3)
+red.reduce_bucket(4)
 red.finish()
 for li in range(3):
     assert torch.all(grads["layers"][li]["q"] == 3.0 * (li + 1)), grads["layers"][li]["q"]
@@ -52,8 +53,12 @@ def test_shard_sequences_covers_everything():
 
 
 def test_bucketed_grads_are_views_of_the_buckets():
-    params = {"embed": torch.zeros(3, 4), "layers": [{"a": torch.zeros(2, 2), "b": torch.zeros(5)}]}
+    params = {"embed": torch.zeros(3, 4), "lm_head": torch.zeros(3, 4), "head_norm": torch.zeros(4),
+              "layers": [{"a": torch.zeros(2, 2), "b": torch.zeros(5)}]}
     grads, buckets = dp.alloc_bucketed_grads(params)
+    assert len(buckets) == 3                 # layer 0, output head, embedding
+    grads["lm_head"].fill_(1.0)
+    assert buckets[1].sum().item() == 12.0 and buckets[2].sum().item() == 0.0
     grads["layers"][0]["b"].fill_(2.0)
     assert buckets[0].sum().item() == 10.0 and grads["layers"][0]["a"].shape == (2, 2)
     assert dp.GradReducer(buckets).enabled is False        # no process group: a single-GPU run reduces nothing
