@@ -116,6 +116,129 @@ __device__ __forceinline__ void decode_tile(long long tile, long long tiles_per_
   tm = m0 + (in - tn * gm);
 }
 
+// Arrive on an mbarrier given by a shared::cluster address (this CTA's own barriers included).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+
+// Epilogue of one accumulator for one warp: TMEM lanes [q*32, q*32+32) x BN columns of accumulator `acc` become
+// rows row0 .. row0+31 of the output tile whose first column is tn * BN.  `tempty_addr` is the shared::cluster
+// address of the barrier that frees the accumulator: the warp arrives on it once, as soon as its last
+// tcgen05.ld has completed.
+template <typename T, int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap& tmC, T* __restrict__ C,
+                                              uint32_t tmem_base, int acc, int row0, int tn, int bj, int bi, int q, int lane,
+                                              unsigned char* mybuf, uint32_t tempty_addr) {
+  if (p.c_tma) {
+    // TMEM -> registers -> swizzled shared staging -> TMA store (clips rows/columns past M, N)
+    // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
+    const bool scale = p.alpha != 1.f;
+    constexpr int TRIPS = (BN + 127) / 128;
+#pragma unroll 1
+    for (int c = 0; c < TRIPS; ++c) {
+      const int col0 = tn * BN + c * 128;
+      if (col0 >= p.N) break;               // warp-uniform
+      const int ncols = BN - c * 128 < 128 ? BN - c * 128 : 128;      // columns of this tile in this trip (128 or 64)
+      uint32_t v[4][32];
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh)
+        if (hh * 32 < ncols)
+          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
+      // both staging buffers must have been read by the stores of the previous trip
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      tc_ld_wait();
+      if (c == TRIPS - 1 || col0 + 128 >= p.N) {         // last trip of this tile: the accumulator is free
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_addr);
+      } else {
+        __syncwarp();
+      }
+#pragma unroll
+      for (int hb = 0; hb < 2; ++hb) {
+        if (hb * 64 >= ncols) break;
+        unsigned char* buf = mybuf + hb * 4096;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float t8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float a = __uint_as_float(v[hb * 2 + hh][g * 8 + i]);
+              t8[i] = scale ? p.alpha * a : a;
+            }
+            const int chunk = hh * 4 + g;       // 16-byte chunk inside the 128-byte row
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pack<T>(t8);
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_4d(&tmC, mybuf, col0, row0, bj, bi);
+        if (col0 + 64 < p.N && ncols > 64) tma_store_4d(&tmC, mybuf + 4096, col0 + 64, row0, bj, bi);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    return;                                   // the accumulator was released inside the loop
+  }
+  const int row = row0 + lane;
+  T* crow = C + (long long)bi * p.c_stride_outer + (long long)bj * p.c_stride_inner + (long long)row * p.ldc;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    const int col0 = tn * BN + c * 32;
+    if (col0 >= p.N) break;               // warp-uniform
+    uint32_t v[32];
+    tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+    tc_ld_wait();
+    if (row < p.M) {
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = p.alpha * __uint_as_float(v[i]);
+      const int nvalid = p.N - col0 < 32 ? p.N - col0 : 32;
+      T* out = crow + col0;
+      if (p.beta != 0.f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i < nvalid) f[i] = fmaf(p.beta, Elem<T>::to_f32(out[i]), f[i]);
+      }
+      if (nvalid == 32 && p.c_align >= 16) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float t8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) t8[i] = f[g * 8 + i];
+          *reinterpret_cast<uint4*>(out + g * 8) = pack<T>(t8);
+        }
+      } else if (p.c_align >= 8) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (g * 4 + 4 <= nvalid) {
+            uint2 w;
+            if constexpr (std::is_same<T, __half>::value) {
+              __half2 a = __floats2half2_rn(f[g * 4], f[g * 4 + 1]), b = __floats2half2_rn(f[g * 4 + 2], f[g * 4 + 3]);
+              w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+            } else {
+              __nv_bfloat162 a = __floats2bfloat162_rn(f[g * 4], f[g * 4 + 1]), b = __floats2bfloat162_rn(f[g * 4 + 2], f[g * 4 + 3]);
+              w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+            }
+            *reinterpret_cast<uint2*>(out + g * 4) = w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) if (g * 4 + i < nvalid) out[g * 4 + i] = Elem<T>::from_f32(f[g * 4 + i]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i < nvalid) out[i] = Elem<T>::from_f32(f[i]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive_cluster(tempty_addr);
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -214,116 +337,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
       tc_fence_after();
-      const int row = tm * kBM + q * 32 + lane;
-      if (p.c_tma) {
-        // TMEM -> registers -> swizzled shared staging -> TMA store (clips rows/columns past M, N)
-        // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
-        unsigned char* mybuf = cstage + (size_t)(warp - 2) * 8192;
-        const bool scale = p.alpha != 1.f;
-        constexpr int TRIPS = (BN + 127) / 128;
-#pragma unroll 1
-        for (int c = 0; c < TRIPS; ++c) {
-          const int col0 = tn * BN + c * 128;
-          if (col0 >= p.N) break;               // warp-uniform
-          const int ncols = BN - c * 128 < 128 ? BN - c * 128 : 128;      // columns of this tile in this trip (128 or 64)
-          uint32_t v[4][32];
-#pragma unroll
-          for (int hh = 0; hh < 4; ++hh)
-            if (hh * 32 < ncols)
-              tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
-          // both staging buffers must have been read by the stores of the previous trip
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          tc_ld_wait();
-          if (c == TRIPS - 1 || col0 + 128 >= p.N) {         // last trip of this tile: the accumulator is free
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty + acc);
-          } else {
-            __syncwarp();
-          }
-#pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            if (hb * 64 >= ncols) break;
-            unsigned char* buf = mybuf + hb * 4096;
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                float t8[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float a = __uint_as_float(v[hb * 2 + hh][g * 8 + i]);
-                  t8[i] = scale ? p.alpha * a : a;
-                }
-                const int chunk = hh * 4 + g;       // 16-byte chunk inside the 128-byte row
-                *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pack<T>(t8);
-              }
-            }
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_4d(&tmC, mybuf, col0, tm * kBM + q * 32, bj, bi);
-            if (col0 + 64 < p.N && ncols > 64) tma_store_4d(&tmC, mybuf + 4096, col0 + 64, tm * kBM + q * 32, bj, bi);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-        }
-        continue;                               // tempty was released inside the loop
-      } else {
-      T* crow = C + (long long)bi * p.c_stride_outer + (long long)bj * p.c_stride_inner + (long long)row * p.ldc;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tn * BN + c * 32;
-        if (col0 >= p.N) break;               // warp-uniform
-        uint32_t v[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-        tc_ld_wait();
-        if (row < p.M) {
-          float f[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = p.alpha * __uint_as_float(v[i]);
-          const int nvalid = p.N - col0 < 32 ? p.N - col0 : 32;
-          T* out = crow + col0;
-          if (p.beta != 0.f) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (i < nvalid) f[i] = fmaf(p.beta, Elem<T>::to_f32(out[i]), f[i]);
-          }
-          if (nvalid == 32 && p.c_align >= 16) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float t8[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) t8[i] = f[g * 8 + i];
-              *reinterpret_cast<uint4*>(out + g * 8) = pack<T>(t8);
-            }
-          } else if (p.c_align >= 8) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (g * 4 + 4 <= nvalid) {
-                uint2 w;
-                if constexpr (std::is_same<T, __half>::value) {
-                  __half2 a = __floats2half2_rn(f[g * 4], f[g * 4 + 1]), b = __floats2half2_rn(f[g * 4 + 2], f[g * 4 + 3]);
-                  w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
-                } else {
-                  __nv_bfloat162 a = __floats2bfloat162_rn(f[g * 4], f[g * 4 + 1]), b = __floats2bfloat162_rn(f[g * 4 + 2], f[g * 4 + 3]);
-                  w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
-                }
-                *reinterpret_cast<uint2*>(out + g * 4) = w;
-              } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) if (g * 4 + i < nvalid) out[g * 4 + i] = Elem<T>::from_f32(f[g * 4 + i]);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (i < nvalid) out[i] = Elem<T>::from_f32(f[i]);
-          }
-        }
-      }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty + acc);
+      epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kBM + q * 32, tn, bj, bi, q, lane,
+                                  cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
     }
   }
 done:
@@ -334,6 +349,179 @@ done:
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- two-SM variant (cta_group::2) -------------------------------------------------------------------------
+// A cluster of two CTAs on one SM pair computes a 256 x 256 output tile.  Each CTA stages its own 128 rows of A
+// and one half (128 rows) of the B tile; the leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2 with
+// M = 256, which reads A from both CTAs, both halves of B, and accumulates rows 0..127 into the leader's TMEM and
+// rows 128..255 into the peer's.  Per flop each SM reads a third less shared memory and L2 than the
+// one-SM 128 x 256 tile.  Signalling:
+//   full[s]   (leader only) : 1 arrival (the leader's expect_tx for both CTAs' bytes); both CTAs' TMA loads
+//                             complete their bytes on it (the load's cta_group::2 form allows a peer barrier)
+//   empty[s]  (both CTAs)   : the leader's tcgen05.commit, multicast to both CTAs
+//   tfull[a]  (both CTAs)   : same, when an accumulator is complete
+//   tempty[a] (leader only) : 8 arrivals, one per epilogue warp of either CTA
+// No load uses cluster multicast.  Every wait is bounded; all threads of both CTAs meet on the cluster barrier
+// before TMEM is freed, and the producers wait for the last stage releases, so neither CTA exits while the other
+// can still signal into its shared memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, uint32_t bar_addr, int c0, int c1, int c2,
+                                                 int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {       // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((unsigned short)3)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum)
+      : "memory");
+}
+
+constexpr int kPairBM = 256, kPairBN = 256, kPairStages = 6;
+constexpr size_t kPairSmem = (size_t)kPairStages * (kBM * kBK * 2 + (kPairBN / 2) * kBK * 2) + 1024 + 1024 + 4 * 8192;
+
+template <typename T, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, T* __restrict__ C, const GemmParams p) {
+  constexpr int BN = kPairBN, HB = BN / 2, STAGES = kPairStages;
+  constexpr uint32_t A_BYTES = kBM * kBK * 2, B_BYTES = HB * kBK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const long long pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 8); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                         // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nkb = (p.K + kBK - 1) / kBK;
+  const long long tiles_per_block = (long long)p.tiles_m * p.tiles_n;
+  const long long total = tiles_per_block * p.nb_inner * p.nb_outer;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    int s = 0; unsigned ph = 0;
+    const int row_off = (int)rank * kBM, col_off = (int)rank * HB;
+    for (long long tile = pair; tile < total; tile += npairs) {
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
+      const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
+      const int m0 = tm * kPairBM + row_off, n0 = tn * BN + col_off;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+        unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
+        unsigned char* sb = sa + A_BYTES;
+        const uint32_t fb = map_to_rank(smem_u32(full + s), 0);
+        if (rank == 0) mbar_expect_tx(full + s, 2 * STAGE_BYTES);
+        if (!A_MN) tma_load_4d_pair(sa, &tmA, fb, kb * kBK, m0, aj, ai);
+        else {
+#pragma unroll
+          for (int h = 0; h < kBM / 64; ++h) tma_load_4d_pair(sa + h * 8192, &tmA, fb, m0 + h * 64, kb * kBK, aj, ai);
+        }
+        if (!B_MN) tma_load_4d_pair(sb, &tmB, fb, kb * kBK, n0, bjj, bii);
+        else {
+#pragma unroll
+          for (int h = 0; h < HB / 64; ++h) tma_load_4d_pair(sb + h * 8192, &tmB, fb, n0 + h * 64, kb * kBK, bjj, bii);
+        }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+    // the leader's last commits still arrive on this CTA's empty barriers: wait for them before leaving
+    for (int i = 0; i < STAGES; ++i) {
+      if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---------------- MMA issuer (leader CTA) ----------------
+    int s = 0; unsigned ph = 0;
+    long long local = 0;
+    for (long long tile = pair; tile < total; tile += npairs, ++local) {
+      const int acc = (int)(local & 1);
+      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4) {
+          const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
+          const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
+          tc_mma_f16_pair(tacc, da, db, p.idesc, (kb | k4) ? 1u : 0u);
+        }
+        tc_commit_pair(empty + s);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+      tc_commit_pair(tfull + acc);
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
+    const int q = warp & 3;
+    long long local = 0;
+    for (long long tile = pair; tile < total; tile += npairs, ++local) {
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
+      const int acc = (int)(local & 1);
+      if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
+      tc_fence_after();
+      epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kPairBM + (int)rank * kBM + q * 32, tn, bj, bi, q, lane,
+                           cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0));
+    }
+  }
+done:
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                         // both CTAs have finished reading TMEM and signalling each other
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
@@ -418,6 +606,7 @@ static size_t packed_bytes(long long rows, long long cols, long long nblk) {
 int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measurement knob)
 int g_gemm_group_m = 0;
 int g_gemm_sms = 0;   // 0: all 148
+int g_gemm_pair = 0;  // 1: 256-wide tiles run as two-SM (cta_group::2) 256 x 256 tiles
 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
@@ -468,21 +657,23 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
       }
     }
   }
+  const bool pair = g_gemm_pair != 0 && BN == kPairBN && M > kBM;
+  const int tile_m = pair ? kPairBM : kBM;
   CUtensorMap tmA, tmB;
   // K-major operand: stored [mn][k] -> box {64 k, tile mn}; MN-major: stored [k][mn] -> box {64 mn, 64 k}
   int rc = encode_operand(&tmA, A, nbi, nbo, 64, a_mn ? 64 : kBM, bf16);
   if (rc) return rc;
-  rc = encode_operand(&tmB, B, nbi, nbo, 64, b_mn ? 64 : BN, bf16);
+  rc = encode_operand(&tmB, B, nbi, nbo, 64, b_mn ? 64 : (pair ? BN / 2 : BN), bf16);
   if (rc) return rc;
   GemmParams p;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.nb_inner = nbi; p.nb_outer = nbo;
-  p.tiles_m = (int)((M + kBM - 1) / kBM); p.tiles_n = (int)((N + BN - 1) / BN);
+  p.tiles_m = (int)((M + tile_m - 1) / tile_m); p.tiles_n = (int)((N + BN - 1) / BN);
   p.a_j = A.has_j && nbi > 1; p.a_i = A.has_i && nbo > 1; p.b_j = B.has_j && nbi > 1; p.b_i = B.has_i && nbo > 1;
   p.ldc = ldc; p.c_stride_inner = csi; p.c_stride_outer = cso;
   p.alpha = alpha; p.beta = beta;
   p.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
-            ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
   const uint64_t all = c | (uint64_t)(ldc * 2) | (uint64_t)(nbi > 1 ? csi * 2 : 0) | (uint64_t)(nbo > 1 ? cso * 2 : 0);
   p.c_align = (all & 15) == 0 ? 16 : (all & 7) == 0 ? 8 : (all & 3) == 0 ? 4 : 2;
   // TMA store of C needs a 16-byte aligned base and strides, and no read-modify-write
@@ -497,7 +688,7 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     }
   }
   // about 16 m-tiles of A (2048 rows) stay hot in L2 while the B panels stream
-  p.group_m = g_gemm_group_m > 0 ? g_gemm_group_m : 16;
+  p.group_m = g_gemm_group_m > 0 ? g_gemm_group_m : (pair ? 8 : 16);
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
   // g_gemm_sms < 148 leaves SMs free for a concurrent kernel (the gradient all-reduce): a persistent grid that
@@ -507,6 +698,20 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   const int stages = BN >= 192 ? 4 : 6;
   const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
+  if (pair) {
+    const long long pairs = total < sms / 2 ? total : sms / 2;
+#define CB_GEMM2(AM_, BM_)                                                                             \
+  do {                                                                                                 \
+    auto kern = gemm_tc_pair_kernel<T, AM_, BM_>;                                                      \
+    static bool attr_set = false;                                                                      \
+    if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem); attr_set = true; } \
+    kern<<<(unsigned)(2 * pairs), kGemmThreads, kPairSmem, st>>>(tmA, tmB, tmC, C, p);                 \
+  } while (0)
+    if (!a_mn && !b_mn) CB_GEMM2(false, false); else if (!a_mn && b_mn) CB_GEMM2(false, true);
+    else if (a_mn && !b_mn) CB_GEMM2(true, false); else CB_GEMM2(true, true);
+#undef CB_GEMM2
+    return check_launch();
+  }
 #define CB_GEMM(BN_, AM_, BM_)                                                                         \
   do {                                                                                                 \
     auto kern = gemm_tc_kernel<T, BN_, AM_, BM_>;                                                      \

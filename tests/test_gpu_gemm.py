@@ -53,6 +53,60 @@ def test_gemm_views_and_bf16(cuda):
     assert_close(host(c), ref, "bfloat16", "bf16 gemm", floor_frac=1.0)
 
 
+@pytest.fixture
+def pair_tiles():
+    """Run 256-wide tiles as two-SM (cta_group::2) 256 x 256 tiles for the duration of a test."""
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"gemm_pair", 1) == capi.OK
+    assert L.cacti_b200_tune(b"gemm_bn", 256) == capi.OK
+    yield
+    L.cacti_b200_tune(b"gemm_pair", 0)
+    L.cacti_b200_tune(b"gemm_bn", 0)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 512, 320), (300, 260, 200), (129, 257, 65), (1000, 700, 1031 // 8 * 8),
+                                   (640, 3200, 3200), (4096 + 128, 1024, 512)])
+def test_gemm_pair_tiles(cuda, pair_tiles, ta, tb, m, n, k):
+    """Same cases as the dense test on the two-SM kernel: ragged M (a tile whose second CTA is partly or wholly
+    past M), ragged N and K, several tiles per CTA pair (both accumulators and every ring stage reused), TMA-store and
+    direct-store (beta = 1) epilogues."""
+    a = _stored(21, m, k, ta)
+    b = _stored(22, k, n, tb, 0.1)
+    c = ops.gemm(dev(a), dev(b), ta, tb, alpha=0.5)
+    ref = R.ref_gemm(a, b, ta, tb, alpha=0.5)
+    assert_close(host(c), ref, "float16", f"pair gemm {m}x{n}x{k} ta={ta} tb={tb}", floor_frac=1.0)
+    old = R.normal(23, (m, n), np.float16)
+    cacc = dev(old)
+    ops.gemm(dev(a), dev(b), ta, tb, alpha=0.5, beta=1.0, c=cacc)
+    assert_close(host(cacc), R.ref_gemm(a, b, ta, tb, alpha=0.5, beta=1.0, c=old), "float16", "pair gemm beta=1",
+                 floor_frac=1.0)
+    import ctypes as C
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0      # no bounded wait ran out
+
+
+def test_gemm_pair_tiles_match_single_sm(cuda):
+    """The two kernels accumulate every output element over k in the same order (one UMMA per 16 k), so their results
+    are bit-identical; block form with batch strides included."""
+    L = capi.lib()
+    a = dev(R.normal(31, (2, 384, 3, 128), np.float16))
+    b = dev(R.normal(32, (2, 384, 3, 128), np.float16))
+    x = dev(R.normal(33, (1536, 1024), np.float16))
+    w = dev(R.normal(34, (2048, 1024), np.float16, 0.05))
+    L.cacti_b200_tune(b"gemm_bn", 256)
+    try:
+        one = (ops.block_gemm(a, b, False, True), ops.gemm(x, w, False, True))
+        L.cacti_b200_tune(b"gemm_pair", 1)
+        two = (ops.block_gemm(a, b, False, True), ops.gemm(x, w, False, True))
+    finally:
+        L.cacti_b200_tune(b"gemm_pair", 0)
+        L.cacti_b200_tune(b"gemm_bn", 0)
+    for o, t in zip(one, two):
+        assert torch.equal(o, t)
+
+
 @pytest.mark.parametrize("hd", [100, 128, 64])
 def test_block_gemm_attention_shapes(cuda, hd):
     """The four block matmuls of one attention layer and their adjoints, layout [B, S, H, hd] / [B, Sq, H, Sk]."""
