@@ -47,6 +47,7 @@ struct GemmParams {
   int c_align;                            // bytes every output row chunk is aligned to: 16, 8, 4 or 2
   int c_tma;                              // 1: C is written with TMA stores from a swizzled staging buffer
   int group_m;                            // tile rasterisation: m-tiles per group (L2 reuse of the B panel)
+  int tri, diag;                          // triangular-structure hint (CACTI_B200_TRI_*) and its diagonal offset
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
@@ -114,6 +115,30 @@ __device__ __forceinline__ void decode_tile(long long tile, long long tiles_per_
   const int gm = p.tiles_m - m0 < p.group_m ? p.tiles_m - m0 : p.group_m;
   tn = in / gm;
   tm = m0 + (in - tn * gm);
+  // With a triangular hint the work of a tile depends on tm; rotating tm by the block index makes the tiles a
+  // CTA meets (tile, tile + grid, ...) run through all row positions instead of a few residues.
+  if (p.tri) tm = (tm + blk) % p.tiles_m;
+}
+
+// Triangular hints, per output tile whose rows are [row0, row0 + rows) and whose first column is col0.
+//   C_LOWER: only C[r, c] with c <= r + diag is wanted; a tile wholly beyond that is skipped (not written).
+//   A_LOWER: op(A)[r, k] == 0 for k > r + diag; k-blocks wholly beyond the tile's last row are skipped.
+//   A_UPPER: op(A)[r, k] == 0 for k < r - diag; k-blocks wholly before the tile's first row are skipped.
+// Skipped products are exact zeros, so the result is bit-identical to the full computation.
+__device__ __forceinline__ bool tile_skipped(const GemmParams& p, int row0, int rows, int col0) {
+  return p.tri == CACTI_B200_TRI_C_LOWER && (long long)col0 > (long long)row0 + rows - 1 + p.diag;
+}
+__device__ __forceinline__ void k_block_range(const GemmParams& p, int row0, int rows, int nkb, int& kb0, int& kb1) {
+  kb0 = 0; kb1 = nkb;
+  if (p.tri == CACTI_B200_TRI_A_LOWER) {
+    const long long last = (long long)row0 + rows - 1 + p.diag;
+    const long long e = last < 0 ? 1 : last / kBK + 1;
+    kb1 = e < 1 ? 1 : (e < nkb ? (int)e : nkb);
+  } else if (p.tri == CACTI_B200_TRI_A_UPPER) {
+    const long long first = (long long)row0 - p.diag;
+    const long long b = first < 0 ? 0 : first / kBK;
+    kb0 = b > nkb - 1 ? nkb - 1 : (int)b;
+  }
 }
 
 // Arrive on an mbarrier given by a shared::cluster address (this CTA's own barriers included).
@@ -284,7 +309,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
-      for (int kb = 0; kb < nkb; ++kb) {
+      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
+      int kb0, kb1;
+      k_block_range(p, tm * kBM, kBM, nkb, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
         unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
@@ -306,12 +334,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- MMA issuer ----------------
     int s = 0; unsigned ph = 0;
     long long local = 0;
-    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      int kb0 = 0, kb1 = nkb;
+      if (p.tri) {
+        int blk, tm, tn;
+        decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+        if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
+        k_block_range(p, tm * kBM, kBM, nkb, kb0, kb1);
+      }
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
-      for (int kb = 0; kb < nkb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
         tc_fence_after();
         const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
@@ -319,26 +354,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int k4 = 0; k4 < kBK / 16; ++k4) {
           const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
           const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
-          tc_mma_f16(tacc, da, db, p.idesc, (kb | k4) ? 1u : 0u);
+          tc_mma_f16(tacc, da, db, p.idesc, (kb > kb0 || k4) ? 1u : 0u);
         }
         tc_commit(empty + s);                 // stage free once these MMAs have read it
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       tc_commit(tfull + acc);                 // accumulator complete
+      ++local;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue ----------------
     const int q = warp & 3;                   // TMEM lane quarter this warp may read
     long long local = 0;
-    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kBM + q * 32, tn, bj, bi, q, lane,
-                                  cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
+                           cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
+      ++local;
     }
   }
 done:
@@ -450,7 +488,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
       const int m0 = tm * kPairBM + row_off, n0 = tn * BN + col_off;
-      for (int kb = 0; kb < nkb; ++kb) {
+      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
+      int kb0, kb1;
+      k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
         unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
@@ -478,12 +519,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- MMA issuer (leader CTA) ----------------
     int s = 0; unsigned ph = 0;
     long long local = 0;
-    for (long long tile = pair; tile < total; tile += npairs, ++local) {
+    for (long long tile = pair; tile < total; tile += npairs) {
+      int kb0 = 0, kb1 = nkb;
+      if (p.tri) {
+        int blk, tm, tn;
+        decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+        if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
+        k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
+      }
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
-      for (int kb = 0; kb < nkb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
         tc_fence_after();
         const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
@@ -491,26 +539,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int k4 = 0; k4 < kBK / 16; ++k4) {
           const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
           const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
-          tc_mma_f16_pair(tacc, da, db, p.idesc, (kb | k4) ? 1u : 0u);
+          tc_mma_f16_pair(tacc, da, db, p.idesc, (kb > kb0 || k4) ? 1u : 0u);
         }
         tc_commit_pair(empty + s);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       tc_commit_pair(tfull + acc);
+      ++local;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
     const int q = warp & 3;
     long long local = 0;
-    for (long long tile = pair; tile < total; tile += npairs, ++local) {
+    for (long long tile = pair; tile < total; tile += npairs) {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kPairBM + (int)rank * kBM + q * 32, tn, bj, bi, q, lane,
                            cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0));
+      ++local;
     }
   }
 done:
@@ -606,12 +657,12 @@ static size_t packed_bytes(long long rows, long long cols, long long nblk) {
 int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measurement knob)
 int g_gemm_group_m = 0;
 int g_gemm_sms = 0;   // 0: all 148
-int g_gemm_pair = 0;  // 1: 256-wide tiles run as two-SM (cta_group::2) 256 x 256 tiles
+int g_gemm_pair = 1;  // 1: 256-wide tiles may run as two-SM (cta_group::2) 256 x 256 tiles; 0: one-SM tiles only
 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
                     long long ldc, long long cso, long long csi, int nbi, int nbo, float alpha, float beta,
-                    uint64_t ws, size_t ws_bytes, cudaStream_t st) {
+                    int tri, long long diag, uint64_t ws, size_t ws_bytes, cudaStream_t st) {
   const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
   size_t ws_off = 0;
   // repack what TMA cannot address
@@ -643,9 +694,12 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     o->stride_outer = o->rows * cp * eff_nbi;
     ws_off += need;
   }
-  // Tile width: the persistent grid runs ceil(tiles / 148) waves; pick the width with the least wave-time
-  // (measured per-flop cost relative to the 256-wide tile: 1.08 for 192, 1.3 for 128).
+  // Tile shape: the persistent grid runs ceil(tiles / CTAs) waves; pick the shape with the least wave-time.
+  // Measured per-flop cost relative to the one-SM 256-wide tile: 1.08 for 192, 1.3 for 128, and 0.9 for the
+  // two-SM 256 x 256 tile (sustained, interleaved runs of the projection shapes: equal to +5 % with both
+  // operands K-major, +8 to +30 % when one of them is MN-major).
   int BN = g_gemm_bn;
+  bool pair = false;
   if (!BN) {
     if (N <= 128) BN = 128;
     else {
@@ -655,9 +709,15 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
         const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * bn * (bn == 128 ? 1.3 : bn == 192 ? 1.08 : 1.0);
         if (cost < best * 0.999) { best = cost; BN = bn; }
       }
+      if (g_gemm_pair && M > kBM) {
+        const long long tiles2 = ((M + kPairBM - 1) / kPairBM) * ((N + kPairBN - 1) / kPairBN) * nbi * nbo;
+        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * 0.9;
+        if (cost < best) { best = cost; BN = kPairBN; pair = true; }
+      }
     }
+  } else {
+    pair = g_gemm_pair != 0 && BN == kPairBN && M > kBM;
   }
-  const bool pair = g_gemm_pair != 0 && BN == kPairBN && M > kBM;
   const int tile_m = pair ? kPairBM : kBM;
   CUtensorMap tmA, tmB;
   // K-major operand: stored [mn][k] -> box {64 k, tile mn}; MN-major: stored [k][mn] -> box {64 mn, 64 k}
@@ -672,6 +732,7 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   p.a_j = A.has_j && nbi > 1; p.a_i = A.has_i && nbo > 1; p.b_j = B.has_j && nbi > 1; p.b_i = B.has_i && nbo > 1;
   p.ldc = ldc; p.c_stride_inner = csi; p.c_stride_outer = cso;
   p.alpha = alpha; p.beta = beta;
+  p.tri = tri; p.diag = (int)diag;
   p.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
             ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
   const uint64_t all = c | (uint64_t)(ldc * 2) | (uint64_t)(nbi > 1 ? csi * 2 : 0) | (uint64_t)(nbo > 1 ? cso * 2 : 0);
@@ -735,11 +796,13 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
 
 static int gemm_entry(uint64_t c, uint64_t a, uint64_t b, long long m, long long n, long long k, long long lda,
                       long long ldb, long long ldc, int ta, int tb, const float* alpha, const float* beta, int nbo, int nbi,
-                      long long sao, long long sai, long long sbo, long long sbi, long long sco, long long sci, int dtype,
-                      uint64_t ws, size_t ws_bytes, void* stream) {
+                      long long sao, long long sai, long long sbo, long long sbi, long long sco, long long sci, int tri,
+                      long long diag, int dtype, uint64_t ws, size_t ws_bytes, void* stream) {
   if (m < 0 || n < 0 || k < 0 || nbo < 0 || nbi < 0 || !alpha || !beta) return CACTI_B200_ERR_INVALID_VALUE;
   if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
   if ((ta & ~1) || (tb & ~1)) return CACTI_B200_ERR_INVALID_VALUE;
+  if (tri < CACTI_B200_TRI_NONE || tri > CACTI_B200_TRI_A_UPPER || diag > 0x3fffffffLL || diag < -0x3fffffffLL)
+    return CACTI_B200_ERR_INVALID_VALUE;
   if (dtype != CACTI_B200_R_16F && dtype != CACTI_B200_R_16BF) return CACTI_B200_ERR_DTYPE;
   if (m == 0 || n == 0 || nbo == 0 || nbi == 0) return CACTI_B200_OK;
   if (!c || (k > 0 && (!a || !b))) return CACTI_B200_ERR_INVALID_VALUE;
@@ -755,8 +818,8 @@ static int gemm_entry(uint64_t c, uint64_t a, uint64_t b, long long m, long long
   // A as [m][k] is K-major; as [k][m] it is MN-major.  B as [n][k] (tb = 1) is K-major; as [k][n] MN-major.
   const bool a_mn = ta != 0, b_mn = tb == 0;
   if (dtype == CACTI_B200_R_16F)
-    return gemm_run<__half>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, ws, ws_bytes, st);
-  return gemm_run<__nv_bfloat16>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, ws, ws_bytes, st);
+    return gemm_run<__half>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, ws, ws_bytes, st);
+  return gemm_run<__nv_bfloat16>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, ws, ws_bytes, st);
 }
 
 }  // namespace cb
@@ -777,8 +840,8 @@ size_t cacti_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t 
 int cacti_b200_gemm(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n, int64_t k, int64_t lda,
                     int64_t ldb, int64_t ldc, int trans_a, int trans_b, const float* alpha, const float* beta, int dtype,
                     cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream) {
-  return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, 1, 1, 0, 0, 0, 0, 0, 0, dtype,
-                        workspace, workspace_bytes, stream);
+  return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, 1, 1, 0, 0, 0, 0, 0, 0,
+                        CACTI_B200_TRI_NONE, 0, dtype, workspace, workspace_bytes, stream);
 }
 
 int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n,
@@ -790,6 +853,19 @@ int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_
   if (batch_outer > 0x7fffffffLL || batch_inner > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
   return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, (int)batch_outer, (int)batch_inner,
                         stride_a_outer, stride_a_inner, stride_b_outer, stride_b_inner, stride_c_outer, stride_c_inner,
-                        dtype, workspace, workspace_bytes, stream);
+                        CACTI_B200_TRI_NONE, 0, dtype, workspace, workspace_bytes, stream);
+}
+
+int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n,
+                                        int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                                        const float* alpha, const float* beta, int64_t batch_outer, int64_t batch_inner,
+                                        int64_t stride_a_outer, int64_t stride_a_inner, int64_t stride_b_outer,
+                                        int64_t stride_b_inner, int64_t stride_c_outer, int64_t stride_c_inner, int tri_mode,
+                                        int64_t diag, int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
+                                        cacti_b200_stream stream) {
+  if (batch_outer > 0x7fffffffLL || batch_inner > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
+  return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, (int)batch_outer, (int)batch_inner,
+                        stride_a_outer, stride_a_inner, stride_b_outer, stride_b_inner, stride_c_outer, stride_c_inner,
+                        tri_mode, diag, dtype, workspace, workspace_bytes, stream);
 }
 }

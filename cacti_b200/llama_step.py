@@ -8,7 +8,10 @@ arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph,
   * attention probabilities are recomputed from the saved scores in the backward instead of being kept
     (the fused softmax forward+backward entry point yields them together with dS; 2.1 GB less live memory per
     layer at B = 8);
-  * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted.
+  * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted;
+  * the six block matmuls of a layer carry the causal structure as a hint: score / dP tiles above the diagonal are
+    not computed (the masked softmax never reads them) and products with the exact zeros of P and dS are skipped;
+    every value that is used is bit-identical to the full product.
 Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
 """
 from __future__ import annotations
@@ -19,7 +22,7 @@ from dataclasses import dataclass
 import torch
 
 from . import ops
-from .capi import lib
+from .capi import TRI_A_LOWER, TRI_A_UPPER, TRI_C_LOWER, lib
 
 
 @dataclass
@@ -98,9 +101,9 @@ class TrainStep:
         self.launches += 1
         return ops.gemm(a, b, ta, tb, beta=beta, c=c)
 
-    def _bmm(self, a, b, ta, tb, alpha=1.0):
+    def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0):
         self.launches += 3
-        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws)
+        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws, tri=tri)
 
     def forward_backward(self, tokens, targets, grads, on_layer_done=None):
         cfg, P, B, T = self.cfg, self.P, self.B, self.T
@@ -116,9 +119,9 @@ class TrainStep:
             q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
             k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
             v = self._mm(n1, Lw["v"], False, True)
-            sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha)        # [B,S,H,S]
+            sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha, TRI_C_LOWER)   # [B,S,H,S]
             p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
-            ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False).view(T, D)
+            ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)
             del p
             x_mid = ops.add(x, self._mm(ctx, Lw["o"], False, True))
             n2 = ops.rmsnorm_fwd(x_mid, Lw["post_norm"], cfg.eps)
@@ -162,14 +165,14 @@ class TrainStep:
             # attention branch: x_mid = x_in + ctx Wo^T
             self._mm(dx, ctx, True, False, c=G["o"])
             dctx = self._mm(dx, Lw["o"], False, False)
-            dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True)                   # dctx V^T
+            dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True, tri=TRI_C_LOWER)  # dctx V^T
             # one fused pass over (S, dP) yields the recomputed probabilities and dS together
             p, ds = ops.softmax_fwd_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
             del dp, sc
-            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False).view(T, D)       # P^T dctx
+            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False, tri=TRI_A_UPPER).view(T, D)   # P^T dctx
             del p, dctx
-            dq = self._bmm(ds.view(B, S, H, S), k.view(B, S, H, hd), False, False, alpha)              # dS K
-            dk = self._bmm(ds.view(B, S, H, S), q.view(B, S, H, hd), True, False, alpha)               # dS^T Q
+            dq = self._bmm(ds.view(B, S, H, S), k.view(B, S, H, hd), False, False, alpha, TRI_A_LOWER)  # dS K
+            dk = self._bmm(ds.view(B, S, H, S), q.view(B, S, H, hd), True, False, alpha, TRI_A_UPPER)   # dS^T Q
             del ds
             dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
             dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)

@@ -253,9 +253,10 @@ def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
     return c
 
 
-def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None):
+def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None, tri=0, diag=0):
     """Block matmul on the reference's 4-d layout [nrow, blk_rows, ncol, blk_cols] (packed); an operand with
-    nrow or ncol equal to 1 is broadcast over that block dimension."""
+    nrow or ncol equal to 1 is broadcast over that block dimension.  `tri` is a CACTI_B200_TRI_* hint
+    (capi.TRI_C_LOWER / TRI_A_LOWER / TRI_A_UPPER) for the matmuls around a causal softmax."""
     nrow, ncol = max(a.shape[0], b.shape[0]), max(a.shape[2], b.shape[2])
     m = a.shape[3] if trans_a else a.shape[1]
     k = a.shape[1] if trans_a else a.shape[3]
@@ -273,6 +274,12 @@ def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, 
     if workspace is None:
         workspace = _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, nrow, ncol), a.device)
     al, be = _scalars(alpha, beta)
+    if tri:
+        check(lib().cacti_b200_gemm_strided_batched_tri(_ptr(c), _ptr(a), _ptr(b), m, n, k, lda, ldb, ldc, int(trans_a),
+                                                        int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci,
+                                                        int(tri), int(diag), _dt(a), _ptr(workspace), workspace.numel(),
+                                                        _stream()), "block_gemm_tri")
+        return c
     check(lib().cacti_b200_gemm_strided_batched(_ptr(c), _ptr(a), _ptr(b), m, n, k, lda, ldb, ldc, int(trans_a),
                                                 int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci, _dt(a),
                                                 _ptr(workspace), workspace.numel(), _stream()), "block_gemm")

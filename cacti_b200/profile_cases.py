@@ -22,7 +22,13 @@ def main():
     ap.add_argument("case")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--batch", type=int, default=2, help="sequences for the qk / pv cases")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
+                    help="set a cacti_b200_tune knob before running (repeatable), e.g. gemm_pair=1")
     a = ap.parse_args()
+    for kv in a.tune:
+        k, v = kv.split("=")
+        if ops.lib().cacti_b200_tune(k.encode(), int(v)) != 0:
+            raise SystemExit(f"tune {kv} rejected")
     gen = torch.Generator(device="cuda").manual_seed(0)
 
     def rnd(*shape, scale=1.0):

@@ -262,6 +262,33 @@ int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_
                                     int64_t stride_c_outer, int64_t stride_c_inner, int dtype,
                                     cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream);
 
+/* Block matmul with a triangular-structure hint, for the block matmuls around a causally masked softmax
+ * (src/librarium/llama.rs:501-507 and their adjoints, src/spine.rs:447-690).  The reference multiplies the full blocks:
+ * half of the scores it computes are overwritten by block_causal_attention_mask, and half of the products with the
+ * probabilities are products with exact zeros.  Same arguments and result as cacti_b200_gemm_strided_batched, except:
+ *   CACTI_B200_TRI_C_LOWER  only C[r, c] with c <= r + diag is wanted (scores, and the adjoint of the probabilities):
+ *                           output tiles wholly beyond the diagonal are neither computed nor written; elements of C
+ *                           with c > r + diag are unspecified after the call (the causal softmax never reads them).
+ *   CACTI_B200_TRI_A_LOWER  the caller guarantees op(A)[r, kk] == 0 for kk > r + diag (P V, dS K);
+ *   CACTI_B200_TRI_A_UPPER  the caller guarantees op(A)[r, kk] == 0 for kk < r - diag (P^T dO, dS^T Q):
+ *                           k-blocks that hold only such zeros are skipped.
+ * Where C is specified it is bit-identical to the unhinted call (the skipped products are exact zeros).
+ * r, c, kk are indices inside one block; diag = 0 for equal query and key lengths.
+ * This entry point has no counterpart in the reference, whose cuBLAS call cannot express the structure. */
+#define CACTI_B200_TRI_NONE 0
+#define CACTI_B200_TRI_C_LOWER 1
+#define CACTI_B200_TRI_A_LOWER 2
+#define CACTI_B200_TRI_A_UPPER 3
+int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b,
+                                        int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                                        int trans_a, int trans_b, const float* alpha, const float* beta,
+                                        int64_t batch_outer, int64_t batch_inner,
+                                        int64_t stride_a_outer, int64_t stride_a_inner,
+                                        int64_t stride_b_outer, int64_t stride_b_inner,
+                                        int64_t stride_c_outer, int64_t stride_c_inner, int tri_mode, int64_t diag,
+                                        int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
+                                        cacti_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

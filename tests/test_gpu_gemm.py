@@ -55,12 +55,11 @@ def test_gemm_views_and_bf16(cuda):
 
 @pytest.fixture
 def pair_tiles():
-    """Run 256-wide tiles as two-SM (cta_group::2) 256 x 256 tiles for the duration of a test."""
+    """Force 256-wide tiles, which run as two-SM (cta_group::2) 256 x 256 tiles, for the duration of a test."""
     L = capi.lib()
     assert L.cacti_b200_tune(b"gemm_pair", 1) == capi.OK
     assert L.cacti_b200_tune(b"gemm_bn", 256) == capi.OK
     yield
-    L.cacti_b200_tune(b"gemm_pair", 0)
     L.cacti_b200_tune(b"gemm_bn", 0)
 
 
@@ -87,6 +86,21 @@ def test_gemm_pair_tiles(cuda, pair_tiles, ta, tb, m, n, k):
     assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0      # no bounded wait ran out
 
 
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 320), (300, 260, 200), (640, 3200, 3200)])
+def test_gemm_single_sm_tiles(cuda, ta, tb, m, n, k):
+    """The one-SM kernel on shapes the automatic choice now gives to the two-SM one."""
+    L = capi.lib()
+    a = _stored(41, m, k, ta)
+    b = _stored(42, k, n, tb, 0.1)
+    L.cacti_b200_tune(b"gemm_pair", 0)
+    try:
+        c = ops.gemm(dev(a), dev(b), ta, tb, alpha=0.5)
+    finally:
+        L.cacti_b200_tune(b"gemm_pair", 1)
+    assert_close(host(c), R.ref_gemm(a, b, ta, tb, alpha=0.5), "float16", f"1-SM gemm {m}x{n}x{k}", floor_frac=1.0)
+
+
 def test_gemm_pair_tiles_match_single_sm(cuda):
     """The two kernels accumulate every output element over k in the same order (one UMMA per 16 k), so their results
     are bit-identical; block form with batch strides included."""
@@ -97,11 +111,12 @@ def test_gemm_pair_tiles_match_single_sm(cuda):
     w = dev(R.normal(34, (2048, 1024), np.float16, 0.05))
     L.cacti_b200_tune(b"gemm_bn", 256)
     try:
+        L.cacti_b200_tune(b"gemm_pair", 0)
         one = (ops.block_gemm(a, b, False, True), ops.gemm(x, w, False, True))
         L.cacti_b200_tune(b"gemm_pair", 1)
         two = (ops.block_gemm(a, b, False, True), ops.gemm(x, w, False, True))
     finally:
-        L.cacti_b200_tune(b"gemm_pair", 0)
+        L.cacti_b200_tune(b"gemm_pair", 1)
         L.cacti_b200_tune(b"gemm_bn", 0)
     for o, t in zip(one, two):
         assert torch.equal(o, t)
@@ -132,6 +147,41 @@ def test_block_gemm_attention_shapes(cuda, hd):
     assert_close(host(dq), R.ref_block_gemm(ds, k, False, False, alpha=alpha), "float16", "dS K", floor_frac=1.0)
     dk = ops.block_gemm(dev(ds), dev(q), True, False, alpha=alpha)                # dK = alpha dS^T Q
     assert_close(host(dk), R.ref_block_gemm(ds, q, True, False, alpha=alpha), "float16", "dS^T Q", floor_frac=1.0)
+
+
+@pytest.mark.parametrize("hd,s,diag", [(100, 512, 0), (128, 640, 0), (64, 384, 70), (100, 300, -33)])
+def test_block_gemm_triangular_hints(cuda, hd, s, diag):
+    """The hinted block matmuls around a causal softmax equal the unhinted ones bit for bit wherever the result is
+    specified: C_LOWER on the wanted triangle, A_LOWER / A_UPPER everywhere (the skipped products are exact zeros)."""
+    bsz, h = 2, 3
+    q = dev(R.normal(50, (bsz, s, h, hd), np.float16))
+    k = dev(R.normal(51, (bsz, s, h, hd), np.float16))
+    v = dev(R.normal(52, (bsz, s, h, hd), np.float16))
+    do = dev(R.normal(53, (bsz, s, h, hd), np.float16))
+    r = torch.arange(s, device="cuda")
+    wanted = (r[None, :] <= r[:, None] + diag)[None, :, None, :]            # [1, Sq, 1, Sk]: c <= r + diag
+    # scores = Q K^T and dP = dO V^T: only the wanted triangle is specified
+    for a, b in ((q, k), (do, v)):
+        full = ops.block_gemm(a, b, False, True, alpha=0.1)
+        c = torch.full_like(full, 7.0)
+        ops.block_gemm(a, b, False, True, alpha=0.1, c=c, tri=capi.TRI_C_LOWER, diag=diag)
+        assert torch.equal(torch.where(wanted, c, 0), torch.where(wanted, full, 0))
+    # a tile wholly beyond the diagonal is left untouched (not a promise of the interface, but it is where the
+    # saving comes from: fails if the hint were ignored)
+    if s >= 512 and diag == 0:
+        assert torch.all(c[:, :128, :, 256:] == 7.0)
+    p_low = torch.where(wanted, dev(R.normal(54, (bsz, s, h, s), np.float16, 0.05)), 0)    # zero for c > r + diag
+    for b_op in (v, k):                                                                      # P V and dS K
+        assert torch.equal(ops.block_gemm(p_low, b_op, False, False, tri=capi.TRI_A_LOWER, diag=diag),
+                           ops.block_gemm(p_low, b_op, False, False))
+    # P^T dO and dS^T Q: op(A)[r = key, kk = query] is zero for kk < r - diag
+    for b_op in (do, q):
+        assert torch.equal(ops.block_gemm(p_low, b_op, True, False, tri=capi.TRI_A_UPPER, diag=diag),
+                           ops.block_gemm(p_low, b_op, True, False))
+    import ctypes as C
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
 
 
 def test_block_gemm_broadcast_and_accumulate(cuda):
