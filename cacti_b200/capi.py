@@ -17,7 +17,7 @@ HEADER = os.path.join(HERE, "..", "include", "cacti_b200.h")
 OK, ERR_INVALID_VALUE, ERR_DTYPE, ERR_WORKSPACE, ERR_LAUNCH, ERR_SHAPE, ERR_INDEX_RANGE, ERR_NO_DEVICE = range(8)
 ERR_SCRATCH_LIMIT = 8
 R_32F, R_16F, R_16BF, R_32I, R_16U = 0, 2, 14, 10, 22
-MASK_NONE, MASK_CAUSAL = 0, 1
+MASK_NONE, MASK_CAUSAL, MASK_CAUSAL_TRIM = 0, 1, 2
 
 _p, _i64, _int, _f32, _sz, _st = C.c_uint64, C.c_int64, C.c_int, C.c_float, C.c_size_t, C.c_void_p
 

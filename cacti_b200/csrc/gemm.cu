@@ -695,23 +695,25 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     ws_off += need;
   }
   // Tile shape: the persistent grid runs ceil(tiles / CTAs) waves; pick the shape with the least wave-time.
-  // Measured per-flop cost relative to the one-SM 256-wide tile: 1.08 for 192, 1.3 for 128, and 0.9 for the
-  // two-SM 256 x 256 tile (sustained, interleaved runs of the projection shapes: equal to +5 % with both
-  // operands K-major, +8 to +30 % when one of them is MN-major).
+  // Per-flop cost relative to the one-SM 256-wide tile with K-major operands, from sustained interleaved runs of
+  // the projection shapes: 1.08 for 192-wide and 1.3 for 128-wide tiles; one-SM tiles with an MN-major operand
+  // 1.25 (their shared-memory reads conflict more); the two-SM 256 x 256 tile 0.95, or 1.05 with an MN-major operand.
   int BN = g_gemm_bn;
   bool pair = false;
   if (!BN) {
     if (N <= 128) BN = 128;
     else {
+      const bool mn = a_mn || b_mn;
       double best = 1e300;
       for (int bn : {256, 192, 128}) {
         const long long tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * nbi * nbo;
-        const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * bn * (bn == 128 ? 1.3 : bn == 192 ? 1.08 : 1.0);
+        const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * bn * (bn == 128 ? 1.3 : bn == 192 ? 1.08 : 1.0) *
+                            (mn ? 1.25 : 1.0);
         if (cost < best * 0.999) { best = cost; BN = bn; }
       }
       if (g_gemm_pair && M > kBM) {
         const long long tiles2 = ((M + kPairBM - 1) / kPairBM) * ((N + kPairBN - 1) / kPairBN) * nbi * nbo;
-        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * 0.9;
+        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * (mn ? 1.05 : 0.95);
         if (cost < best) { best = cost; BN = kPairBN; pair = true; }
       }
     }

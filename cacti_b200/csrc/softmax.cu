@@ -20,10 +20,20 @@ int g_softmax_waves = 1;       // grid = SMs * resident CTAs * this (capped by t
 
 __device__ __forceinline__ int active_cols(int64_t row, int cols, int mask_mode,
                                            int64_t q_div, int64_t q_mod, int64_t q_off) {
-  if (mask_mode != CACTI_B200_MASK_CAUSAL) return cols;
+  if (mask_mode == CACTI_B200_MASK_NONE) return cols;
   int64_t q = (row / q_div) % q_mod + q_off;
   if (q < 0) return 0;
   return (q + 1 < (int64_t)cols) ? (int)(q + 1) : cols;
+}
+
+// Columns of a row that get written.  CACTI_B200_MASK_CAUSAL_TRIM zero-fills the masked tail only as far as a
+// consumer with a CACTI_B200_TRI_A_* hint can read (tiles of at most 256 rows, k-blocks of 64): up to the next
+// multiple of 256 past q_pos when q_off is a multiple of 256, else 320 columns past it.
+__device__ __forceinline__ int written_cols(int active, int cols, int mask_mode, int64_t q_off) {
+  if (mask_mode != CACTI_B200_MASK_CAUSAL_TRIM || active <= 0) return cols;
+  const int64_t q = (int64_t)active - 1;
+  const int64_t b = (q_off & 255) == 0 ? (q & ~(int64_t)255) + 256 : ((q + 320 + 7) & ~(int64_t)7);
+  return b < (int64_t)cols ? (int)b : cols;
 }
 
 // -inf / 0 fill of the masked tail of the one vector that straddles the causal boundary, so that the
@@ -137,10 +147,11 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
     T* prow = FWD ? P + row * cols : nullptr;
     T* drow = BWD ? dS + row * cols : nullptr;
     // pass 3: outputs (explicitly rounded ops: every entry point produces the same bits)
+    const int wcols = written_cols(cur_active, cols, mask_mode, q_off);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cols) {
+      if (col0 < wcols) {
         float y[VEC], d[VEC];
         if (col0 < cur_active) {
           float a[VEC], gv[VEC];
@@ -177,10 +188,11 @@ softmax_rows_generic_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __re
   __shared__ float sm[33];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int64_t active = cols;
-    if (mask_mode == CACTI_B200_MASK_CAUSAL) {
+    if (mask_mode != CACTI_B200_MASK_NONE) {
       int64_t q = (row / q_div) % q_mod + q_off;
       active = q < 0 ? 0 : (q + 1 < cols ? q + 1 : cols);
     }
+    const int64_t wcols = written_cols((int)active, (int)cols, mask_mode, q_off);
     const T* srow = S + row * cols;
     float m = -INFINITY;
     for (int64_t j = threadIdx.x; j < active; j += blockDim.x) m = fmaxf(m, Elem<T>::to_f32(srow[j]));
@@ -195,7 +207,7 @@ softmax_rows_generic_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __re
     if (BWD) cg = block_reduce<SumOp>(cg, sm);
     const float rz = 1.f / z, c = cg * rz;
     const float fill = active <= 0 ? __int_as_float(0x7fc00000) : 0.f;
-    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+    for (int64_t j = threadIdx.x; j < wcols; j += blockDim.x) {
       float y = fill, d = fill;
       if (j < active) {
         const float ex = exp_for<T>(Elem<T>::to_f32(srow[j]) - m);
@@ -258,8 +270,8 @@ static int softmax_entry(bool fwd, bool bwd, uint64_t p, uint64_t ds, uint64_t s
                          int64_t cols, int mask_mode, int64_t q_div, int64_t q_mod, int64_t q_off, int dtype,
                          int beta, void* stream) {
   if (rows < 0 || cols < 0 || cols > 0x7fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
-  if (mask_mode != CACTI_B200_MASK_NONE && mask_mode != CACTI_B200_MASK_CAUSAL) return CACTI_B200_ERR_INVALID_VALUE;
-  if (mask_mode == CACTI_B200_MASK_CAUSAL && (q_div <= 0 || q_mod <= 0)) return CACTI_B200_ERR_INVALID_VALUE;
+  if (mask_mode < CACTI_B200_MASK_NONE || mask_mode > CACTI_B200_MASK_CAUSAL_TRIM) return CACTI_B200_ERR_INVALID_VALUE;
+  if (mask_mode != CACTI_B200_MASK_NONE && (q_div <= 0 || q_mod <= 0)) return CACTI_B200_ERR_INVALID_VALUE;
   if (beta != 0 && beta != 1) return CACTI_B200_ERR_INVALID_VALUE;
   if (rows == 0 || cols == 0) return CACTI_B200_OK;
   if (!s || (fwd && !p) || (bwd && (!ds || !dp))) return CACTI_B200_ERR_INVALID_VALUE;

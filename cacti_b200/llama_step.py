@@ -11,7 +11,8 @@ arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph,
   * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted;
   * the six block matmuls of a layer carry the causal structure as a hint: score / dP tiles above the diagonal are
     not computed (the masked softmax never reads them) and products with the exact zeros of P and dS are skipped;
-    every value that is used is bit-identical to the full product.
+    every value that is used is bit-identical to the full product.  The softmax zero-fills the masked tails of P
+    and dS only as far as those matmuls read (CACTI_B200_MASK_CAUSAL_TRIM).
 Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
 """
 from __future__ import annotations
@@ -109,7 +110,9 @@ class TrainStep:
         cfg, P, B, T = self.cfg, self.P, self.B, self.T
         S, H, hd, D = cfg.seq, cfg.heads, cfg.head_dim, cfg.d_model
         alpha = 1.0 / math.sqrt(hd)
-        mask = (H, S, 0)                                  # scores [B, S, H, S]: q_pos = (row / H) % S
+        # scores [B, S, H, S]: q_pos = (row / H) % S; P and dS feed only hinted block matmuls, so their masked
+        # tails are zero-filled just as far as those can read
+        mask = (H, S, 0, True)
         self.launches = 0
         x, _ = ops.gather_rows(P["embed"], tokens, status=self.status)
         self.launches += 1

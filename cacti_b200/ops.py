@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import capi
-from .capi import MASK_CAUSAL, MASK_NONE, R_16BF, R_16F, R_16U, R_32F, R_32I, check, lib
+from .capi import MASK_CAUSAL, MASK_CAUSAL_TRIM, MASK_NONE, R_16BF, R_16F, R_16U, R_32F, R_32I, check, lib
 
 _DT = {torch.float32: R_32F, torch.float16: R_16F, torch.bfloat16: R_16BF}
 _IDX = {torch.int32: R_32I, torch.uint16: R_16U, torch.int16: R_16U}
@@ -77,11 +77,11 @@ def rmsnorm_fwd_bwd(x, gamma, dy, eps, y=None, dx=None, dgamma=None, beta_dx=0, 
 
 # ---- K2 ---------------------------------------------------------------------------------------
 def _mask_args(mask):
-    """mask: None or (q_div, q_mod, q_off)."""
+    """mask: None, (q_div, q_mod, q_off) or (q_div, q_mod, q_off, trim); trim selects CACTI_B200_MASK_CAUSAL_TRIM."""
     if mask is None:
         return MASK_NONE, 1, 1, 0
-    q_div, q_mod, q_off = mask
-    return MASK_CAUSAL, q_div, q_mod, q_off
+    q_div, q_mod, q_off = mask[:3]
+    return (MASK_CAUSAL_TRIM if len(mask) > 3 and mask[3] else MASK_CAUSAL), q_div, q_mod, q_off
 
 
 def softmax_fwd(s, mask=None, p=None):

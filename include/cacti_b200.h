@@ -64,7 +64,12 @@ enum {
 /* mask_mode of the row softmax */
 enum {
   CACTI_B200_MASK_NONE   = 0,
-  CACTI_B200_MASK_CAUSAL = 1   /* column c of row r is masked when c > q_pos(r) */
+  CACTI_B200_MASK_CAUSAL = 1,  /* column c of row r is masked when c > q_pos(r) */
+  /* Same values as CACTI_B200_MASK_CAUSAL, but the zero fill of the masked outputs stops at column
+   * B(q_pos) = (q_pos rounded down to a multiple of 256) + 256 when q_off is a multiple of 256, else q_pos + 320;
+   * columns at or beyond B are left untouched.  For outputs whose only consumers are block matmuls with a
+   * CACTI_B200_TRI_A_* hint (diag = q_off), which read nothing at or beyond B.  No counterpart in the reference. */
+  CACTI_B200_MASK_CAUSAL_TRIM = 2
 };
 
 int         cacti_b200_version(void);               /* 10000*major + 100*minor + patch */
@@ -271,7 +276,9 @@ int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_
  *                           with c > r + diag are unspecified after the call (the causal softmax never reads them).
  *   CACTI_B200_TRI_A_LOWER  the caller guarantees op(A)[r, kk] == 0 for kk > r + diag (P V, dS K);
  *   CACTI_B200_TRI_A_UPPER  the caller guarantees op(A)[r, kk] == 0 for kk < r - diag (P^T dO, dS^T Q):
- *                           k-blocks that hold only such zeros are skipped.
+ *                           k-blocks that hold only such zeros are skipped.  Of the stored matrix (P or dS, row =
+ *                           query q, column = key) nothing is read at or beyond column B(q + diag) as defined for
+ *                           CACTI_B200_MASK_CAUSAL_TRIM, so that region need not hold zeros, or anything.
  * Where C is specified it is bit-identical to the unhinted call (the skipped products are exact zeros).
  * r, c, kk are indices inside one block; diag = 0 for equal query and key lengths.
  * This entry point has no counterpart in the reference, whose cuBLAS call cannot express the structure. */

@@ -184,6 +184,29 @@ def test_block_gemm_triangular_hints(cuda, hd, s, diag):
     assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
 
 
+@pytest.mark.parametrize("hd,s,q_off", [(100, 512, 0), (128, 768, 256), (64, 600, 77)])
+def test_trimmed_softmax_feeds_hinted_block_gemms(cuda, hd, s, q_off):
+    """P and dS from the trimmed-fill softmax (garbage left beyond the fill bound) through the hinted block matmuls
+    equal the fully zero-filled, unhinted chain bit for bit."""
+    bsz, h = 2, 3
+    sc = dev(R.normal(60, (bsz, s, h, s), np.float16, 0.5))
+    dp = dev(R.normal(61, (bsz, s, h, s), np.float16))
+    v = dev(R.normal(62, (bsz, s, h, hd), np.float16))
+    do = dev(R.normal(63, (bsz, s, h, hd), np.float16))
+    mask = (h, s, q_off)
+    p_ref, ds_ref = ops.softmax_fwd_bwd(sc.view(-1, s), dp.view(-1, s), mask)
+    p = torch.full_like(p_ref, float("nan"))
+    ds = torch.full_like(p_ref, float("nan"))
+    ops.softmax_fwd_bwd(sc.view(-1, s), dp.view(-1, s), mask + (True,), p=p, ds=ds)
+    p4, ds4, pr4, dsr4 = (t.view(bsz, s, h, s) for t in (p, ds, p_ref, ds_ref))
+    assert torch.equal(ops.block_gemm(p4, v, False, False, tri=capi.TRI_A_LOWER, diag=q_off), ops.block_gemm(pr4, v, False, False))
+    assert torch.equal(ops.block_gemm(ds4, v, False, False, alpha=0.1, tri=capi.TRI_A_LOWER, diag=q_off),
+                       ops.block_gemm(dsr4, v, False, False, alpha=0.1))
+    assert torch.equal(ops.block_gemm(p4, do, True, False, tri=capi.TRI_A_UPPER, diag=q_off), ops.block_gemm(pr4, do, True, False))
+    assert torch.equal(ops.block_gemm(ds4, do, True, False, alpha=0.1, tri=capi.TRI_A_UPPER, diag=q_off),
+                       ops.block_gemm(dsr4, do, True, False, alpha=0.1))
+
+
 def test_block_gemm_broadcast_and_accumulate(cuda):
     a = R.normal(20, (3, 64, 2, 40), np.float16)
     b1 = R.normal(21, (1, 40, 2, 24), np.float16)      # broadcast over block rows

@@ -151,6 +151,33 @@ def test_softmax_shapes(cuda, dtype, rows, cols, mask):
     assert torch.equal(ops.softmax_bwd(dev(s), dev(dp), mask), ds)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,cols,mask", [(64, 256, (1, 64, 0)), (600, 1024, (1, 600, 0)), (48, 2048, (4, 12, 512)),
+                                            (40, 1000, (2, 20, 77)), (9, 3001, (1, 9, 1000)), (8, 64, (1, 8, -3))])
+def test_softmax_trimmed_zero_fill(cuda, dtype, rows, cols, mask):
+    """CACTI_B200_MASK_CAUSAL_TRIM: the same values as the causal mode up to column B(q_pos), nothing written beyond."""
+    s = dev(R.normal(34, (rows, cols), dtype, 0.5))
+    dp = dev(R.normal(35, (rows, cols), dtype))
+    p_full, ds_full = ops.softmax_fwd_bwd(s, dp, mask)
+    p = torch.full_like(s, 7.0)
+    ds = torch.full_like(s, 7.0)
+    ops.softmax_fwd_bwd(s, dp, mask + (True,), p=p, ds=ds)
+    q_div, q_mod, q_off = mask
+    q = (torch.arange(rows, device="cuda") // q_div) % q_mod + q_off
+    bound = torch.where(torch.tensor(q_off % 256 == 0, device="cuda"), q // 256 * 256 + 256, (q + 320 + 7) // 8 * 8)
+    bound = torch.where(q < 0, cols, bound)                       # all-masked rows are written in full (NaN)
+    written = torch.arange(cols, device="cuda")[None, :] < bound[:, None]
+    for got, full in ((p, p_full), (ds, ds_full)):
+        assert torch.equal(torch.where(written, got, 0).view(torch.uint8), torch.where(written, full, 0).view(torch.uint8))
+        assert (got[~written] == 7.0).all()
+    p1 = torch.full_like(s, 7.0)
+    ops.softmax_fwd(s, mask + (True,), p=p1)
+    assert torch.equal(p1.view(torch.uint8), p.view(torch.uint8))
+    ds1 = torch.full_like(s, 7.0)
+    ops.softmax_bwd(s, dp, mask + (True,), ds=ds1)
+    assert torch.equal(ds1.view(torch.uint8), ds.view(torch.uint8))
+
+
 def test_softmax_unaligned_accumulate_bf16_dead_rows(cuda):
     a = G.inputs(3)
     s, dp = offset_view(a["s"], 1), offset_view(a["dp"], 5)
