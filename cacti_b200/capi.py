@@ -30,6 +30,7 @@ SIGNATURES = {
     "cacti_b200_device_error": (_int, [C.POINTER(C.c_uint)]),
     "cacti_b200_rmsnorm_workspace_bytes": (_sz, [_i64, _i64]),
     "cacti_b200_rmsnorm_fwd": (_int, [_p, _p, _p, _f32, _i64, _i64, _int, _st]),
+    "cacti_b200_add_rmsnorm_fwd": (_int, [_p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _st]),
     "cacti_b200_rmsnorm_bwd": (_int, [_p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _p, _sz, _st]),
     "cacti_b200_rmsnorm_fwd_bwd": (_int, [_p, _p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _p, _sz, _st]),
     "cacti_b200_rmsnorm_fwd_bwd_noalloc": (_int, [_p, _p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _int, _int, _int, _st]),

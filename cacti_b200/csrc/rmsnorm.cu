@@ -21,16 +21,20 @@ int g_rmsnorm_smem_kb = 96;       // shared memory per CTA spent on the row ring
 
 constexpr int kRmsMaxPartials = kNumSMs * 8;
 
-template <typename T, int NV, bool FWD, bool BWD>
+// ADD (forward only): the normalised row is T(X + R), the residual add that precedes every norm of the decoder
+// layer (src/librarium/llama.rs:514,533); the rounded sum is also written to SUM.  The second stage row then holds R.
+template <typename T, int NV, bool FWD, bool BWD, bool ADD = false>
 __global__ void __launch_bounds__(512)
 rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
                     const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
-                    float eps, int64_t rows, int cols, int G, int nstages, int beta_dx) {
+                    float eps, int64_t rows, int cols, int G, int nstages, int beta_dx,
+                    const T* __restrict__ R = nullptr, T* __restrict__ SUM = nullptr) {
+  static_assert(!ADD || (FWD && !BWD), "the residual add is fused into the forward norm only");
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
   const unsigned row_bytes = (unsigned)cols * sizeof(T);
-  const unsigned stage_bytes = row_bytes * (BWD ? 2 : 1);
+  const unsigned stage_bytes = row_bytes * ((BWD || ADD) ? 2 : 1);
   // shared: [groups][nstages] stage buffers (x row, dy row) | mbarriers | reduction slots | dgamma fold [cols]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * stage_bytes);
   float* red = reinterpret_cast<float*>(bars + groups * nstages);
@@ -62,6 +66,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
       mbar_expect_tx(bar0 + sl, stage_bytes);
       bulk_g2s(dst, X + r * cols, row_bytes, bar0 + sl);
       if (BWD) bulk_g2s(dst + row_bytes, dY + r * cols, row_bytes, bar0 + sl);
+      if (ADD) bulk_g2s(dst + row_bytes, R + r * cols, row_bytes, bar0 + sl);
     }
   };
   for (int sl = 0; sl < nstages; ++sl)
@@ -79,6 +84,15 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
       if (col0 < cols) {
         xraw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
         if (BWD) yraw[k] = *reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T));
+        if (ADD) {
+          float a[VEC], b[VEC];
+          unpack<T>(xraw[k], a);
+          unpack<T>(*reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T)), b);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) a[e] = __fadd_rn(a[e], b[e]);
+          xraw[k] = pack<T>(a);                  // rounded to T: what a separate add would have stored
+          st_stream(SUM + row * cols + col0, xraw[k]);
+        }
       }
     }
     const int cur_slot = slot;
@@ -241,10 +255,11 @@ static size_t rmsnorm_ws_bytes(int64_t rows, int64_t cols, int max_partials = kR
   return (a > b ? a : b) + 256;
 }
 
-template <typename T, typename TO, bool FWD, bool BWD>
+// Returns -1 (nothing launched) when ADD is set and the shape does not fit the row kernel.
+template <typename T, typename TO, bool FWD, bool BWD, bool ADD = false>
 static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, uint64_t gamma, uint64_t dy,
                           float eps, int64_t rows, int64_t cols, int beta_dx, int beta_dg, uint64_t ws,
-                          cudaStream_t st, int max_partials = kRmsMaxPartials) {
+                          cudaStream_t st, int max_partials = kRmsMaxPartials, uint64_t r = 0, uint64_t sum = 0) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NVMAX = 4;
   T* Y = reinterpret_cast<T*>(y); T* dX = reinterpret_cast<T*>(dx);
@@ -252,15 +267,16 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
   const T* dY = reinterpret_cast<const T*>(dy);
   TO* dG = reinterpret_cast<TO*>(dgamma);
   float* wsf = reinterpret_cast<float*>(ws);
+  const T* Rp = reinterpret_cast<const T*>(r); T* Sp = reinterpret_cast<T*>(sum);
   const bool vec_ok = (cols % VEC == 0) && aligned16(x) && aligned16(gamma) && (!FWD || aligned16(y)) &&
-                      (!BWD || (aligned16(dx) && aligned16(dy))) && cols / VEC <= 512LL * NVMAX &&
+                      (!BWD || (aligned16(dx) && aligned16(dy))) && (!ADD || (aligned16(r) && aligned16(sum))) && cols / VEC <= 512LL * NVMAX &&
                       (size_t)cols * sizeof(float) <= 64 * 1024;
   if (vec_ok) {
     GroupPlan pl = plan_group(cols / VEC, NVMAX, g_rmsnorm_gpref, g_rmsnorm_threads);
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      const size_t stage = (size_t)cols * sizeof(T) * (BWD ? 2 : 1);
+      const size_t stage = (size_t)cols * sizeof(T) * ((BWD || ADD) ? 2 : 1);
       auto smem_for = [&](int ns) {
         return pl.groups * ns * (stage + sizeof(uint64_t)) +
                ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
@@ -272,11 +288,12 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
       int64_t grid = 0;
 #define CB_LAUNCH(NV_)                                                                                      \
   do {                                                                                                      \
-    auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD>;                                                      \
+    auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD, ADD>;                                                 \
     grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                                           \
     if (grid > max_partials) grid = max_partials;                                                           \
     if (grid > want) grid = want;                                                                           \
-    kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, nstages, beta_dx); \
+    kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, nstages, beta_dx, \
+                                                Rp, Sp);                                                    \
   } while (0)
       if (smem <= kMaxDynSmem) {
         switch (pl.NV) {
@@ -293,6 +310,7 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
       }
     }
   }
+  if (ADD) return -1;
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
   rmsnorm_rows_generic_kernel<T, FWD, BWD><<<(unsigned)grid, 256, 0, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, cols,
                                                                            beta_dx);
@@ -371,6 +389,24 @@ size_t cacti_b200_rmsnorm_workspace_bytes(int64_t rows, int64_t cols) {
 int cacti_b200_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr gamma, float eps, int64_t rows,
                            int64_t cols, int dtype, cacti_b200_stream stream) {
   return cb::rmsnorm_entry(true, false, y, 0, 0, x, gamma, 0, eps, rows, cols, dtype, dtype, 0, 0, 0, 0, stream);
+}
+int cacti_b200_add_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr sum, cacti_b200_dptr a, cacti_b200_dptr b,
+                               cacti_b200_dptr gamma, float eps, int64_t rows, int64_t cols, int dtype,
+                               cacti_b200_stream stream) {
+  using namespace cb;
+  if (rows < 0 || cols < 0 || cols > 0x7fffffffLL) return CACTI_B200_ERR_INVALID_VALUE;
+  if (rows == 0 || cols == 0) return CACTI_B200_OK;
+  if (!y || !sum || !a || !b || !gamma) return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int rc = dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    return launch_rmsnorm<T, T, true, false, true>(y, 0, 0, a, gamma, 0, eps, rows, cols, 0, 0, 0, st, kRmsMaxPartials, b, sum);
+  });
+  if (rc != -1) return rc;
+  // shapes the row kernel does not take: the two steps as separate launches, same results
+  const int rc2 = cacti_b200_add(sum, a, b, rows * cols, dtype, stream);
+  if (rc2) return rc2;
+  return rmsnorm_entry(true, false, y, 0, 0, sum, gamma, 0, eps, rows, cols, dtype, dtype, 0, 0, 0, 0, stream);
 }
 int cacti_b200_rmsnorm_bwd(cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr dy, cacti_b200_dptr x,
                            cacti_b200_dptr gamma, float eps, int64_t rows, int64_t cols, int dtype, int dgamma_dtype,

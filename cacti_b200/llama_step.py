@@ -8,6 +8,7 @@ arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph,
   * attention probabilities are recomputed from the saved scores in the backward instead of being kept
     (the fused softmax forward+backward entry point yields them together with dS; 2.1 GB less live memory per
     layer at B = 8);
+  * each residual add (llama.rs:514,533) runs inside the RMSNorm that follows it (same bits, one pass less);
   * the diagnostics thunks the example runs on every tensor (examples/open_llama_3b_train.rs:412-425) are omitted;
   * the six block matmuls of a layer carry the causal structure as a hint: score / dP tiles above the diagonal are
     not computed (the masked softmax never reads them) and products with the exact zeros of P and dS are skipped;
@@ -117,8 +118,13 @@ class TrainStep:
         x, _ = ops.gather_rows(P["embed"], tokens, status=self.status)
         self.launches += 1
         saved = []
+        branch = None                                     # output of the previous MLP, not yet added to the stream
         for Lw in P["layers"]:
-            n1 = ops.rmsnorm_fwd(x, Lw["pre_norm"], cfg.eps)
+            # each residual add is fused into the norm that follows it (one pass instead of two over [T, D])
+            if branch is None:
+                n1 = ops.rmsnorm_fwd(x, Lw["pre_norm"], cfg.eps)
+            else:
+                n1, x = ops.add_rmsnorm_fwd(x, branch, Lw["pre_norm"], cfg.eps)
             q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
             k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
             v = self._mm(n1, Lw["v"], False, True)
@@ -126,16 +132,16 @@ class TrainStep:
             p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
             ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)
             del p
-            x_mid = ops.add(x, self._mm(ctx, Lw["o"], False, True))
-            n2 = ops.rmsnorm_fwd(x_mid, Lw["post_norm"], cfg.eps)
+            n2, x_mid = ops.add_rmsnorm_fwd(x, self._mm(ctx, Lw["o"], False, True), Lw["post_norm"], cfg.eps)
             up = self._mm(n2, Lw["up"], False, True)
             gate = self._mm(n2, Lw["gate"], False, True)
             h = ops.swiglu_fwd(gate, up)
-            x_out = ops.add(x_mid, self._mm(h, Lw["down"], False, True))
-            self.launches += 9
+            branch = self._mm(h, Lw["down"], False, True)
+            self.launches += 6
             saved.append((x, n1, q, k, v, sc, ctx, x_mid, n2, up, gate, h))
-            x = x_out
-        nf = ops.rmsnorm_fwd(x, P["head_norm"], cfg.eps)
+            x = x_mid
+        nf, x = ops.add_rmsnorm_fwd(x, branch, P["head_norm"], cfg.eps)
+        del branch
         logits = self._mm(nf, P["lm_head"], False, True)
         loss, _, dlogits, _ = ops.softmax_nll_fwd_bwd(logits, targets, w_scalar=1.0 / self.loss_tokens, want_rows=False,
                                                        status=self.status)

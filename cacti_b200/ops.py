@@ -50,6 +50,16 @@ def rmsnorm_fwd(x, gamma, eps, y=None):
     return y
 
 
+def add_rmsnorm_fwd(a, b, gamma, eps, y=None, total=None):
+    """(y, total) with total = a + b (rounded to the storage type) and y = rmsnorm(total); one pass over HBM."""
+    rows, cols = a.shape
+    y = torch.empty_like(a) if y is None else y
+    total = torch.empty_like(a) if total is None else total
+    check(lib().cacti_b200_add_rmsnorm_fwd(_ptr(y), _ptr(total), _ptr(a), _ptr(b), _ptr(gamma), eps, rows, cols, _dt(a),
+                                           _stream()), "add_rmsnorm_fwd")
+    return y, total
+
+
 def rmsnorm_bwd(x, gamma, dy, eps, dx=None, dgamma=None, beta_dx=0, beta_dgamma=0, dgamma_dtype=None, workspace=None):
     rows, cols = x.shape
     dx = torch.empty_like(x) if dx is None else dx

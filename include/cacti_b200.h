@@ -96,6 +96,13 @@ int         cacti_b200_tune(const char* name, int value);
 size_t cacti_b200_rmsnorm_workspace_bytes(int64_t rows, int64_t cols);
 int cacti_b200_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr gamma, float eps,
                            int64_t rows, int64_t cols, int dtype, cacti_b200_stream stream);
+/* Residual add fused into the norm that follows it: sum = T(a + b) (AddFutThunkSpec, src/thunk/op.rs:1480-1535; the
+ * `stream + o_stream` adds of src/librarium/llama.rs:514,533), y = rmsnorm(sum) as cacti_b200_rmsnorm_fwd.  Both
+ * outputs are bit-identical to cacti_b200_add followed by cacti_b200_rmsnorm_fwd; the sum is read back from
+ * registers instead of HBM.  `sum` may alias `a` or `b`. */
+int cacti_b200_add_rmsnorm_fwd(cacti_b200_dptr y, cacti_b200_dptr sum, cacti_b200_dptr a, cacti_b200_dptr b,
+                               cacti_b200_dptr gamma, float eps, int64_t rows, int64_t cols, int dtype,
+                               cacti_b200_stream stream);
 int cacti_b200_rmsnorm_bwd(cacti_b200_dptr dx, cacti_b200_dptr dgamma, cacti_b200_dptr dy,
                            cacti_b200_dptr x, cacti_b200_dptr gamma, float eps,
                            int64_t rows, int64_t cols, int dtype, int dgamma_dtype,

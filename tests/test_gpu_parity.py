@@ -131,6 +131,26 @@ def test_softmax_golden(cuda, case):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (37, 3200), (300, 104), (64, 8192), (5, 20000), (9, 7), (16, 3201)])
+def test_add_rmsnorm_fwd_equals_separate_steps(cuda, dtype, rows, cols):
+    """The residual add fused into the norm gives the bits of add followed by rmsnorm_fwd (and the oracle's values);
+    shapes that fall back to two launches included; in-place sum."""
+    kind = KIND[np.dtype(dtype)]
+    a, b = R.normal(90, (rows, cols), dtype), R.normal(91, (rows, cols), dtype, 0.3)
+    gm = R.normal(92, (cols,), dtype, 0.5) + dtype(1)
+    total_ref = ops.add(dev(a), dev(b))
+    y_ref = ops.rmsnorm_fwd(total_ref, dev(gm), 1e-6)
+    y, total = ops.add_rmsnorm_fwd(dev(a), dev(b), dev(gm), 1e-6)
+    assert torch.equal(total.view(torch.uint8), total_ref.view(torch.uint8))
+    assert torch.equal(y.view(torch.uint8), y_ref.view(torch.uint8))
+    assert_close(host(y), R.ref_rmsnorm_fwd((a + b).astype(dtype), gm, 1e-6), kind, "fused add + norm")
+    inplace = dev(a)
+    y2, t2 = ops.add_rmsnorm_fwd(inplace, dev(b), dev(gm), 1e-6, total=inplace)
+    assert t2.data_ptr() == inplace.data_ptr() and torch.equal(y2.view(torch.uint8), y_ref.view(torch.uint8))
+    assert torch.equal(inplace.view(torch.uint8), total_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
 @pytest.mark.parametrize("rows,cols,mask", [(1, 1, None), (3, 2, None), (33, 7, (1, 7, 0)), (5, 8, None),
                                             (6, 9, (2, 3, 0)), (4, 100, (1, 4, 50)), (33, 104, None),
                                             (64, 256, (1, 64, 0)), (16, 2048, (4, 4, 1000)), (7, 2056, None),
