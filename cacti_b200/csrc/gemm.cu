@@ -27,8 +27,7 @@
 // slices at 200-byte offsets) are first repacked into the caller's workspace with the inner
 // dimension zero-padded to a multiple of 64 elements; the reference pads the same operands to 16 bytes
 // with a separate thunk before calling cuBLAS (src/op.rs:1454-1482).  Outputs need no alignment.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 #include <type_traits>
 
 namespace cb {
@@ -49,59 +48,6 @@ struct GemmParams {
   int group_m;                            // tile rasterisation: m-tiles per group (L2 reuse of the B panel)
   int tri, diag;                          // triangular-structure hint (CACTI_B200_TRI_*) and its diagonal offset
 };
-
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum)
-      : "memory");
-}
-// issues the load; the registers are valid after tc_ld_wait()
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (sm_100 UMMA): start address, leading / stride byte offsets in
-// 16-byte units, version 1, 128-byte swizzle.
-//   K-major tile  [rows][64 k]: rows are 128 B apart, 8-row groups 1024 B apart (SBO); a 16-wide k step
-//                               advances the start address by 32 B inside the swizzle atom.
-//   MN-major tile [64 k][64 mn] per 8 KB box: k rows are 128 B apart, 8-k groups 1024 B apart (SBO),
-//                               the next 64 mn-columns 8192 B further (LBO); a k step advances 2048 B.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo16, uint32_t sbo16) {
-  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | ((lbo16 & 0x3FFFu) << 16);
-  const uint32_t hi = (sbo16 & 0x3FFFu) | (1u << 14) | (2u << 29);
-  return ((uint64_t)hi << 32) | lo;
-}
 
 // Tile order inside one block: groups of `group_m` m-tiles; inside a group the m index runs fastest, so
 // the CTAs that run at the same time share a few B (weight) panels and a bounded set of A rows in L2.
@@ -139,11 +85,6 @@ __device__ __forceinline__ void k_block_range(const GemmParams& p, int row0, int
     const long long b = first < 0 ? 0 : first / kBK;
     kb0 = b > nkb - 1 ? nkb - 1 : (int)b;
   }
-}
-
-// Arrive on an mbarrier given by a shared::cluster address (this CTA's own barriers included).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
 }
 
 // Epilogue of one accumulator for one warp: TMEM lanes [q*32, q*32+32) x BN columns of accumulator `acc` become
@@ -595,22 +536,6 @@ pack_blocks_kernel(U* __restrict__ dst, const U* __restrict__ src, unsigned rows
     if (c < upr_src) v = src[bo * so_units + bi * si_units + (long long)r * ld_units + c];
     dst[i] = v;
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 // One operand as stored: `rows` x `cols` elements, cols contiguous, leading dimension ld, block strides.

@@ -294,3 +294,22 @@ def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, 
                                                 int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci, _dt(a),
                                                 _ptr(workspace), workspace.numel(), _stream()), "block_gemm")
     return c
+
+
+# ---- A1 ---------------------------------------------------------------------------------------
+def block_pad(x, cols_pad=128, out=None):
+    """[nrow, rows, ncol, cols] -> [nrow, rows, ncol, cols_pad], zeros in the added columns."""
+    nrow, rows, ncol, cols = x.shape
+    out = torch.empty(nrow, rows, ncol, cols_pad, dtype=x.dtype, device=x.device) if out is None else out
+    check(lib().cacti_b200_block_pad(_ptr(out), _ptr(x), nrow, rows, ncol, cols, cols_pad, _dt(x), _stream()), "block_pad")
+    return out
+
+
+def attention_fwd(q_pad, k_pad, v_pad, head_dim, alpha, ctx=None, stats=None):
+    """Fused causal attention on head-dim-padded [B, S, H, 128] operands -> (ctx [B, S, H, head_dim], stats [B, H, S, 2])."""
+    b, s, h, _ = q_pad.shape
+    ctx = torch.empty(b, s, h, head_dim, dtype=q_pad.dtype, device=q_pad.device) if ctx is None else ctx
+    stats = torch.empty(b, h, s, 2, dtype=torch.float32, device=q_pad.device) if stats is None else stats
+    check(lib().cacti_b200_attention_fwd(_ptr(ctx), _ptr(stats), _ptr(q_pad), _ptr(k_pad), _ptr(v_pad), b, s, h, head_dim,
+                                         alpha, _dt(q_pad), _stream()), "attention_fwd")
+    return ctx, stats

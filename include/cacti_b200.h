@@ -303,6 +303,30 @@ int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, ca
                                         int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
                                         cacti_b200_stream stream);
 
+/* ---- A1 block padding and fused causal attention ------------------------------------------------------------
+ * block_pad replaces BlockPadFutThunkSpec (src/thunk/op.rs:4065-4186), which the reference stages before a block
+ * matmul whose blocks are not 16-byte multiples (src/op.rs:1454-1482): dst[nrow, rows, ncol, cols_pad] =
+ * src[nrow, rows, ncol, cols] with zeros in the added columns.  16-bit types. */
+int cacti_b200_block_pad(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t nrow, int64_t rows, int64_t ncol,
+                         int64_t cols, int64_t cols_pad, int dtype, cacti_b200_stream stream);
+
+/* Fused causal attention forward: the thunk sequence block_matmul_scale, cast, block_causal_attention_mask,
+ * inner_softmax, lossy_cast, block_matmul of src/librarium/llama.rs:501-507 as one kernel; the [B, S, H, S] scores and
+ * probabilities never reach HBM.  No single counterpart in the reference.
+ *   q, k, v : [batch, seq, heads, 128] of dtype (R_16F / R_16BF), head_dim columns of data then zeros
+ *             (cacti_b200_block_pad with cols_pad = 128); 16-byte aligned
+ *   ctx     : [batch, seq, heads, head_dim], 8-byte aligned
+ *   stats   : [batch, heads, seq, 2] f32: row maximum m of the rounded scaled scores and sum of exp(s - m) over the
+ *             unmasked keys; what a backward pass needs to rebuild the probabilities
+ * Scores are rounded to dtype as block_matmul_scale stores them and the softmax runs in f32 on the rounded values
+ * with the row maximum subtracted, as the reference does.  exp(s - m) is rounded to dtype before the product with V
+ * and the division by the row sum is applied to the f32 result, where the reference rounds the quotient first: ctx
+ * agrees with the unfused chain to rounding noise (relative 2^-11 per probability), not bit for bit.
+ * Requires seq % 128 == 0, head_dim <= 128, head_dim % 4 == 0 (else CACTI_B200_ERR_SHAPE); query i sees keys <= i. */
+int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b200_dptr q, cacti_b200_dptr k,
+                             cacti_b200_dptr v, int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha,
+                             int dtype, cacti_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,92 @@
+"""GPU parity tests of the fused causal attention forward and of block_pad.
+
+Oracle: the reference chain in f64 with its rounding points (scores rounded to the storage type, softmax in f32 on
+the rounded scores; src/librarium/llama.rs:501-507).  Tolerance: the block matmul's, 2e-3 relative to max(|ref|, rms),
+measured against max(|ref|, sum_j p_j |v_j|): the context is a sum of 16-bit-rounded probabilities times V, each
+term carrying a relative rounding error of 2^-12 (in the reference's own chain as well), so the error scales with the
+sum of magnitudes, not with the possibly cancelled result."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from cacti_b200 import capi, ops
+from oracle import ref_chain as R
+from tests.gpu_util import dev, host
+from tests.tolerances import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_attention(q, k, v, alpha):
+    """q, k, v: [B, S, H, hd] float16 arrays -> (ctx f64, m, l) along the reference chain."""
+    qf, kf, vf = (np.transpose(t.astype(np.float64), (0, 2, 1, 3)) for t in (q, k, v))          # [B, H, S, hd]
+    acc = np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(np.float32)                                 # fp32 accumulate
+    sc = (np.float32(alpha) * acc).astype(q.dtype).astype(np.float64)                             # stored scores
+    s = sc.shape[-1]
+    keep = np.tril(np.ones((s, s), bool))
+    sc = np.where(keep, sc, -np.inf)
+    m = sc.max(-1, keepdims=True)
+    e = np.exp(sc - m)
+    l = e.sum(-1, keepdims=True)
+    ctx = np.einsum("bhqk,bhkd->bhqd", e / l, vf)
+    mag = np.einsum("bhqk,bhkd->bhqd", e / l, np.abs(vf))
+    return np.transpose(ctx, (0, 2, 1, 3)), m[..., 0], l[..., 0], np.transpose(mag, (0, 2, 1, 3))
+
+
+@pytest.mark.parametrize("cols,cols_pad", [(100, 128), (64, 128), (7, 16), (128, 128), (30, 33)])
+def test_block_pad(cuda, cols, cols_pad):
+    x = dev(R.normal(70, (2, 37, 3, cols), np.float16))
+    y = ops.block_pad(x, cols_pad)
+    assert torch.equal(y[..., :cols], x) and (y[..., cols:] == 0).all()
+    L = capi.lib()
+    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, 37, 3, cols, cols - 1, capi.R_16F, None) == capi.ERR_INVALID_VALUE
+    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, 37, 3, cols, cols_pad, capi.R_32F, None) == capi.ERR_DTYPE
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(1, 128, 1, 128), (2, 256, 3, 100), (1, 640, 2, 64), (2, 1024, 2, 100)])
+def test_attention_fwd(cuda, bsz, s, h, hd):
+    q = R.normal(71, (bsz, s, h, hd), np.float16)
+    k = R.normal(72, (bsz, s, h, hd), np.float16)
+    v = R.normal(73, (bsz, s, h, hd), np.float16)
+    alpha = float(1.0 / np.sqrt(hd))
+    qp, kp, vp = (ops.block_pad(dev(t), 128) for t in (q, k, v))
+    ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+    rctx, rm, rl, mag = ref_attention(q, k, v, alpha)
+    assert_close(host(ctx), rctx, "float16", f"fused attention ctx B={bsz} S={s} H={h} hd={hd}", floor_frac=1.0, floor_abs=mag)
+    st = host(stats)
+    # the row maximum is a maximum of 16-bit values: exact unless the fp32 accumulation order moved a score by one ulp
+    assert np.abs(st[..., 0] - rm).max() <= 2.0 ** -9 * np.abs(rm).max()
+    assert np.abs(st[..., 1] / (rl * np.exp(rm - st[..., 0])) - 1).max() < 2e-3
+    # and against the unfused entry points on the same inputs
+    sc = ops.block_gemm(dev(q), dev(k), False, True, alpha=alpha)
+    pr = ops.softmax_fwd(sc.view(-1, s), (h, s, 0)).view(bsz, s, h, s)
+    unfused = ops.block_gemm(pr, dev(v), False, False)
+    # both sides carry their own 16-bit roundings: twice the tolerance of one
+    assert_close(host(ctx), host(unfused).astype(np.float64), "float16", "fused vs unfused chain", rtol=4e-3, floor_frac=1.0,
+                 floor_abs=mag)
+
+
+def test_attention_fwd_bf16_and_errors(cuda):
+    bsz, s, h, hd = 1, 256, 2, 100
+    q, k, v = (R.bf16_round(R.normal(80 + i, (bsz, s, h, hd))) for i in range(3))
+    alpha = 0.1
+    qp, kp, vp = (ops.block_pad(dev(t, bf16=True), 128) for t in (q, k, v))
+    ctx, _ = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    qf, kf, vf = (np.transpose(t.astype(np.float64), (0, 2, 1, 3)) for t in (q, k, v))
+    sc = R.bf16_round((np.float32(alpha) * np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(np.float32))).astype(np.float64)
+    sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+    e = np.exp(sc - sc.max(-1, keepdims=True))
+    ref = np.transpose(np.einsum("bhqk,bhkd->bhqd", e / e.sum(-1, keepdims=True), vf), (0, 2, 1, 3))
+    assert_close(host(ctx), ref, "bfloat16", "bf16 fused attention", floor_frac=1.0)
+    L = capi.lib()
+    P = qp.data_ptr()
+    assert L.cacti_b200_attention_fwd(P, P, P, P, P, 1, 200, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_SHAPE      # seq % 128
+    assert L.cacti_b200_attention_fwd(P, P, P, P, P, 1, 256, 2, 130, 0.1, capi.R_16F, None) == capi.ERR_SHAPE      # head_dim
+    assert L.cacti_b200_attention_fwd(P, P, P, P, P, 1, 256, 2, 100, 0.1, capi.R_32F, None) == capi.ERR_DTYPE
+    assert L.cacti_b200_attention_fwd(P, P, P, P, P, 0, 256, 2, 100, 0.1, capi.R_16F, None) == capi.OK
+    assert L.cacti_b200_attention_fwd(0, P, P, P, P, 1, 256, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_INVALID_VALUE
