@@ -14,13 +14,15 @@
 // probability, so the context differs from the unfused chain by rounding noise only (tests bound it at the fp16
 // tolerance of the block matmul).
 //
-// Kernel layout (one CTA = 128 query rows of one (batch, head); 192 threads):
+// Kernel layout (one CTA = 128 query rows of one (batch, head); 320 threads):
 //   warp 0      TMA producer: Q once, then K tiles (pass 1), then K and V tiles (pass 2) through two-slot rings
 //   warp 1      allocates tensor memory, issues tcgen05.mma: S = Q K^T (128 x 128 x hd_pad) into one of two S
 //               buffers; in pass 2 also O += P V
-//   warps 2..5  one thread per query row (TMEM lane = row): pass 1 reads S and keeps the row maximum; pass 2 reads S
-//               again, forms exp(s - m), sums it, writes the 16-bit probabilities into shared memory in the
-//               128-byte-swizzled K-major layout the MMA reads; at the end scales O by 1 / sum and stores the row
+//   warps 2..9  two softmax groups of 128 threads, one thread per query row (TMEM lane = row), group g on key tiles
+//               j = g (mod 2) with its own S buffer and probability buffer: pass 1 reads S and keeps the row maximum;
+//               pass 2 reads S again, forms exp(s - m), sums it, writes the 16-bit probabilities into shared memory
+//               in the 128-byte-swizzled K-major layout the MMA reads; the groups' maxima and sums are combined
+//               through shared memory; at the end each group scales half of O's columns by 1 / sum and stores them
 // Two passes (max first, then exp / sum / P V) instead of an online softmax: no rescaling of O in tensor memory, and
 // the row maximum is the true one as in the reference; the price is computing S twice (K = hd_pad, cheap).
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
@@ -32,7 +34,7 @@ namespace cb {
 constexpr unsigned kDevErrAttnTimeout = 3u;
 constexpr int kAttnRows = 128;      // query rows per CTA = keys per tile
 constexpr int kAttnHd = 128;        // padded head dimension
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // producer warp, MMA warp, two softmax groups of 4 warps
 
 struct AttnParams {
   int batch, seq, heads, head_dim;
@@ -52,6 +54,29 @@ __device__ __forceinline__ uint64_t v_desc(uint32_t base, int k16) {            
   return make_desc(base + (uint32_t)(k16 >> 2) * 16384u + (uint32_t)(k16 & 3) * 2048u, 512, 64);
 }
 
+// alpha * acc for two accumulator words, rounded to the 16-bit type (the stored score of the reference), as floats
+template <typename T>
+__device__ __forceinline__ float2 rounded_scores(float alpha, uint32_t a, uint32_t b) {
+  if constexpr (std::is_same<T, __half>::value) {
+    return __half22float2(__floats2half2_rn(alpha * __uint_as_float(a), alpha * __uint_as_float(b)));
+  } else {
+    return __bfloat1622float2(__floats2bfloat162_rn(alpha * __uint_as_float(a), alpha * __uint_as_float(b)));
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (std::is_same<T, __half>::value) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -62,8 +87,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   unsigned char* sQ = base;                        // 32 KB
   unsigned char* sK = sQ + kTileBytes;             // 2 x 32 KB
   unsigned char* sV = sK + 2 * kTileBytes;         // 2 x 32 KB
-  unsigned char* sP = sV + 2 * kTileBytes;         // 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kTileBytes);
+  unsigned char* sP = sV + 2 * kTileBytes;         // 2 x 32 KB (one per softmax group)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kTileBytes);
   uint64_t* q_full = bars;                         // 1
   uint64_t* k_full = bars + 1;                     // 2
   uint64_t* k_empty = bars + 3;                    // 2
@@ -71,10 +96,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* v_empty = bars + 7;                    // 2
   uint64_t* s_full = bars + 9;                     // 2
   uint64_t* s_empty = bars + 11;                   // 2
-  uint64_t* p_full = bars + 13;                    // 1
-  uint64_t* p_empty = bars + 14;                   // 1
-  uint64_t* o_full = bars + 15;                    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_full = bars + 13;                    // 2
+  uint64_t* p_empty = bars + 15;                   // 2
+  uint64_t* o_full = bars + 17;                    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  float* part = reinterpret_cast<float*>(bars + 20);       // [2 groups][128 rows] partial max, then partial sum
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // heaviest query tiles (most key tiles under the diagonal) are launched first
@@ -89,9 +115,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
-      mbar_init(s_full + s, 1); mbar_init(s_empty + s, 4);
+      mbar_init(s_full + s, 1); mbar_init(s_empty + s, 4); mbar_init(p_full + s, 4); mbar_init(p_empty + s, 1);
     }
-    mbar_init(p_full, 4); mbar_init(p_empty, 1); mbar_init(o_full, 1);
+    mbar_init(o_full, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -103,8 +129,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 128u};
-  const uint32_t tO = tmem_base + 256u;
+  const uint32_t tO = tmem_base + 256u;            // S buffers at columns 0 and 128
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -136,7 +161,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
     if (!mbar_wait_bounded(q_full, 0, kDevErrAttnTimeout)) goto done;
-    const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+    const uint32_t aQ = smem_u32(sQ);
     auto issue_s = [&](int n) -> bool {             // S[n & 1] = Q K_n^T
       const int ks = n & 1;
       const unsigned ph = (unsigned)((n >> 1) & 1);
@@ -146,7 +171,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t aK = smem_u32(sK + (size_t)ks * kTileBytes);
 #pragma unroll
       for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
-        tc_mma_f16(tS[ks], kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
+        tc_mma_f16(tmem_base + (uint32_t)ks * 128u, kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
       tc_commit(k_empty + ks);
       tc_commit(s_full + ks);
       return true;
@@ -154,112 +179,144 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     int n = 0;
     for (int j = 0; j < ntiles; ++j, ++n)           // pass 1: scores only
       if (!issue_s(n)) goto done;
-    if (!issue_s(n)) goto done;                     // first S of pass 2
-    ++n;
+    // pass 2: both S buffers are filled ahead; each P V follows its group's probabilities
+    for (int j = 0; j < 2 && j < ntiles; ++j, ++n)
+      if (!issue_s(n)) goto done;
     for (int j = 0; j < ntiles; ++j) {
-      if (j + 1 < ntiles) { if (!issue_s(n)) goto done; ++n; }      // S of the next tile overlaps this tile's softmax
       const int vs = j & 1;
-      if (!mbar_wait_bounded(v_full + vs, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) goto done;
-      if (!mbar_wait_bounded(p_full, (unsigned)(j & 1), kDevErrAttnTimeout)) goto done;
+      const unsigned ph = (unsigned)((j >> 1) & 1);
+      if (!mbar_wait_bounded(v_full + vs, ph, kDevErrAttnTimeout)) goto done;
+      if (!mbar_wait_bounded(p_full + vs, ph, kDevErrAttnTimeout)) goto done;
       tc_fence_after();
-      const uint32_t aV = smem_u32(sV + (size_t)vs * kTileBytes);
+      const uint32_t aV = smem_u32(sV + (size_t)vs * kTileBytes), aP = smem_u32(sP + (size_t)vs * kTileBytes);
 #pragma unroll
       for (int k16 = 0; k16 < kAttnRows / 16; ++k16)
         tc_mma_f16(tO, kmajor_desc(aP, k16), v_desc(aV, k16), p.idesc_pv, (j | k16) ? 1u : 0u);
       tc_commit(v_empty + vs);
-      tc_commit(p_empty);
+      tc_commit(p_empty + vs);
+      if (j + 2 < ntiles) { if (!issue_s(n)) goto done; ++n; }
     }
     tc_commit(o_full);
   } else if (warp >= 2) {
-    // ---------------- softmax warps: thread = query row ----------------
-    const int qq = warp & 3;                        // TMEM lane quarter
+    // ---------------- softmax groups: 2 x 128 threads, thread = query row, group g takes key tiles j = g (mod 2) ------
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;                        // TMEM lane quarter this warp may read
     const int r = qq * 32 + lane;                   // row inside the tile
     const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
     constexpr float kLog2e = 1.4426950408889634f;
     float m = -INFINITY;
-    int n = 0;
-    for (int j = 0; j < ntiles; ++j, ++n) {         // pass 1: row maximum of the rounded, scaled, masked scores
-      const int sb = n & 1;
-      if (!mbar_wait_bounded(s_full + sb, (unsigned)((n >> 1) & 1), kDevErrAttnTimeout)) goto done;
+    bool ok = true;   // a wait that ran out ends this thread's work, but it still meets the group barriers below
+    for (int j = grp; j < ntiles; j += 2) {         // pass 1: row maximum of the rounded, scaled, masked scores
+      const int sb = j & 1;
+      if (!mbar_wait_bounded(s_full + sb, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
       tc_fence_after();
-      const int lim = (j == qi) ? r : kAttnRows;    // columns <= lim are unmasked (diagonal tile: c <= r)
+      const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kAttnRows; c0 += 32) {
-        uint32_t v[32];
-        tc_ld32(tS[sb] + lane_off + (uint32_t)c0, v);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
         tc_ld_wait();
+        if (half == 1) {                            // the accumulator is in registers: the next S may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + sb);
+        }
+        if (j != qi) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * __uint_as_float(v[i])));
-          if (c0 + i <= lim) m = fmaxf(m, s);
+          for (int i = 0; i < 64; i += 2) {
+            const float2 s2 = rounded_scores<T>(p.alpha, v[i >> 5][i & 31], v[i >> 5][(i & 31) + 1]);
+            m = fmaxf(m, fmaxf(s2.x, s2.y));
+          }
+        } else {                                    // diagonal tile: columns c <= r are unmasked
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float2 s2 = rounded_scores<T>(p.alpha, v[i >> 5][i & 31], v[i >> 5][(i & 31) + 1]);
+            const int c = half * 64 + i;
+            if (c <= r) m = fmaxf(m, s2.x);
+            if (c + 1 <= r) m = fmaxf(m, s2.y);
+          }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty + sb);
     }
+    part[grp * kAttnRows + r] = m;
+    named_barrier(1, 256);
+    m = fmaxf(part[r], part[kAttnRows + r]);
+    named_barrier(1, 256);                          // everyone has read the maxima before the sums overwrite them
     float l = 0.f;
     const float mb = m * kLog2e;
-    for (int j = 0; j < ntiles; ++j, ++n) {         // pass 2: exp, row sum, probabilities to shared memory
-      const int sb = n & 1;
-      if (!mbar_wait_bounded(s_full + sb, (unsigned)((n >> 1) & 1), kDevErrAttnTimeout)) goto done;
+    unsigned char* myP = sP + (size_t)grp * kTileBytes;
+    for (int j = grp; ok && j < ntiles; j += 2) {   // pass 2: exp, row sum, probabilities to shared memory
+      const int n = ntiles + j, sb = n & 1;
+      if (!mbar_wait_bounded(s_full + sb, (unsigned)((n >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
       tc_fence_after();
-      // the previous tile's P V has read the probability buffer
-      if (!mbar_wait_bounded(p_empty, (unsigned)(j & 1) ^ 1, kDevErrAttnTimeout)) goto done;
-      const int lim = (j == qi) ? r : kAttnRows;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kAttnRows; c0 += 32) {
-        uint32_t v[32];
-        tc_ld32(tS[sb] + lane_off + (uint32_t)c0, v);
+      const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
+      uint4 pk[16];                                 // this row's 128 probabilities, 8 per 16-byte chunk
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
         tc_ld_wait();
-        unsigned char* prow = sP + (size_t)(c0 >> 6) * 16384 + (size_t)r * 128;
+        if (half == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + sb);
+        }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float e8[8];
+        for (int g = 0; g < 8; ++g) {
+          uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float s = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * __uint_as_float(v[g * 8 + i])));
-            const float e = (c0 + g * 8 + i <= lim) ? exp2f_approx(__fmaf_rn(s, kLog2e, -mb)) : 0.f;
-            l += e;
-            e8[i] = e;
+          for (int i = 0; i < 4; ++i) {
+            const int idx = g * 8 + i * 2;
+            const float2 s2 = rounded_scores<T>(p.alpha, v[idx >> 5][idx & 31], v[idx >> 5][(idx & 31) + 1]);
+            float e0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+            float e1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
+            if (j == qi) {
+              const int c = half * 64 + idx;
+              if (c > r) e0 = 0.f;
+              if (c + 1 > r) e1 = 0.f;
+            }
+            l += e0 + e1;
+            w[i] = pack2<T>(e0, e1);
           }
-          const int chunk = ((c0 & 63) >> 3) + g;   // 16-byte chunk inside the 128-byte row of this key half
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = pack<T>(e8);
+          pk[half * 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-      tc_fence_before();
+      // the P V two tiles back has read this group's probability buffer
+      if (!mbar_wait_bounded(p_empty + grp, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+#pragma unroll
+      for (int c = 0; c < 16; ++c)                  // chunk c: keys 8c .. 8c+7; key half c >> 3, chunk c & 7 of the 128-byte row
+        *reinterpret_cast<uint4*>(myP + (size_t)(c >> 3) * 16384 + (size_t)r * 128 + (((c & 7) ^ (r & 7)) << 4)) = pk[c];
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) { mbar_arrive(s_empty + sb); mbar_arrive(p_full); }
+      if (lane == 0) mbar_arrive(p_full + grp);
     }
-    // context row = O / l
-    if (!mbar_wait_bounded(o_full, 0, kDevErrAttnTimeout)) goto done;
+    part[grp * kAttnRows + r] = l;
+    named_barrier(1, 256);
+    l = part[r] + part[kAttnRows + r];
+    // context row = O / l; group 0 stores columns 0..63, group 1 columns 64..head_dim-1
+    if (!ok || !mbar_wait_bounded(o_full, 0, kDevErrAttnTimeout)) goto done;
     tc_fence_after();
     const float rl = 1.f / l;
     const long long row = (long long)b * p.seq + q0 + r;
     T* out = ctx + (row * p.heads + h) * p.head_dim;
-    float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 2;
-    st[0] = m; st[1] = l;
+    if (grp == 0) {
+      float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 2;
+      st[0] = m; st[1] = l;
+    }
 #pragma unroll 1
-    for (int c0 = 0; c0 < p.head_dim; c0 += 32) {
+    for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
       uint32_t v[32];
       tc_ld32(tO + lane_off + (uint32_t)c0, v);
       tc_ld_wait();
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {                 // 4 elements = 8 bytes per store (rows start 8-byte aligned when hd % 4 == 0)
+      for (int g = 0; g < 8; ++g) {                 // 4 elements = 8 bytes per store (rows start 8-byte aligned: hd % 4 == 0)
         const int c = c0 + g * 4;
         if (c + 4 <= p.head_dim) {
-          float f4[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) f4[i] = __uint_as_float(v[g * 4 + i]) * rl;
           uint2 w;
-          if constexpr (std::is_same<T, __half>::value) {
-            __half2 a = __floats2half2_rn(f4[0], f4[1]), bb = __floats2half2_rn(f4[2], f4[3]);
-            w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&bb);
-          } else {
-            __nv_bfloat162 a = __floats2bfloat162_rn(f4[0], f4[1]), bb = __floats2bfloat162_rn(f4[2], f4[3]);
-            w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&bb);
-          }
+          w.x = pack2<T>(__uint_as_float(v[g * 4]) * rl, __uint_as_float(v[g * 4 + 1]) * rl);
+          w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * rl, __uint_as_float(v[g * 4 + 3]) * rl);
           *reinterpret_cast<uint2*>(out + c) = w;
         }
       }
@@ -267,6 +324,212 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_before();
   }
 done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- backward: probabilities and score adjoints, rebuilt tile by tile -------------------------------------------
+// The adjoint of the chain needs P (for dV = P^T dO) and dS (for dQ = dS K, dK = dS^T Q).  The reference keeps the
+// scores and recomputes the softmax from them inside InnerSoftmaxPostAdj (src/thunk/op.rs:3376-3457) after a block
+// matmul has produced dP = dO V^T.  Here neither scores nor dP exist in HBM: per 128 x 128 tile two MMAs rebuild
+// S = Q K^T and dP = dO V^T in tensor memory and the softmax threads turn them into
+//   y = exp(s - m) / l   (m, l: the forward's row statistics),   P = T(y),   dS = T(y * T(dP) - c * y)
+// with the reference's rounding points (s and dP rounded to the storage type first).  c = sum_j y_j dP_j is taken as
+// D = dO . O (equal in exact arithmetic; O is the stored context row), so no pass over the whole row is needed
+// before the first tile can be written.  Tiles above the diagonal are not written, except the one zero tile that
+// completes the last written pair of tiles to 256 columns (what a CACTI_B200_TRI_A_* consumer may read).
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                          const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmdS,
+                          const T* __restrict__ ctx, const T* __restrict__ dctx_pad,
+                          const float* __restrict__ stats, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = base;                        // 32 KB
+  unsigned char* sdO = sQ + kTileBytes;            // 32 KB
+  unsigned char* sK = sdO + kTileBytes;            // 2 x 32 KB
+  unsigned char* sV = sK + 2 * kTileBytes;         // 2 x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kTileBytes);
+  uint64_t* q_full = bars;                         // 1: Q and dO
+  uint64_t* kv_full = bars + 1;                    // 2
+  uint64_t* kv_empty = bars + 3;                   // 2
+  uint64_t* t_full = bars + 5;                     // 2: S and dP of one tile are complete
+  uint64_t* t_empty = bars + 7;                    // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  // output staging: per softmax warp one [32 rows][64 columns] box in the 128-byte-swizzled layout of a TMA store
+  unsigned char* stage = sV + 2 * kTileBytes + 1024;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int nq = p.seq / kAttnRows, bh_count = p.batch * p.heads;
+  const int qi = nq - 1 - (int)(blockIdx.x / bh_count);
+  const int bh = (int)(blockIdx.x % bh_count);
+  const int b = bh / p.heads, h = bh - b * p.heads;
+  const int ntiles = qi + 1;
+  const int q0 = qi * kAttnRows;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); mbar_init(t_full + s, 1); mbar_init(t_empty + s, 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;           // columns: S0 0, dP0 128, S1 256, dP1 384
+
+  if (warp == 0 && lane == 0) {
+    mbar_expect_tx(q_full, 2 * kTileBytes);
+    tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+    tma_load_4d(sQ + 16384, &tmQ, q_full, 64, q0, h, b);
+    tma_load_4d(sdO, &tmdO, q_full, 0, q0, h, b);
+    tma_load_4d(sdO + 16384, &tmdO, q_full, 64, q0, h, b);
+    for (int j = 0; j < ntiles; ++j) {
+      const int sl = j & 1;
+      if (!mbar_wait_bounded(kv_empty + sl, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) goto done;
+      unsigned char* dk = sK + (size_t)sl * kTileBytes;
+      unsigned char* dv = sV + (size_t)sl * kTileBytes;
+      mbar_expect_tx(kv_full + sl, 2 * kTileBytes);
+      tma_load_4d(dk, &tmK, kv_full + sl, 0, j * kAttnRows, h, b);
+      tma_load_4d(dk + 16384, &tmK, kv_full + sl, 64, j * kAttnRows, h, b);
+      tma_load_4d(dv, &tmV, kv_full + sl, 0, j * kAttnRows, h, b);
+      tma_load_4d(dv + 16384, &tmV, kv_full + sl, 64, j * kAttnRows, h, b);
+    }
+  } else if (warp == 1 && lane == 0) {
+    if (!mbar_wait_bounded(q_full, 0, kDevErrAttnTimeout)) goto done;
+    const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
+    for (int j = 0; j < ntiles; ++j) {
+      const int sl = j & 1;
+      const unsigned ph = (unsigned)((j >> 1) & 1);
+      if (!mbar_wait_bounded(kv_full + sl, ph, kDevErrAttnTimeout)) goto done;
+      if (!mbar_wait_bounded(t_empty + sl, ph ^ 1, kDevErrAttnTimeout)) goto done;
+      tc_fence_after();
+      const uint32_t aK = smem_u32(sK + (size_t)sl * kTileBytes), aV = smem_u32(sV + (size_t)sl * kTileBytes);
+      const uint32_t tS = tmem_base + (uint32_t)sl * 256u, tdP = tS + 128u;
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+        tc_mma_f16(tS, kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+        tc_mma_f16(tdP, kmajor_desc(adO, k16), kmajor_desc(aV, k16), p.idesc_s, k16 ? 1u : 0u);
+      tc_commit(kv_empty + sl);
+      tc_commit(t_full + sl);
+    }
+  } else if (warp >= 2) {
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;
+    const int r = qq * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const long long row = (long long)b * p.seq + q0 + r;
+    const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 2;
+    const float mb = st[0] * kLog2e, rl = 1.f / st[1];
+    // c = dO . O over the head dimension (f32 accumulation of the stored 16-bit values)
+    float cdot = 0.f;
+    {
+      const uint2* o2 = reinterpret_cast<const uint2*>(ctx + (row * p.heads + h) * p.head_dim);
+      const uint2* g2 = reinterpret_cast<const uint2*>(dctx_pad + (row * p.heads + h) * kAttnHd);
+      for (int i = 0; i < p.head_dim / 4; ++i) {
+        const uint2 a = o2[i], g = g2[i];
+        float2 a0, a1, g0, g1;
+        if constexpr (std::is_same<T, __half>::value) {
+          a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)); a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+          g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)); g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
+        } else {
+          a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)); a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+          g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x)); g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+        }
+        cdot = __fmaf_rn(a0.x, g0.x, cdot); cdot = __fmaf_rn(a0.y, g0.y, cdot);
+        cdot = __fmaf_rn(a1.x, g1.x, cdot); cdot = __fmaf_rn(a1.y, g1.y, cdot);
+      }
+    }
+    unsigned char* mystage = stage + (size_t)(warp - 2) * 4096 + (size_t)lane * 128;
+    const int row0 = q0 + qq * 32;                  // first query row of this warp
+    // one [32 x 64] box: wait until the previous store has read the staging buffer, fill it, hand it to the TMA unit
+    auto store_box = [&](const CUtensorMap* map, const uint4 (&chunks)[8], int col0) {
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+#pragma unroll
+      for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(mystage + ((g ^ (lane & 7)) << 4)) = chunks[g];
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_4d(map, mystage - (size_t)lane * 128, col0, row0, h, b);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    };
+    for (int j = grp; j < ntiles; j += 2) {
+      const int sl = j & 1;
+      if (!mbar_wait_bounded(t_full + sl, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) goto done;
+      tc_fence_after();
+      const uint32_t ts = tmem_base + (uint32_t)sl * 256u + lane_off;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[2][32], gv[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), sv[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), sv[1]);
+        tc_ld32(ts + 128u + (uint32_t)(half * 64), gv[0]);
+        tc_ld32(ts + 128u + (uint32_t)(half * 64 + 32), gv[1]);
+        tc_ld_wait();
+        if (half == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(t_empty + sl);
+        }
+        uint4 pc[8], dc[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint32_t pw[4], dw[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int idx = g * 8 + i * 2;
+            const float2 s2 = rounded_scores<T>(p.alpha, sv[idx >> 5][idx & 31], sv[idx >> 5][(idx & 31) + 1]);
+            const float2 g2 = rounded_scores<T>(1.f, gv[idx >> 5][idx & 31], gv[idx >> 5][(idx & 31) + 1]);
+            float y0 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb)), rl);
+            float y1 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb)), rl);
+            if (j == qi) {
+              const int c = half * 64 + idx;
+              if (c > r) y0 = 0.f;
+              if (c + 1 > r) y1 = 0.f;
+            }
+            pw[i] = pack2<T>(y0, y1);
+            dw[i] = pack2<T>(__fmaf_rn(y0, g2.x, -__fmul_rn(cdot, y0)), __fmaf_rn(y1, g2.y, -__fmul_rn(cdot, y1)));
+          }
+          pc[g] = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+          dc[g] = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        }
+        const int col0 = j * kAttnRows + half * 64;
+        store_box(&tmP, pc, col0);
+        store_box(&tmdS, dc, col0);
+      }
+    }
+    // zero tile that completes an odd count of written tiles to a multiple of 256 columns
+    if ((ntiles & 1) && ntiles * kAttnRows < p.seq && grp == (ntiles & 1)) {
+      uint4 z[8];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) z[g] = make_uint4(0, 0, 0, 0);
+      for (int half = 0; half < 2; ++half) {
+        store_box(&tmP, z, ntiles * kAttnRows + half * 64);
+        store_box(&tmdS, z, ntiles * kAttnRows + half * 64);
+      }
+    }
+    tc_fence_before();
+  }
+done:
+  if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -308,7 +571,7 @@ static int encode_bshd(CUtensorMap* map, uint64_t ptr, int batch, int seq, int h
   return CACTI_B200_OK;
 }
 
-constexpr size_t kAttnFwdSmem = 1024 + 6 * (size_t)kTileBytes + 256;
+constexpr size_t kAttnFwdSmem = 1024 + 7 * (size_t)kTileBytes + 256 + 2 * kAttnRows * sizeof(float);
 
 template <typename T>
 static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t k, uint64_t v, int batch, int seq, int heads,
@@ -331,6 +594,37 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
   kern<<<(unsigned)grid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
                                                            reinterpret_cast<float*>(stats), p);
+  return check_launch();
+}
+
+constexpr size_t kAttnBwdSmem = 1024 + 6 * (size_t)kTileBytes + 1024 + 8 * 4096;
+
+template <typename T>
+static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t k, uint64_t v, uint64_t dctx, uint64_t ctx,
+                                  uint64_t stats, int batch, int seq, int heads, int head_dim, float alpha, cudaStream_t st) {
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  int rc = encode_bshd(&tmQ, q, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmK, k, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmV, v, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmdO, dctx, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  // P and dS: [batch, seq, heads, seq] written as [32 rows][64 columns] boxes
+  CUtensorMap tmP, tmdS;
+  if (!rc) rc = encode_bshd(&tmP, pp, batch, seq, heads, seq, 64, 32, bf16);
+  if (!rc) rc = encode_bshd(&tmdS, ds, batch, seq, heads, seq, 64, 32, bf16);
+  if (rc) return rc;
+  AttnParams p;
+  p.batch = batch; p.seq = seq; p.heads = heads; p.head_dim = head_dim; p.alpha = alpha;
+  p.idesc_s = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(128 >> 3) << 17) |
+              ((uint32_t)(128 >> 4) << 24);
+  p.idesc_pv = p.idesc_s;
+  auto kern = attention_bwd_prep_kernel<T>;
+  static bool attr_set = false;
+  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnBwdSmem); attr_set = true; }
+  const long long grid = (long long)batch * heads * (seq / kAttnRows);
+  kern<<<(unsigned)grid, kAttnThreads, kAttnBwdSmem, st>>>(tmQ, tmK, tmV, tmdO, tmP, tmdS,
+                                                           reinterpret_cast<const T*>(ctx), reinterpret_cast<const T*>(dctx),
+                                                           reinterpret_cast<const float*>(stats), p);
   return check_launch();
 }
 
@@ -376,5 +670,25 @@ int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b
   if (dtype == CACTI_B200_R_16F)
     return attention_fwd_run<__half>(ctx, stats, q, k, v, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha, st);
   return attention_fwd_run<__nv_bfloat16>(ctx, stats, q, k, v, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha, st);
+}
+
+int cacti_b200_attention_bwd_prep(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b200_dptr q, cacti_b200_dptr k,
+                                  cacti_b200_dptr v, cacti_b200_dptr dctx, cacti_b200_dptr ctx, cacti_b200_dptr stats,
+                                  int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha, int dtype,
+                                  cacti_b200_stream stream) {
+  using namespace cb;
+  if (batch < 0 || seq < 0 || heads < 0 || head_dim <= 0) return CACTI_B200_ERR_INVALID_VALUE;
+  if (dtype != CACTI_B200_R_16F && dtype != CACTI_B200_R_16BF) return CACTI_B200_ERR_DTYPE;
+  if (head_dim > kAttnHd || head_dim % 4 || seq % kAttnRows || batch * heads * (seq / kAttnRows) > 0x7fffffffLL)
+    return CACTI_B200_ERR_SHAPE;
+  if (batch == 0 || seq == 0 || heads == 0) return CACTI_B200_OK;
+  if (!p || !ds || !q || !k || !v || !dctx || !ctx || !stats || ((p | ds | q | k | v | dctx) & 15) || (ctx & 7) || (stats & 7))
+    return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == CACTI_B200_R_16F)
+    return attention_bwd_prep_run<__half>(p, ds, q, k, v, dctx, ctx, stats, (int)batch, (int)seq, (int)heads, (int)head_dim,
+                                          alpha, st);
+  return attention_bwd_prep_run<__nv_bfloat16>(p, ds, q, k, v, dctx, ctx, stats, (int)batch, (int)seq, (int)heads,
+                                               (int)head_dim, alpha, st);
 }
 }

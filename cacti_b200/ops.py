@@ -313,3 +313,15 @@ def attention_fwd(q_pad, k_pad, v_pad, head_dim, alpha, ctx=None, stats=None):
     check(lib().cacti_b200_attention_fwd(_ptr(ctx), _ptr(stats), _ptr(q_pad), _ptr(k_pad), _ptr(v_pad), b, s, h, head_dim,
                                          alpha, _dt(q_pad), _stream()), "attention_fwd")
     return ctx, stats
+
+
+def attention_bwd_prep(q_pad, k_pad, v_pad, dctx_pad, ctx, stats, alpha, p=None, ds=None):
+    """(P, dS) [B, S, H, S] for the three hinted block matmuls of the attention adjoint; nothing beyond the trimmed-fill
+    bound of each row is written."""
+    b, s, h, _ = q_pad.shape
+    p = torch.empty(b, s, h, s, dtype=q_pad.dtype, device=q_pad.device) if p is None else p
+    ds = torch.empty(b, s, h, s, dtype=q_pad.dtype, device=q_pad.device) if ds is None else ds
+    check(lib().cacti_b200_attention_bwd_prep(_ptr(p), _ptr(ds), _ptr(q_pad), _ptr(k_pad), _ptr(v_pad), _ptr(dctx_pad),
+                                              _ptr(ctx), _ptr(stats), b, s, h, ctx.shape[-1], alpha, _dt(q_pad), _stream()),
+          "attention_bwd_prep")
+    return p, ds

@@ -327,6 +327,21 @@ int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b
                              cacti_b200_dptr v, int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha,
                              int dtype, cacti_b200_stream stream);
 
+/* Backward companion of cacti_b200_attention_fwd: rebuilds, tile by tile on the tensor cores, the probabilities and the
+ * score adjoints that the reference obtains from its stored scores (block matmul dP = dO V^T, then
+ * InnerSoftmaxPostAdj with the recomputed softmax, src/thunk/op.rs:3376-3457):
+ *   y = exp(s - m) / l,  P = T(y),  dS = T(y * T(dP) - c * y),  s = T(alpha q.k),  c = dO . O
+ * (c equals sum_j y_j dP_j in exact arithmetic; taking it from the stored context row removes the pass over the whole
+ * row).  p, ds: [batch, seq, heads, seq]; entries above the diagonal are written (as zeros) up to the bound B of
+ * CACTI_B200_MASK_CAUSAL_TRIM and left untouched beyond it: feed them to cacti_b200_gemm_strided_batched_tri with
+ * CACTI_B200_TRI_A_UPPER (dV = P^T dO, dK = alpha dS^T Q) and CACTI_B200_TRI_A_LOWER (dQ = alpha dS K).
+ * q, k, v, dctx: [batch, seq, heads, 128] zero-padded (cacti_b200_block_pad); ctx: [batch, seq, heads, head_dim] and
+ * stats as produced by cacti_b200_attention_fwd.  Same shape limits.  No single counterpart in the reference. */
+int cacti_b200_attention_bwd_prep(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b200_dptr q, cacti_b200_dptr k,
+                                  cacti_b200_dptr v, cacti_b200_dptr dctx, cacti_b200_dptr ctx, cacti_b200_dptr stats,
+                                  int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha, int dtype,
+                                  cacti_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,8 +81,10 @@ def test_attention_fwd_bf16_and_errors(cuda):
     sc = R.bf16_round((np.float32(alpha) * np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(np.float32))).astype(np.float64)
     sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
     e = np.exp(sc - sc.max(-1, keepdims=True))
-    ref = np.transpose(np.einsum("bhqk,bhkd->bhqd", e / e.sum(-1, keepdims=True), vf), (0, 2, 1, 3))
-    assert_close(host(ctx), ref, "bfloat16", "bf16 fused attention", floor_frac=1.0)
+    pn = e / e.sum(-1, keepdims=True)
+    ref = np.transpose(np.einsum("bhqk,bhkd->bhqd", pn, vf), (0, 2, 1, 3))
+    mag = np.transpose(np.einsum("bhqk,bhkd->bhqd", pn, np.abs(vf)), (0, 2, 1, 3))
+    assert_close(host(ctx), ref, "bfloat16", "bf16 fused attention", floor_frac=1.0, floor_abs=mag)
     L = capi.lib()
     P = qp.data_ptr()
     assert L.cacti_b200_attention_fwd(P, P, P, P, P, 1, 200, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_SHAPE      # seq % 128
@@ -90,3 +92,67 @@ def test_attention_fwd_bf16_and_errors(cuda):
     assert L.cacti_b200_attention_fwd(P, P, P, P, P, 1, 256, 2, 100, 0.1, capi.R_32F, None) == capi.ERR_DTYPE
     assert L.cacti_b200_attention_fwd(P, P, P, P, P, 0, 256, 2, 100, 0.1, capi.R_16F, None) == capi.OK
     assert L.cacti_b200_attention_fwd(0, P, P, P, P, 1, 256, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_INVALID_VALUE
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(1, 128, 1, 128), (2, 256, 3, 100), (1, 640, 2, 64), (2, 1024, 2, 100)])
+def test_attention_bwd_prep(cuda, bsz, s, h, hd):
+    """P and dS against the unfused entry points (scores and dP through HBM, softmax_fwd_bwd), inside the bound up to
+    which they are specified; nothing is written beyond it; the three hinted block matmuls of the adjoint accept them."""
+    q, k, v, do = (dev(R.normal(90 + i, (bsz, s, h, hd), np.float16)) for i in range(4))
+    alpha = float(1.0 / np.sqrt(hd))
+    qp, kp, vp, dop = (ops.block_pad(t, 128) for t in (q, k, v, do))
+    ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    p = torch.full((bsz, s, h, s), float("nan"), dtype=torch.float16, device="cuda")
+    ds = torch.full_like(p, float("nan"))
+    ops.attention_bwd_prep(qp, kp, vp, dop, ctx, stats, alpha, p=p, ds=ds)
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+    sc = ops.block_gemm(q, k, False, True, alpha=alpha)
+    dp = ops.block_gemm(do, v, False, True)
+    p_ref, ds_ref = ops.softmax_fwd_bwd(sc.view(-1, s), dp.view(-1, s), (h, s, 0))
+    p_ref, ds_ref = p_ref.view(bsz, s, h, s), ds_ref.view(bsz, s, h, s)
+    r = torch.arange(s, device="cuda")
+    bound = r // 256 * 256 + 256
+    written = (r[None, :] < bound[:, None])[None, :, None, :]
+    assert torch.isnan(p[~written.expand_as(p)]).all() and torch.isnan(ds[~written.expand_as(p)]).all()
+    pw, dsw = torch.where(written, p, 0), torch.where(written, ds, 0)
+    assert not torch.isnan(pw).any() and not torch.isnan(dsw).any()
+    keep = (r[None, :] <= r[:, None])[None, :, None, :]
+    assert (pw[~keep.expand_as(p)] == 0).all() and (dsw[~keep.expand_as(p)] == 0).all()
+    # P: the same formula on the same rounded scores; the row sum is accumulated in another order
+    assert_close(host(pw), host(p_ref).astype(np.float64), "float16", "P", rtol=2e-3)
+    # dS = y (dP - c).  c is dO . O here and sum_j y_j T(dP_j) in the unfused chain: each carries the half-ulp rounding
+    # of its 16-bit inputs (O there, dP here), so the two differ by up to an ulp of the row's largest |dP|, times y
+    pr, dpr = host(p_ref).astype(np.float64), host(dp).astype(np.float64)
+    c = (pr * dpr).sum(-1, keepdims=True)
+    mag = pr * (np.abs(dpr) + np.abs(c) + np.abs(np.where(host(keep.expand_as(p)), dpr, 0)).max(-1, keepdims=True))
+    assert_close(host(dsw), host(ds_ref).astype(np.float64), "float16", "dS", rtol=4e-3, floor_abs=mag)
+    # the adjoint's block matmuls on the trimmed tensors (NaN beyond the bound would poison them if read)
+    dv = ops.block_gemm(p, do, True, False, tri=capi.TRI_A_UPPER)
+    dq = ops.block_gemm(ds, k, False, False, alpha=alpha, tri=capi.TRI_A_LOWER)
+    dk = ops.block_gemm(ds, q, True, False, alpha=alpha, tri=capi.TRI_A_UPPER)
+    assert_close(host(dv), host(ops.block_gemm(p_ref, do, True, False)).astype(np.float64), "float16", "dV", rtol=4e-3, floor_frac=1.0)
+    # dQ and dK: c = dO . O and the unfused chain's sum_j y_j T(dP_j) are two roundings of the same number, so the two
+    # chains differ by rounding noise that no element-wise bound captures on rows with one or two keys (the unfused
+    # dS of row 0 is exactly 0).  Both are measured against the exact adjoint (f64, no intermediate rounding): the
+    # fused chain must be as close to it as the unfused one.
+    qf, kf, vf, dof = (np.transpose(host(t).astype(np.float64), (0, 2, 1, 3)) for t in (q, k, v, do))
+    sce = alpha * np.einsum("bhqd,bhkd->bhqk", qf, kf)
+    sce = np.where(np.tril(np.ones((s, s), bool)), sce, -np.inf)
+    pe = np.exp(sce - sce.max(-1, keepdims=True))
+    pe /= pe.sum(-1, keepdims=True)
+    dpe = np.einsum("bhqd,bhkd->bhqk", dof, vf)
+    dse = pe * (dpe - (pe * dpe).sum(-1, keepdims=True))
+    exact = {"dq": alpha * np.einsum("bhqk,bhkd->bhqd", dse, kf), "dk": alpha * np.einsum("bhqk,bhqd->bhkd", dse, qf),
+             "dv": np.einsum("bhqk,bhqd->bhkd", pe, dof)}
+    unfused = {"dq": ops.block_gemm(ds_ref, k, False, False, alpha=alpha), "dk": ops.block_gemm(ds_ref, q, True, False, alpha=alpha),
+               "dv": ops.block_gemm(p_ref, do, True, False)}
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        ex = np.transpose(exact[name], (0, 2, 1, 3))
+        e_f = host(got).astype(np.float64) - ex
+        e_u = host(unfused[name]).astype(np.float64) - ex
+        rms_f, rms_u = np.sqrt((e_f ** 2).mean()), np.sqrt((e_u ** 2).mean())
+        scale = np.sqrt((ex ** 2).mean())
+        assert rms_f <= 1.5 * rms_u + 1e-4 * scale, (name, rms_f, rms_u)
+        assert np.abs(e_f).max() <= 3 * np.abs(e_u).max() + 2e-3 * scale, (name, np.abs(e_f).max(), np.abs(e_u).max())
