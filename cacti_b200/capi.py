@@ -63,10 +63,11 @@ SIGNATURES = {
     "cacti_b200_attention_bwd_prep": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _st]),
     "cacti_b200_gemm_strided_batched_tri": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int,
                                                    C.POINTER(_f32), C.POINTER(_f32), _i64, _i64, _i64, _i64, _i64, _i64,
-                                                   _i64, _i64, _int, _i64, _int, _p, _sz, _st]),
+                                                   _i64, _i64, _int, _i64, _int, _int, _p, _sz, _st]),
 }
 
 TRI_NONE, TRI_C_LOWER, TRI_A_LOWER, TRI_A_UPPER = 0, 1, 2, 3
+OPERAND_A_PADDED, OPERAND_B_PADDED = 1, 2
 
 _lib = None
 

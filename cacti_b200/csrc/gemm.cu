@@ -587,12 +587,20 @@ int g_gemm_pair = 1;  // 1: 256-wide tiles may run as two-SM (cta_group::2) 256 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
                     long long ldc, long long cso, long long csi, int nbi, int nbo, float alpha, float beta,
-                    int tri, long long diag, uint64_t ws, size_t ws_bytes, cudaStream_t st) {
+                    int tri, long long diag, int opflags, uint64_t ws, size_t ws_bytes, cudaStream_t st) {
   const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
   size_t ws_off = 0;
   // repack what TMA cannot address
   for (Operand* o : {&A, &B}) {
-    if (tma_ok(*o, nbi, nbo)) continue;
+    if (tma_ok(*o, nbi, nbo)) {
+      // rows stored zero-padded to a multiple of 64 elements: let the tensor map cover the padding, so that no box
+      // is partly out of range (the slow path of the TMA unit) and nothing has to be repacked
+      if (opflags & (o == &A ? CACTI_B200_OPERAND_A_PADDED : CACTI_B200_OPERAND_B_PADDED)) {
+        if (o->ld < packed_cols(o->cols)) return CACTI_B200_ERR_INVALID_VALUE;
+        o->map_cols = packed_cols(o->cols);
+      }
+      continue;
+    }
     const long long nblk = (long long)((o->has_j ? nbi : 1)) * (o->has_i ? nbo : 1);
     const size_t need = packed_bytes(o->rows, o->cols, nblk);
     if (!ws || (ws & 255) || ws_off + need > ws_bytes) return CACTI_B200_ERR_WORKSPACE;
@@ -724,7 +732,7 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
 static int gemm_entry(uint64_t c, uint64_t a, uint64_t b, long long m, long long n, long long k, long long lda,
                       long long ldb, long long ldc, int ta, int tb, const float* alpha, const float* beta, int nbo, int nbi,
                       long long sao, long long sai, long long sbo, long long sbi, long long sco, long long sci, int tri,
-                      long long diag, int dtype, uint64_t ws, size_t ws_bytes, void* stream) {
+                      long long diag, int opflags, int dtype, uint64_t ws, size_t ws_bytes, void* stream) {
   if (m < 0 || n < 0 || k < 0 || nbo < 0 || nbi < 0 || !alpha || !beta) return CACTI_B200_ERR_INVALID_VALUE;
   if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
   if ((ta & ~1) || (tb & ~1)) return CACTI_B200_ERR_INVALID_VALUE;
@@ -745,8 +753,8 @@ static int gemm_entry(uint64_t c, uint64_t a, uint64_t b, long long m, long long
   // A as [m][k] is K-major; as [k][m] it is MN-major.  B as [n][k] (tb = 1) is K-major; as [k][n] MN-major.
   const bool a_mn = ta != 0, b_mn = tb == 0;
   if (dtype == CACTI_B200_R_16F)
-    return gemm_run<__half>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, ws, ws_bytes, st);
-  return gemm_run<__nv_bfloat16>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, ws, ws_bytes, st);
+    return gemm_run<__half>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, opflags, ws, ws_bytes, st);
+  return gemm_run<__nv_bfloat16>(c, A, B, a_mn, b_mn, m, n, k, ldc, sco, sci, nbi, nbo, *alpha, *beta, tri, diag, opflags, ws, ws_bytes, st);
 }
 
 }  // namespace cb
@@ -768,7 +776,7 @@ int cacti_b200_gemm(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int
                     int64_t ldb, int64_t ldc, int trans_a, int trans_b, const float* alpha, const float* beta, int dtype,
                     cacti_b200_dptr workspace, size_t workspace_bytes, cacti_b200_stream stream) {
   return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, 1, 1, 0, 0, 0, 0, 0, 0,
-                        CACTI_B200_TRI_NONE, 0, dtype, workspace, workspace_bytes, stream);
+                        CACTI_B200_TRI_NONE, 0, 0, dtype, workspace, workspace_bytes, stream);
 }
 
 int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n,
@@ -780,7 +788,7 @@ int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_
   if (batch_outer > 0x7fffffffLL || batch_inner > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
   return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, (int)batch_outer, (int)batch_inner,
                         stride_a_outer, stride_a_inner, stride_b_outer, stride_b_inner, stride_c_outer, stride_c_inner,
-                        CACTI_B200_TRI_NONE, 0, dtype, workspace, workspace_bytes, stream);
+                        CACTI_B200_TRI_NONE, 0, 0, dtype, workspace, workspace_bytes, stream);
 }
 
 int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n,
@@ -788,11 +796,12 @@ int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, ca
                                         const float* alpha, const float* beta, int64_t batch_outer, int64_t batch_inner,
                                         int64_t stride_a_outer, int64_t stride_a_inner, int64_t stride_b_outer,
                                         int64_t stride_b_inner, int64_t stride_c_outer, int64_t stride_c_inner, int tri_mode,
-                                        int64_t diag, int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
+                                        int64_t diag, int operand_flags, int dtype, cacti_b200_dptr workspace,
+                                        size_t workspace_bytes,
                                         cacti_b200_stream stream) {
   if (batch_outer > 0x7fffffffLL || batch_inner > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
   return cb::gemm_entry(c, a, b, m, n, k, lda, ldb, ldc, trans_a, trans_b, alpha, beta, (int)batch_outer, (int)batch_inner,
                         stride_a_outer, stride_a_inner, stride_b_outer, stride_b_inner, stride_c_outer, stride_c_inner,
-                        tri_mode, diag, dtype, workspace, workspace_bytes, stream);
+                        tri_mode, diag, operand_flags, dtype, workspace, workspace_bytes, stream);
 }
 }

@@ -14,6 +14,9 @@ arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph,
     not computed (the masked softmax never reads them) and products with the exact zeros of P and dS are skipped;
     every value that is used is bit-identical to the full product.  The softmax zero-fills the masked tails of P
     and dS only as far as those matmuls read (CACTI_B200_MASK_CAUSAL_TRIM).
+  * by default attention runs fused (cacti_b200_attention_fwd / _bwd_prep): scores and probabilities stay on chip in
+    the forward, and the backward rebuilds P and dS per tile instead of reading stored scores; `attention="unfused"`
+    keeps the reference's op sequence.
 Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
 """
 from __future__ import annotations
@@ -82,8 +85,14 @@ class TrainStep:
     gradients are complete, and with i = cfg.layers as soon as the output head's gradients are (the hook a
     data-parallel reducer attaches to; the embedding gradient is complete when the call returns)."""
 
-    def __init__(self, cfg: LlamaShape, params, batch: int, loss_tokens: int | None = None):
+    def __init__(self, cfg: LlamaShape, params, batch: int, loss_tokens: int | None = None, attention: str = "auto"):
         self.cfg, self.P, self.B = cfg, params, batch
+        # "fused": attention_fwd / attention_bwd_prep (scores never reach HBM); "unfused": the reference's op sequence,
+        # block matmul - softmax - block matmul; "auto": fused when the shape allows it
+        can_fuse = cfg.seq % 128 == 0 and cfg.head_dim <= 128 and cfg.head_dim % 4 == 0
+        if attention == "fused" and not can_fuse:
+            raise ValueError("fused attention needs seq % 128 == 0, head_dim <= 128 and head_dim % 4 == 0")
+        self.fused = can_fuse if attention == "auto" else attention == "fused"
         dev = params["embed"].device
         self.dev = dev
         self.T = batch * cfg.seq
@@ -103,9 +112,9 @@ class TrainStep:
         self.launches += 1
         return ops.gemm(a, b, ta, tb, beta=beta, c=c)
 
-    def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0):
-        self.launches += 3
-        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws, tri=tri)
+    def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0, b_valid=None):
+        self.launches += 3 if b_valid is None else 1       # unaligned operands are repacked first; padded ones are not
+        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws, tri=tri, b_valid=b_valid)
 
     def forward_backward(self, tokens, targets, grads, on_layer_done=None):
         cfg, P, B, T = self.cfg, self.P, self.B, self.T
@@ -128,16 +137,24 @@ class TrainStep:
             q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
             k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
             v = self._mm(n1, Lw["v"], False, True)
-            sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha, TRI_C_LOWER)   # [B,S,H,S]
-            p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
-            ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)
-            del p
+            if self.fused:
+                # head dimension zero-padded to 128 once; the padded copies also serve the backward pass
+                q, k, v = (ops.block_pad(t.view(B, S, H, hd), 128) for t in (q, k, v))
+                ctx, sc = ops.attention_fwd(q, k, v, hd, alpha)               # sc: the row statistics (m, l)
+                ctx = ctx.view(T, D)
+                self.launches += 4
+            else:
+                sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha, TRI_C_LOWER)   # [B,S,H,S]
+                p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
+                ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)
+                del p
+                self.launches += 1
             n2, x_mid = ops.add_rmsnorm_fwd(x, self._mm(ctx, Lw["o"], False, True), Lw["post_norm"], cfg.eps)
             up = self._mm(n2, Lw["up"], False, True)
             gate = self._mm(n2, Lw["gate"], False, True)
             h = ops.swiglu_fwd(gate, up)
             branch = self._mm(h, Lw["down"], False, True)
-            self.launches += 6
+            self.launches += 5
             saved.append((x, n1, q, k, v, sc, ctx, x_mid, n2, up, gate, h))
             x = x_mid
         nf, x = ops.add_rmsnorm_fwd(x, branch, P["head_norm"], cfg.eps)
@@ -174,14 +191,24 @@ class TrainStep:
             # attention branch: x_mid = x_in + ctx Wo^T
             self._mm(dx, ctx, True, False, c=G["o"])
             dctx = self._mm(dx, Lw["o"], False, False)
-            dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True, tri=TRI_C_LOWER)  # dctx V^T
-            # one fused pass over (S, dP) yields the recomputed probabilities and dS together
-            p, ds = ops.softmax_fwd_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
-            del dp, sc
-            dv = self._bmm(p.view(B, S, H, S), dctx.view(B, S, H, hd), True, False, tri=TRI_A_UPPER).view(T, D)   # P^T dctx
+            if self.fused:
+                # P and dS are rebuilt from q, k, v, dctx and the row statistics; q, k, v here are the padded copies
+                dctx = ops.block_pad(dctx.view(B, S, H, hd), 128)
+                p, ds = ops.attention_bwd_prep(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha)
+                self.launches += 2
+                bv = hd
+            else:
+                dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True, tri=TRI_C_LOWER)  # dctx V^T
+                # one fused pass over (S, dP) yields the recomputed probabilities and dS together
+                p, ds = ops.softmax_fwd_bwd(sc.view(B * S * H, S), dp.view(B * S * H, S), mask)
+                del dp
+                self.launches += 1
+                dctx, q, k, bv = dctx.view(B, S, H, hd), q.view(B, S, H, hd), k.view(B, S, H, hd), None
+            del sc
+            dv = self._bmm(p.view(B, S, H, S), dctx, True, False, tri=TRI_A_UPPER, b_valid=bv).view(T, D)      # P^T dctx
             del p, dctx
-            dq = self._bmm(ds.view(B, S, H, S), k.view(B, S, H, hd), False, False, alpha, TRI_A_LOWER)  # dS K
-            dk = self._bmm(ds.view(B, S, H, S), q.view(B, S, H, hd), True, False, alpha, TRI_A_UPPER)   # dS^T Q
+            dq = self._bmm(ds.view(B, S, H, S), k, False, False, alpha, TRI_A_LOWER, b_valid=bv)               # dS K
+            dk = self._bmm(ds.view(B, S, H, S), q, True, False, alpha, TRI_A_UPPER, b_valid=bv)                # dS^T Q
             del ds
             dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
             dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)
@@ -195,7 +222,7 @@ class TrainStep:
             ops.rmsnorm_bwd(x_in, Lw["pre_norm"], dn1, cfg.eps, dx=dx, dgamma=G["pre_norm"], beta_dx=1,
                             workspace=self.norm_ws)
             del dn1
-            self.launches += 11
+            self.launches += 10
             if on_layer_done is not None:
                 on_layer_done(li)
         ops.scatter_add_rows(dx, tokens, cfg.vocab, dtable=grads["embed"], status=self.status)

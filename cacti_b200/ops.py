@@ -263,14 +263,19 @@ def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
     return c
 
 
-def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None, tri=0, diag=0):
+def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None, tri=0, diag=0,
+               a_valid=None, b_valid=None):
     """Block matmul on the reference's 4-d layout [nrow, blk_rows, ncol, blk_cols] (packed); an operand with
     nrow or ncol equal to 1 is broadcast over that block dimension.  `tri` is a CACTI_B200_TRI_* hint
-    (capi.TRI_C_LOWER / TRI_A_LOWER / TRI_A_UPPER) for the matmuls around a causal softmax."""
+    (capi.TRI_C_LOWER / TRI_A_LOWER / TRI_A_UPPER) for the matmuls around a causal softmax.  a_valid / b_valid: the
+    operand's rows are zero-padded (block_pad) and only that many leading columns are data."""
     nrow, ncol = max(a.shape[0], b.shape[0]), max(a.shape[2], b.shape[2])
-    m = a.shape[3] if trans_a else a.shape[1]
-    k = a.shape[1] if trans_a else a.shape[3]
-    n = b.shape[1] if trans_b else b.shape[3]
+    a_cols = a.shape[3] if a_valid is None else a_valid
+    b_cols = b.shape[3] if b_valid is None else b_valid
+    m = a_cols if trans_a else a.shape[1]
+    k = a.shape[1] if trans_a else a_cols
+    n = b.shape[1] if trans_b else b_cols
+    flags = (1 if a_cols < a.shape[3] else 0) | (2 if b_cols < b.shape[3] else 0)
     c = torch.empty(nrow, m, ncol, n, dtype=a.dtype, device=a.device) if c is None else c
 
     def strides(t):
@@ -284,11 +289,11 @@ def block_gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, 
     if workspace is None:
         workspace = _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, nrow, ncol), a.device)
     al, be = _scalars(alpha, beta)
-    if tri:
+    if tri or flags:
         check(lib().cacti_b200_gemm_strided_batched_tri(_ptr(c), _ptr(a), _ptr(b), m, n, k, lda, ldb, ldc, int(trans_a),
                                                         int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci,
-                                                        int(tri), int(diag), _dt(a), _ptr(workspace), workspace.numel(),
-                                                        _stream()), "block_gemm_tri")
+                                                        int(tri), int(diag), flags, _dt(a), _ptr(workspace),
+                                                        workspace.numel(), _stream()), "block_gemm_tri")
         return c
     check(lib().cacti_b200_gemm_strided_batched(_ptr(c), _ptr(a), _ptr(b), m, n, k, lda, ldb, ldc, int(trans_a),
                                                 int(trans_b), al, be, nrow, ncol, sao, sai, sbo, sbi, sco, sci, _dt(a),

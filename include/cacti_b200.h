@@ -288,11 +288,16 @@ int cacti_b200_gemm_strided_batched(cacti_b200_dptr c, cacti_b200_dptr a, cacti_
  *                           CACTI_B200_MASK_CAUSAL_TRIM, so that region need not hold zeros, or anything.
  * Where C is specified it is bit-identical to the unhinted call (the skipped products are exact zeros).
  * r, c, kk are indices inside one block; diag = 0 for equal query and key lengths.
+ * operand_flags: CACTI_B200_OPERAND_A_PADDED / _B_PADDED say that every stored row of that operand is followed by
+ * zeros up to the next multiple of 64 elements (lda / ldb at least that; what cacti_b200_block_pad to 128 produces for
+ * head_dim 100): the matmul then reads the padding instead of repacking the operand or clipping its loads.
  * This entry point has no counterpart in the reference, whose cuBLAS call cannot express the structure. */
 #define CACTI_B200_TRI_NONE 0
 #define CACTI_B200_TRI_C_LOWER 1
 #define CACTI_B200_TRI_A_LOWER 2
 #define CACTI_B200_TRI_A_UPPER 3
+#define CACTI_B200_OPERAND_A_PADDED 1
+#define CACTI_B200_OPERAND_B_PADDED 2
 int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b,
                                         int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
                                         int trans_a, int trans_b, const float* alpha, const float* beta,
@@ -300,7 +305,7 @@ int cacti_b200_gemm_strided_batched_tri(cacti_b200_dptr c, cacti_b200_dptr a, ca
                                         int64_t stride_a_outer, int64_t stride_a_inner,
                                         int64_t stride_b_outer, int64_t stride_b_inner,
                                         int64_t stride_c_outer, int64_t stride_c_inner, int tri_mode, int64_t diag,
-                                        int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
+                                        int operand_flags, int dtype, cacti_b200_dptr workspace, size_t workspace_bytes,
                                         cacti_b200_stream stream);
 
 /* ---- A1 block padding and fused causal attention ------------------------------------------------------------

@@ -42,3 +42,36 @@ def test_reduced_step_matches_oracle(cuda, hd, heads):
         for name, g in grads["layers"][li].items():
             assert_close(host(g), ref_g["layers"][li][name], "float16", f"layer {li} {name}", rtol=2e-2, floor_frac=1.0)
     assert step.launches > 0
+
+
+@pytest.mark.parametrize("hd,heads,seq", [(100, 2, 256), (64, 3, 128)])
+def test_fused_attention_step_matches_oracle_and_unfused(cuda, hd, heads, seq):
+    """Same step with attention fused (scores never in HBM, P and dS rebuilt per tile in the backward): against the
+    composed CPU oracle at the tolerance of the unfused step, and against the unfused step itself."""
+    cfg = LS.LlamaShape(layers=2, d_model=hd * heads, heads=heads, head_dim=hd, ffn=96, vocab=160, seq=seq)
+    B = 2
+    P = LS.init_weights(cfg, cuda, seed=1, std=0.08)
+    for L in P["layers"]:
+        L["pre_norm"].copy_(dev(R.normal(52, (cfg.d_model,), np.float16, 0.1, 1.0)))
+        L["post_norm"].copy_(dev(R.normal(53, (cfg.d_model,), np.float16, 0.1, 1.0)))
+    tok = R.uniform_int(3, B * cfg.seq, cfg.vocab)
+    tgt = R.uniform_int(4, B * cfg.seq, cfg.vocab)
+    out = {}
+    for mode in ("fused", "unfused"):
+        grads = LS.zeros_like_params(P)
+        step = LS.TrainStep(cfg, P, B, attention=mode)
+        assert step.fused == (mode == "fused")
+        loss = step.forward_backward(dev(tok), dev(tgt), grads)
+        torch.cuda.synchronize()
+        assert host(step.status)[0] == 0
+        out[mode] = (float(host(loss)[0]), grads)
+    assert LS.TrainStep(cfg, P, B).fused                     # "auto" picks the fused path for this shape
+    ref_loss, ref_g = llama_oracle.step(_np_params(P), tok, tgt, cfg)
+    for mode, (loss, grads) in out.items():
+        assert abs(loss - float(ref_loss)) < 2e-3 * abs(float(ref_loss)), mode
+        for name in ("lm_head", "head_norm", "embed"):
+            assert_close(host(grads[name]), ref_g[name], "float16", f"{mode} {name}", rtol=2e-2, floor_frac=1.0)
+        for li in range(cfg.layers):
+            for name, g in grads["layers"][li].items():
+                assert_close(host(g), ref_g["layers"][li][name], "float16", f"{mode} layer {li} {name}", rtol=2e-2, floor_frac=1.0)
+    assert abs(out["fused"][0] - out["unfused"][0]) < 1e-3 * abs(out["unfused"][0])
