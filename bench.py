@@ -249,6 +249,36 @@ def other_thunks(torch, ops, peak):
     sec = time_thunk(lambda: ops.block_gemm(sc, v, False, False, c=ctx, workspace=ws), 5, 3, torch)
     out["block_gemm PV[8x2048x32x100]"] = {"TFLOP/s": round(2 * B * H * S * S * hd / sec / 1e12, 1), "GB/s": round(nbytes / sec / 1e9, 1),
                                            "frac_of_peak": round(nbytes / sec / 1e9 / peak, 3), "us": round(sec * 1e6, 1), "launches_per_step": 2}
+    # the same two block matmuls with the causal-structure hints the training step passes
+    from cacti_b200 import capi
+    sec = time_thunk(lambda: ops.block_gemm(q, k, False, True, alpha=0.1, c=sc, workspace=ws, tri=capi.TRI_C_LOWER), 5, 3, torch)
+    out["block_gemm QK^T, C_LOWER hint[8x2048x32x100]"] = {"us": round(sec * 1e6, 1), "launches_per_step": 3}
+    pz = torch.tril(torch.ones(S, S, device="cuda", dtype=torch.float16))[None, :, None, :].expand(B, S, H, S).contiguous()
+    sec = time_thunk(lambda: ops.block_gemm(pz, v, False, False, c=ctx, workspace=ws, tri=capi.TRI_A_LOWER), 5, 3, torch)
+    out["block_gemm PV, A_LOWER hint[8x2048x32x100]"] = {"us": round(sec * 1e6, 1), "launches_per_step": 2}
+    del sc, pz
+    # A1 fused attention (what the training step runs by default): q, k, v padded to 128 columns; HBM traffic is
+    # q, k, v, ctx and the row statistics; "TFLOP/s" counts the 2 * 2 * S^2/2 * hd useful flops per (batch, head)
+    qp, kp, vp = (ops.block_pad(t, 128) for t in (q, k, v))
+    st = torch.empty(B, H, S, 2, device="cuda")
+    sec = time_thunk(lambda: ops.attention_fwd(qp, kp, vp, hd, 0.1, ctx=ctx, stats=st), 10, 3, torch)
+    useful = 2 * 2 * B * H * (S * S / 2) * hd
+    out["attention_fwd[8x2048x32x100]"] = {"us": round(sec * 1e6, 1), "TFLOP/s_useful": round(useful / sec / 1e12, 1), "launches_per_step": 1}
+    do = rnd(B, S, H, hd)
+    dop = ops.block_pad(do, 128)
+    pp = torch.empty(B, S, H, S, dtype=torch.float16, device="cuda")
+    dss = torch.empty_like(pp)
+    sec = time_thunk(lambda: ops.attention_bwd_prep(qp, kp, vp, dop, ctx, st, 0.1, p=pp, ds=dss), 5, 3, torch)
+    wbytes = 2 * B * H * (S * S // 2) * 2                       # P and dS, lower triangles
+    out["attention_bwd_prep[8x2048x32x100]"] = {"us": round(sec * 1e6, 1), "GB/s_written": round(wbytes / sec / 1e9, 1), "launches_per_step": 1}
+    sec = time_thunk(lambda: ops.block_pad(q, 128, out=qp), 10, 3, torch)
+    report("block_pad[8x2048x32x100->128]", sec, B * S * H * (100 + 128) * 2, 1)
+    del pp, dss
+    # residual add fused into the norm (one pass over [16384, 3200] saved per norm)
+    a_, b_, g_ = rnd(16384, 3200), rnd(16384, 3200), rnd(3200)
+    y_, t_ = torch.empty_like(a_), torch.empty_like(a_)
+    sec = time_thunk(lambda: ops.add_rmsnorm_fwd(a_, b_, g_, 1e-6, y=y_, total=t_), 20, 5, torch)
+    report("add_rmsnorm_fwd[16384x3200,f16]", sec, 4 * 16384 * 3200 * 2, 1)
     return out
 
 
