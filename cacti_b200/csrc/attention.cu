@@ -103,11 +103,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* part = reinterpret_cast<float*>(bars + 20);       // [2 groups][128 rows] partial max, then partial sum
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // heaviest query tiles (most key tiles under the diagonal) are launched first
-  const int nq = p.seq / kAttnRows, bh_count = p.batch * p.heads;
-  const int qi = nq - 1 - (int)(blockIdx.x / bh_count);
-  const int bh = (int)(blockIdx.x % bh_count);
-  const int b = bh / p.heads, h = bh - b * p.heads;
+  // Launch order: batch element slowest, then query tile (heaviest first), then head.  The CTAs that run at the same
+  // time then belong to one or two batch elements, whose K and V (2 x 8 MB at 2048 x 32 x 128) stay in L2 while all 16
+  // query tiles stream them, and the tiles that finish the kernel are light ones.  (Query tile slowest over the whole
+  // batch: K and V no longer fit L2 between uses.  (batch, head) slowest: the last CTAs are heavy and leave a tail.)
+  const int nq = p.seq / kAttnRows;
+  const int b = (int)(blockIdx.x / (nq * p.heads));
+  const int rem = (int)(blockIdx.x % (nq * p.heads));
+  const int qi = nq - 1 - rem / p.heads;
+  const int h = rem % p.heads;
   const int ntiles = qi + 1;                       // key tiles 0 .. qi
   const int q0 = qi * kAttnRows;
 
@@ -367,10 +371,11 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   unsigned char* stage = sV + 2 * kTileBytes + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int nq = p.seq / kAttnRows, bh_count = p.batch * p.heads;
-  const int qi = nq - 1 - (int)(blockIdx.x / bh_count);
-  const int bh = (int)(blockIdx.x % bh_count);
-  const int b = bh / p.heads, h = bh - b * p.heads;
+  const int nq = p.seq / kAttnRows;                // launch order as in the forward kernel
+  const int b = (int)(blockIdx.x / (nq * p.heads));
+  const int rem = (int)(blockIdx.x % (nq * p.heads));
+  const int qi = nq - 1 - rem / p.heads;
+  const int h = rem % p.heads;
   const int ntiles = qi + 1;
   const int q0 = qi * kAttnRows;
 

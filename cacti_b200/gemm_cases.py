@@ -1,4 +1,5 @@
-"""GEMM workloads for cacti_b200.profile_cases (dense projection shapes and the two attention block matmuls)."""
+"""Tensor-core workloads for cacti_b200.profile_cases: dense projection shapes, the two attention block matmuls and the
+fused attention kernels (attn_fwd, attn_bwd)."""
 import torch
 
 from . import ops
@@ -30,4 +31,13 @@ def make(case, rnd, batch=2):
         c = torch.empty(bsz, s, h, hd, dtype=torch.float16, device="cuda")
         ws = torch.empty(ops.lib().cacti_b200_gemm_workspace_bytes(s, hd, s, bsz, h), dtype=torch.uint8, device="cuda")
         return lambda: ops.block_gemm(pr, v, False, False, c=c, workspace=ws)
+    if case in ("attn_fwd", "attn_bwd"):
+        alpha = hd ** -0.5
+        q, kk, v, do = (ops.block_pad(rnd(bsz, s, h, hd), 128) for _ in range(4))
+        ctx, st = ops.attention_fwd(q, kk, v, hd, alpha)
+        if case == "attn_fwd":
+            return lambda: ops.attention_fwd(q, kk, v, hd, alpha, ctx=ctx, stats=st)
+        pp = torch.empty(bsz, s, h, s, dtype=torch.float16, device="cuda")
+        ds = torch.empty_like(pp)
+        return lambda: ops.attention_bwd_prep(q, kk, v, do, ctx, st, alpha, p=pp, ds=ds)
     raise SystemExit(f"unknown gemm case {case}")

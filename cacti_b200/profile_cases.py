@@ -4,7 +4,7 @@
 
 cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16), softmax_full (config 2), nll (2048 x 32000 f16),
 rmsnorm (16384 x 3200 f16), rope (16384 x 32 x 100 f16), swiglu (4096 x 8640 f16),
-gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200 f16), qk / pv (--batch sequences of config 5),
+gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200 f16), qk / pv / attn_fwd / attn_bwd (--batch sequences of config 5),
 train_step (one config-5 forward+backward over --batch sequences; only for the single-pass launch list).
 Inputs are larger than the 126 MB L2 so DRAM counters are meaningful.
 """
@@ -69,7 +69,7 @@ def main():
         tok = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
         tgt = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
         fn = lambda: step.forward_backward(tok, tgt, grads)
-    elif a.case.startswith("gemm_") or a.case in ("qk", "pv"):
+    elif a.case.startswith("gemm_") or a.case in ("qk", "pv", "attn_fwd", "attn_bwd"):
         from . import gemm_cases
         fn = gemm_cases.make(a.case, rnd, a.batch)
     else:
