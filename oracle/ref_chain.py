@@ -438,6 +438,30 @@ def ref_block_gemm(a, b, ta=False, tb=False, alpha=1.0, beta=0.0, c=None):
     return outs.astype(T)
 
 
+def ref_causal_attention(q, k, v, alpha, round_scores=None):
+    """The attention block of one decoder layer as the reference stages it (src/librarium/llama.rs:501-507):
+    block_matmul_scale (scores = alpha q.k, fp32 accumulation, stored in the operand type), cast to f32,
+    block_causal_attention_mask (src/thunk/op.rs:4189-4278), inner_softmax (:3257-3383), lossy_cast, block_matmul.
+    q, k, v: [B, S, H, hd].  Computed in f64 from the rounded scores, with no rounding of the probabilities, so that
+    both the reference's chain (which rounds exp / sum) and a fused kernel (which may round exp) can be held to it.
+    round_scores: function rounding an f32 array to the storage type (default: the dtype of q).
+    Returns (ctx [B, S, H, hd] f64, row maximum [B, H, S], row sum of exp(s - max) [B, H, S],
+    sum_j p_j |v_j| [B, S, H, hd], the magnitude rounding errors scale with)."""
+    qf, kf, vf = (np.transpose(t.astype(F64), (0, 2, 1, 3)) for t in (q, k, v))               # [B, H, S, hd]
+    acc = np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(F32)
+    sc32 = F32(alpha) * acc
+    sc = (sc32.astype(q.dtype) if round_scores is None else round_scores(sc32)).astype(F64)
+    s = sc.shape[-1]
+    sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+    m = sc.max(-1, keepdims=True)
+    e = np.exp(sc - m)
+    l = e.sum(-1, keepdims=True)
+    ctx = np.einsum("bhqk,bhkd->bhqd", e / l, vf)
+    mag = np.einsum("bhqk,bhkd->bhqd", e / l, np.abs(vf))
+    return np.transpose(ctx, (0, 2, 1, 3)), m[..., 0], l[..., 0], np.transpose(mag, (0, 2, 1, 3))
+
+
+
 # --------------------------------------------------------------------------- seeded inputs
 def normal(seed, shape, dtype=F32, scale=1.0, shift=0.0):
     """standard_normal in f32 from default_rng(seed), scaled and shifted, then cast."""

@@ -19,20 +19,7 @@ from tests.tolerances import assert_close
 pytestmark = pytest.mark.gpu
 
 
-def ref_attention(q, k, v, alpha):
-    """q, k, v: [B, S, H, hd] float16 arrays -> (ctx f64, m, l) along the reference chain."""
-    qf, kf, vf = (np.transpose(t.astype(np.float64), (0, 2, 1, 3)) for t in (q, k, v))          # [B, H, S, hd]
-    acc = np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(np.float32)                                 # fp32 accumulate
-    sc = (np.float32(alpha) * acc).astype(q.dtype).astype(np.float64)                             # stored scores
-    s = sc.shape[-1]
-    keep = np.tril(np.ones((s, s), bool))
-    sc = np.where(keep, sc, -np.inf)
-    m = sc.max(-1, keepdims=True)
-    e = np.exp(sc - m)
-    l = e.sum(-1, keepdims=True)
-    ctx = np.einsum("bhqk,bhkd->bhqd", e / l, vf)
-    mag = np.einsum("bhqk,bhkd->bhqd", e / l, np.abs(vf))
-    return np.transpose(ctx, (0, 2, 1, 3)), m[..., 0], l[..., 0], np.transpose(mag, (0, 2, 1, 3))
+ref_attention = R.ref_causal_attention
 
 
 @pytest.mark.parametrize("cols,cols_pad", [(100, 128), (64, 128), (7, 16), (128, 128), (30, 33)])
@@ -77,13 +64,7 @@ def test_attention_fwd_bf16_and_errors(cuda):
     alpha = 0.1
     qp, kp, vp = (ops.block_pad(dev(t, bf16=True), 128) for t in (q, k, v))
     ctx, _ = ops.attention_fwd(qp, kp, vp, hd, alpha)
-    qf, kf, vf = (np.transpose(t.astype(np.float64), (0, 2, 1, 3)) for t in (q, k, v))
-    sc = R.bf16_round((np.float32(alpha) * np.einsum("bhqd,bhkd->bhqk", qf, kf).astype(np.float32))).astype(np.float64)
-    sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
-    e = np.exp(sc - sc.max(-1, keepdims=True))
-    pn = e / e.sum(-1, keepdims=True)
-    ref = np.transpose(np.einsum("bhqk,bhkd->bhqd", pn, vf), (0, 2, 1, 3))
-    mag = np.transpose(np.einsum("bhqk,bhkd->bhqd", pn, np.abs(vf)), (0, 2, 1, 3))
+    ref, _, _, mag = R.ref_causal_attention(q, k, v, alpha, round_scores=R.bf16_round)
     assert_close(host(ctx), ref, "bfloat16", "bf16 fused attention", floor_frac=1.0, floor_abs=mag)
     L = capi.lib()
     P = qp.data_ptr()

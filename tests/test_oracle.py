@@ -157,3 +157,22 @@ def test_gemm_oracle_small():
     assert s.shape == (2, 6, 3, 5)
     ref = 0.5 * np.einsum("bqhd,bkhd->bqhk", q.astype(np.float64), k.astype(np.float64))
     assert_close(s, ref.astype(np.float16), "float16", "block gemm")
+
+
+def test_causal_attention_reference_agrees_with_the_chain_of_primitives():
+    """ref_causal_attention (f64 from the rounded scores) against the same block composed from the per-thunk oracle
+    functions with every intermediate rounded to f16, as the reference materialises them."""
+    import numpy as np
+    from oracle import ref_chain as R
+    bsz, s, h, hd = 2, 48, 3, 20
+    q, k, v = (R.normal(200 + i, (bsz, s, h, hd), np.float16) for i in range(3))
+    alpha = 1.0 / np.sqrt(hd)
+    ctx, m, l, mag = R.ref_causal_attention(q, k, v, alpha)
+    sc = R.ref_block_gemm(q, k, False, True, alpha=alpha)                                    # [B, S, H, S] f16
+    keep = R.causal_keep_mask(bsz * s * h, s, h, s, 0)
+    p, _ = R.ref_softmax_fwd(sc.reshape(-1, s), keep)
+    chain = R.ref_block_gemm(p.reshape(bsz, s, h, s), v, False, False).astype(np.float64)
+    assert np.all(np.abs(chain - ctx) <= 2e-3 * np.maximum(np.abs(ctx), mag) + 1e-6)
+    sc64 = np.where(keep.reshape(bsz, s, h, s), sc.astype(np.float64), -np.inf)
+    assert np.array_equal(np.transpose(sc64.max(-1), (0, 2, 1)), m)
+    assert np.all(l >= 1.0) and np.all(l <= s)
