@@ -260,7 +260,7 @@ def other_thunks(torch, ops, peak):
     # A1 fused attention (what the training step runs by default): q, k, v padded to 128 columns; HBM traffic is
     # q, k, v, ctx and the row statistics; "TFLOP/s" counts the 2 * 2 * S^2/2 * hd useful flops per (batch, head)
     qp, kp, vp = (ops.block_pad(t, 128) for t in (q, k, v))
-    st = torch.empty(B, H, S, 2, device="cuda")
+    st = torch.empty(B, H, S, 4, device="cuda")
     sec = time_thunk(lambda: ops.attention_fwd(qp, kp, vp, hd, 0.1, ctx=ctx, stats=st), 10, 3, torch)
     useful = 2 * 2 * B * H * (S * S / 2) * hd
     out["attention_fwd[8x2048x32x100]"] = {"us": round(sec * 1e6, 1), "TFLOP/s_useful": round(useful / sec / 1e12, 1), "launches_per_step": 1}

@@ -209,6 +209,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
     constexpr float kLog2e = 1.4426950408889634f;
     float m = -INFINITY;
+    const bool neg = p.alpha < 0.f;
     bool ok = true;   // a wait that ran out ends this thread's work, but it still meets the group barriers below
     for (int j = grp; j < ntiles; j += 2) {         // pass 1: row maximum of the rounded, scaled, masked scores
       const int sb = j & 1;
@@ -226,23 +227,29 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(s_empty + sb);
         }
+        // Scaling by alpha and rounding to the storage type are monotone, so the maximum of the rounded scores is the
+        // rounded, scaled maximum (minimum, for a negative alpha) of the raw accumulators: one instruction per score
+        // here, four independent chains, and one scaling and rounding after the loop.
+        float mq[4] = {m, -INFINITY, -INFINITY, -INFINITY};
         if (j != qi) {
 #pragma unroll
-          for (int i = 0; i < 64; i += 2) {
-            const float2 s2 = rounded_scores<T>(p.alpha, v[i >> 5][i & 31], v[i >> 5][(i & 31) + 1]);
-            m = fmaxf(m, fmaxf(s2.x, s2.y));
+          for (int i = 0; i < 64; ++i) {
+            const float a = __uint_as_float(v[i >> 5][i & 31]);
+            mq[i & 3] = fmaxf(mq[i & 3], neg ? -a : a);
           }
         } else {                                    // diagonal tile: columns c <= r are unmasked
 #pragma unroll
-          for (int i = 0; i < 64; i += 2) {
-            const float2 s2 = rounded_scores<T>(p.alpha, v[i >> 5][i & 31], v[i >> 5][(i & 31) + 1]);
-            const int c = half * 64 + i;
-            if (c <= r) m = fmaxf(m, s2.x);
-            if (c + 1 <= r) m = fmaxf(m, s2.y);
+          for (int i = 0; i < 64; ++i) {
+            const float a = __uint_as_float(v[i >> 5][i & 31]);
+            if (half * 64 + i <= r) mq[i & 3] = fmaxf(mq[i & 3], neg ? -a : a);
           }
         }
+        m = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
       }
     }
+    // m holds the extreme raw accumulator (sign-folded); back to a rounded, scaled score.  Rows with no unmasked
+    // key in this group's tiles keep -inf.
+    if (m != -INFINITY) m = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * (neg ? -m : m)));
     part[grp * kAttnRows + r] = m;
     named_barrier(1, 256);
     m = fmaxf(part[r], part[kAttnRows + r]);
@@ -256,6 +263,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
       uint4 pk[16];                                 // this row's 128 probabilities, 8 per 16-byte chunk
+      float lq[4] = {0.f, 0.f, 0.f, 0.f};           // independent partial row sums
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t v[2][32];
@@ -281,12 +289,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               if (c > r) e0 = 0.f;
               if (c + 1 > r) e1 = 0.f;
             }
-            l += e0 + e1;
+            lq[i] += e0 + e1;
             w[i] = pack2<T>(e0, e1);
           }
           pk[half * 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
+      l += (lq[0] + lq[1]) + (lq[2] + lq[3]);
       // the P V two tiles back has read this group's probability buffer
       if (!mbar_wait_bounded(p_empty + grp, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
 #pragma unroll
@@ -306,7 +315,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const long long row = (long long)b * p.seq + q0 + r;
     T* out = ctx + (row * p.heads + h) * p.head_dim;
     if (grp == 0) {
-      float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 2;
+      float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
       st[0] = m; st[1] = l;
     }
 #pragma unroll 1
@@ -337,6 +346,41 @@ done:
   }
 }
 
+// c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  One warp per
+// (b, s, h) row: lanes read consecutive 8-byte pieces, so both tensors stream coalesced.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attention_rowdot_kernel(float* __restrict__ stats, const T* __restrict__ ctx, const T* __restrict__ dctx_pad, long long rows,
+                        int seq, int heads, int head_dim) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    float acc = 0.f;
+    if (lane < head_dim / 4) {
+      const uint2 a = __ldg(reinterpret_cast<const uint2*>(ctx + row * head_dim) + lane);
+      const uint2 g = __ldg(reinterpret_cast<const uint2*>(dctx_pad + row * kAttnHd) + lane);
+      float2 a0, a1, g0, g1;
+      if constexpr (std::is_same<T, __half>::value) {
+        a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)); a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+        g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)); g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
+      } else {
+        a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)); a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+        g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x)); g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+      }
+      acc = __fmaf_rn(a0.x, g0.x, __fmaf_rn(a0.y, g0.y, __fmaf_rn(a1.x, g1.x, __fmul_rn(a1.y, g1.y))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const long long bs = row / heads;              // row = (b * seq + s) * heads + h
+      const int h = (int)(row - bs * heads);
+      const long long b = bs / seq;
+      const int sq = (int)(bs - b * seq);
+      stats[((b * heads + h) * seq + sq) * 4 + 2] = acc;
+    }
+  }
+}
+
 // ---- backward: probabilities and score adjoints, rebuilt tile by tile -------------------------------------------
 // The adjoint of the chain needs P (for dV = P^T dO) and dS (for dQ = dS K, dK = dS^T Q).  The reference keeps the
 // scores and recomputes the softmax from them inside InnerSoftmaxPostAdj (src/thunk/op.rs:3376-3457) after a block
@@ -345,7 +389,7 @@ done:
 //   y = exp(s - m) / l   (m, l: the forward's row statistics),   P = T(y),   dS = T(y * T(dP) - c * y)
 // with the reference's rounding points (s and dP rounded to the storage type first).  c = sum_j y_j dP_j is taken as
 // D = dO . O (equal in exact arithmetic; O is the stored context row), so no pass over the whole row is needed
-// before the first tile can be written.  Tiles above the diagonal are not written, except the one zero tile that
+// before the first tile can be written; a small streaming kernel computes it per row into the statistics first.  Tiles above the diagonal are not written, except the one zero tile that
 // completes the last written pair of tiles to 256 columns (what a CACTI_B200_TRI_A_* consumer may read).
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -440,27 +484,9 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
     constexpr float kLog2e = 1.4426950408889634f;
     const long long row = (long long)b * p.seq + q0 + r;
-    const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 2;
+    const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
     const float mb = st[0] * kLog2e, rl = 1.f / st[1];
-    // c = dO . O over the head dimension (f32 accumulation of the stored 16-bit values)
-    float cdot = 0.f;
-    {
-      const uint2* o2 = reinterpret_cast<const uint2*>(ctx + (row * p.heads + h) * p.head_dim);
-      const uint2* g2 = reinterpret_cast<const uint2*>(dctx_pad + (row * p.heads + h) * kAttnHd);
-      for (int i = 0; i < p.head_dim / 4; ++i) {
-        const uint2 a = o2[i], g = g2[i];
-        float2 a0, a1, g0, g1;
-        if constexpr (std::is_same<T, __half>::value) {
-          a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)); a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
-          g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)); g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
-        } else {
-          a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)); a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
-          g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x)); g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
-        }
-        cdot = __fmaf_rn(a0.x, g0.x, cdot); cdot = __fmaf_rn(a0.y, g0.y, cdot);
-        cdot = __fmaf_rn(a1.x, g1.x, cdot); cdot = __fmaf_rn(a1.y, g1.y, cdot);
-      }
-    }
+    const float cdot = st[2];                       // c = dO . O, from attention_rowdot_kernel
     unsigned char* mystage = stage + (size_t)(warp - 2) * 4096 + (size_t)lane * 128;
     const int row0 = q0 + qq * 32;                  // first query row of this warp
     // one [32 x 64] box: wait until the previous store has read the staging buffer, fill it, hand it to the TMA unit
@@ -640,6 +666,15 @@ static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t
   p.idesc_s = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(128 >> 3) << 17) |
               ((uint32_t)(128 >> 4) << 24);
   p.idesc_pv = p.idesc_s;
+  {
+    const long long rows = (long long)batch * seq * heads;
+    long long grid = (rows + 7) / 8;
+    if (grid > (long long)kNumSMs * 16) grid = (long long)kNumSMs * 16;
+    attention_rowdot_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<float*>(stats), reinterpret_cast<const T*>(ctx),
+                                                               reinterpret_cast<const T*>(dctx), rows, seq, heads, head_dim);
+    rc = check_launch();
+    if (rc) return rc;
+  }
   auto kern = attention_bwd_prep_kernel<T>;
   static bool attr_set = false;
   if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnBwdSmem); attr_set = true; }
@@ -694,7 +729,7 @@ int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b
   if (head_dim > kAttnHd || head_dim % 4 || seq % kAttnRows || batch * heads * (seq / kAttnRows) > 0x7fffffffLL)
     return CACTI_B200_ERR_SHAPE;
   if (batch == 0 || seq == 0 || heads == 0) return CACTI_B200_OK;
-  if (!ctx || !stats || !q || !k || !v || (q & 15) || (k & 15) || (v & 15) || (ctx & 7) || (stats & 7))
+  if (!ctx || !stats || !q || !k || !v || (q & 15) || (k & 15) || (v & 15) || (ctx & 7) || (stats & 15))
     return CACTI_B200_ERR_INVALID_VALUE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == CACTI_B200_R_16F)

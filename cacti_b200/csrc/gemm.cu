@@ -66,6 +66,11 @@ __device__ __forceinline__ void decode_tile(long long tile, long long tiles_per_
   if (p.tri) tm = (tm + blk) % p.tiles_m;
 }
 
+// Instruction descriptor with the N extent replaced (edge tiles issue narrower MMAs instead of multiplying zeros).
+__device__ __forceinline__ uint32_t idesc_with_n(uint32_t idesc, int n) {
+  return (idesc & ~(0x3Fu << 17)) | ((uint32_t)(n >> 3) << 17);
+}
+
 // Triangular hints, per output tile whose rows are [row0, row0 + rows) and whose first column is col0.
 //   C_LOWER: only C[r, c] with c <= r + diag is wanted; a tile wholly beyond that is skipped (not written).
 //   A_LOWER: op(A)[r, k] == 0 for k > r + diag; k-blocks wholly beyond the tile's last row are skipped.
@@ -277,12 +282,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     long long local = 0;
     for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
       int kb0 = 0, kb1 = nkb;
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       if (p.tri) {
-        int blk, tm, tn;
-        decode_tile(tile, tiles_per_block, p, blk, tm, tn);
         if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
         k_block_range(p, tm * kBM, kBM, nkb, kb0, kb1);
       }
+      // the last column tile multiplies only the columns that exist (rounded up to the MMA's granularity of 16)
+      const int nvalid = p.N - tn * BN;
+      const uint32_t idesc = nvalid >= BN ? p.idesc : idesc_with_n(p.idesc, (nvalid + 15) & ~15);
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
       tc_fence_after();
@@ -295,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int k4 = 0; k4 < kBK / 16; ++k4) {
           const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
           const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
-          tc_mma_f16(tacc, da, db, p.idesc, (kb > kb0 || k4) ? 1u : 0u);
+          tc_mma_f16(tacc, da, db, idesc, (kb > kb0 || k4) ? 1u : 0u);
         }
         tc_commit(empty + s);                 // stage free once these MMAs have read it
         if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -422,13 +430,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     int s = 0; unsigned ph = 0;
-    const int row_off = (int)rank * kBM, col_off = (int)rank * HB;
+    const int row_off = (int)rank * kBM;
     for (long long tile = pair; tile < total; tile += npairs) {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
-      const int m0 = tm * kPairBM + row_off, n0 = tn * BN + col_off;
+      // a last column tile with at most 128 columns runs as an N = 128 MMA: each CTA then supplies 64 rows of B
+      // (the first 64 of the box it loads), so the CTAs' boxes start 64 rows apart instead of 128
+      const int hb = (p.N - tn * BN <= HB) ? HB / 2 : HB;
+      const int m0 = tm * kPairBM + row_off, n0 = tn * BN + (int)rank * hb;
       if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
       int kb0, kb1;
       k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
@@ -462,12 +473,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     long long local = 0;
     for (long long tile = pair; tile < total; tile += npairs) {
       int kb0 = 0, kb1 = nkb;
+      int blk, tm, tn;
+      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       if (p.tri) {
-        int blk, tm, tn;
-        decode_tile(tile, tiles_per_block, p, blk, tm, tn);
         if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
         k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
       }
+      const uint32_t idesc = (p.N - tn * BN <= HB) ? idesc_with_n(p.idesc, HB) : p.idesc;      // see the producer
       const int acc = (int)(local & 1);
       if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
       tc_fence_after();
@@ -480,7 +492,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int k4 = 0; k4 < kBK / 16; ++k4) {
           const uint64_t da = A_MN ? make_desc(sa + k4 * 2048, 512, 64) : make_desc(sa + k4 * 32, 1, 64);
           const uint64_t db = B_MN ? make_desc(sb + k4 * 2048, 512, 64) : make_desc(sb + k4 * 32, 1, 64);
-          tc_mma_f16_pair(tacc, da, db, p.idesc, (kb > kb0 || k4) ? 1u : 0u);
+          tc_mma_f16_pair(tacc, da, db, idesc, (kb > kb0 || k4) ? 1u : 0u);
         }
         tc_commit_pair(empty + s);
         if (++s == STAGES) { s = 0; ph ^= 1; }

@@ -195,7 +195,7 @@ class TrainStep:
                 # P and dS are rebuilt from q, k, v, dctx and the row statistics; q, k, v here are the padded copies
                 dctx = ops.block_pad(dctx.view(B, S, H, hd), 128)
                 p, ds = ops.attention_bwd_prep(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha)
-                self.launches += 2
+                self.launches += 3
                 bv = hd
             else:
                 dp = self._bmm(dctx.view(B, S, H, hd), v.view(B, S, H, hd), False, True, tri=TRI_C_LOWER)  # dctx V^T

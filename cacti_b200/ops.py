@@ -311,10 +311,10 @@ def block_pad(x, cols_pad=128, out=None):
 
 
 def attention_fwd(q_pad, k_pad, v_pad, head_dim, alpha, ctx=None, stats=None):
-    """Fused causal attention on head-dim-padded [B, S, H, 128] operands -> (ctx [B, S, H, head_dim], stats [B, H, S, 2])."""
+    """Fused causal attention on head-dim-padded [B, S, H, 128] operands -> (ctx [B, S, H, head_dim], stats [B, H, S, 4])."""
     b, s, h, _ = q_pad.shape
     ctx = torch.empty(b, s, h, head_dim, dtype=q_pad.dtype, device=q_pad.device) if ctx is None else ctx
-    stats = torch.empty(b, h, s, 2, dtype=torch.float32, device=q_pad.device) if stats is None else stats
+    stats = torch.empty(b, h, s, 4, dtype=torch.float32, device=q_pad.device) if stats is None else stats
     check(lib().cacti_b200_attention_fwd(_ptr(ctx), _ptr(stats), _ptr(q_pad), _ptr(k_pad), _ptr(v_pad), b, s, h, head_dim,
                                          alpha, _dt(q_pad), _stream()), "attention_fwd")
     return ctx, stats

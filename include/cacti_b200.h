@@ -321,8 +321,9 @@ int cacti_b200_block_pad(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t nrow,
  *   q, k, v : [batch, seq, heads, 128] of dtype (R_16F / R_16BF), head_dim columns of data then zeros
  *             (cacti_b200_block_pad with cols_pad = 128); 16-byte aligned
  *   ctx     : [batch, seq, heads, head_dim], 8-byte aligned
- *   stats   : [batch, heads, seq, 2] f32: row maximum m of the rounded scaled scores and sum of exp(s - m) over the
- *             unmasked keys; what a backward pass needs to rebuild the probabilities
+ *   stats   : [batch, heads, seq, 4] f32, 16-byte aligned: word 0 the row maximum m of the rounded scaled scores,
+ *             word 1 the sum of exp(s - m) over the unmasked keys (what a backward pass needs to rebuild the
+ *             probabilities); words 2 and 3 are scratch of cacti_b200_attention_bwd_prep
  * Scores are rounded to dtype as block_matmul_scale stores them and the softmax runs in f32 on the rounded values
  * with the row maximum subtracted, as the reference does.  exp(s - m) is rounded to dtype before the product with V
  * and the division by the row sum is applied to the f32 result, where the reference rounds the quotient first: ctx
@@ -337,7 +338,8 @@ int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b
  * InnerSoftmaxPostAdj with the recomputed softmax, src/thunk/op.rs:3376-3457):
  *   y = exp(s - m) / l,  P = T(y),  dS = T(y * T(dP) - c * y),  s = T(alpha q.k),  c = dO . O
  * (c equals sum_j y_j dP_j in exact arithmetic; taking it from the stored context row removes the pass over the whole
- * row).  p, ds: [batch, seq, heads, seq]; entries above the diagonal are written (as zeros) up to the bound B of
+ * row; it is computed first, by a small streaming kernel, into word 2 of each row's stats: two launches).
+ * p, ds: [batch, seq, heads, seq]; entries above the diagonal are written (as zeros) up to the bound B of
  * CACTI_B200_MASK_CAUSAL_TRIM and left untouched beyond it: feed them to cacti_b200_gemm_strided_batched_tri with
  * CACTI_B200_TRI_A_UPPER (dV = P^T dO, dK = alpha dS^T Q) and CACTI_B200_TRI_A_LOWER (dQ = alpha dS K).
  * q, k, v, dctx: [batch, seq, heads, 128] zero-padded (cacti_b200_block_pad); ctx: [batch, seq, heads, head_dim] and
