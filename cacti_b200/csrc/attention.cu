@@ -308,30 +308,44 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     part[grp * kAttnRows + r] = l;
     named_barrier(1, 256);
     l = part[r] + part[kAttnRows + r];
-    // context row = O / l; group 0 stores columns 0..63, group 1 columns 64..head_dim-1
-    if (!ok || !mbar_wait_bounded(o_full, 0, kDevErrAttnTimeout)) goto done;
-    tc_fence_after();
-    const float rl = 1.f / l;
-    const long long row = (long long)b * p.seq + q0 + r;
-    T* out = ctx + (row * p.heads + h) * p.head_dim;
-    if (grp == 0) {
-      float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
-      st[0] = m; st[1] = l;
-    }
+    // context rows = O / l.  Each thread scales its row (group 0 columns 0..63, group 1 the rest) into a packed
+    // [128][head_dim] staging area (the probability buffers are free once the last P V has completed); the warps then
+    // write whole rows with consecutive lanes on consecutive 8-byte pieces (a thread = row store would touch 32
+    // sectors per instruction).
+    const bool fin = ok && mbar_wait_bounded(o_full, 0, kDevErrAttnTimeout);
+    unsigned char* rowbuf = sP;
+    if (fin) {
+      tc_fence_after();
+      const float rl = 1.f / l;
+      if (grp == 0) {
+        float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
+        st[0] = m; st[1] = l;
+      }
 #pragma unroll 1
-    for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
-      uint32_t v[32];
-      tc_ld32(tO + lane_off + (uint32_t)c0, v);
-      tc_ld_wait();
+      for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tO + lane_off + (uint32_t)c0, v);
+        tc_ld_wait();
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {                 // 4 elements = 8 bytes per store (rows start 8-byte aligned: hd % 4 == 0)
-        const int c = c0 + g * 4;
-        if (c + 4 <= p.head_dim) {
-          uint2 w;
-          w.x = pack2<T>(__uint_as_float(v[g * 4]) * rl, __uint_as_float(v[g * 4 + 1]) * rl);
-          w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * rl, __uint_as_float(v[g * 4 + 3]) * rl);
-          *reinterpret_cast<uint2*>(out + c) = w;
+        for (int g = 0; g < 8; ++g) {               // 4 elements = 8 bytes (head_dim % 4 == 0)
+          const int c = c0 + g * 4;
+          if (c + 4 <= p.head_dim) {
+            uint2 w;
+            w.x = pack2<T>(__uint_as_float(v[g * 4]) * rl, __uint_as_float(v[g * 4 + 1]) * rl);
+            w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * rl, __uint_as_float(v[g * 4 + 3]) * rl);
+            *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+          }
         }
+      }
+      tc_fence_before();
+    }
+    named_barrier(1, 256);
+    if (fin) {
+      const int cw = warp - 2;                      // 8 softmax warps, 16 rows each
+      for (int rr = cw * 16; rr < cw * 16 + 16; ++rr) {
+        T* out = ctx + (((long long)b * p.seq + q0 + rr) * p.heads + h) * p.head_dim;
+        if (lane < p.head_dim / 4)
+          reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
       }
     }
     tc_fence_before();
@@ -487,18 +501,27 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
     const float mb = st[0] * kLog2e, rl = 1.f / st[1];
     const float cdot = st[2];                       // c = dO . O, from attention_rowdot_kernel
-    unsigned char* mystage = stage + (size_t)(warp - 2) * 4096 + (size_t)lane * 128;
+    // Output staging: the warp's 4 KB hold one [32 rows][32 columns] box of P and one of dS (2 KB each, 64-byte rows in
+    // the TMA unit's 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)).  Both stores of a
+    // quarter tile are issued together, and the wait for the TMA unit to have read them comes a quarter tile of
+    // arithmetic later.
+    unsigned char* boxP = stage + (size_t)(warp - 2) * 4096;
+    unsigned char* boxD = boxP + 2048;
     const int row0 = q0 + qq * 32;                  // first query row of this warp
-    // one [32 x 64] box: wait until the previous store has read the staging buffer, fill it, hand it to the TMA unit
-    auto store_box = [&](const CUtensorMap* map, const uint4 (&chunks)[8], int col0) {
+    const int sw = (lane >> 1) & 3;
+    auto store_quarter = [&](const uint4 (&pc)[4], const uint4 (&dc)[4], int col0) {
       if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       __syncwarp();
 #pragma unroll
-      for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(mystage + ((g ^ (lane & 7)) << 4)) = chunks[g];
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(boxP + lane * 64 + ((c ^ sw) << 4)) = pc[c];
+        *reinterpret_cast<uint4*>(boxD + lane * 64 + ((c ^ sw) << 4)) = dc[c];
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        tma_store_4d(map, mystage - (size_t)lane * 128, col0, row0, h, b);
+        tma_store_4d(&tmP, boxP, col0, row0, h, b);
+        tma_store_4d(&tmdS, boxD, col0, row0, h, b);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     };
@@ -508,31 +531,29 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       tc_fence_after();
       const uint32_t ts = tmem_base + (uint32_t)sl * 256u + lane_off;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[2][32], gv[2][32];
-        tc_ld32(ts + (uint32_t)(half * 64), sv[0]);
-        tc_ld32(ts + (uint32_t)(half * 64 + 32), sv[1]);
-        tc_ld32(ts + 128u + (uint32_t)(half * 64), gv[0]);
-        tc_ld32(ts + 128u + (uint32_t)(half * 64 + 32), gv[1]);
+      for (int qt = 0; qt < 4; ++qt) {              // 32 key columns at a time
+        uint32_t sv[32], gv[32];
+        tc_ld32(ts + (uint32_t)(qt * 32), sv);
+        tc_ld32(ts + 128u + (uint32_t)(qt * 32), gv);
         tc_ld_wait();
-        if (half == 1) {
+        if (qt == 3) {                              // S and dP of this tile are in registers
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(t_empty + sl);
         }
-        uint4 pc[8], dc[8];
+        uint4 pc[4], dc[4];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < 4; ++g) {
           uint32_t pw[4], dw[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int idx = g * 8 + i * 2;
-            const float2 s2 = rounded_scores<T>(p.alpha, sv[idx >> 5][idx & 31], sv[idx >> 5][(idx & 31) + 1]);
-            const float2 g2 = rounded_scores<T>(1.f, gv[idx >> 5][idx & 31], gv[idx >> 5][(idx & 31) + 1]);
+            const float2 s2 = rounded_scores<T>(p.alpha, sv[idx], sv[idx + 1]);
+            const float2 g2 = rounded_scores<T>(1.f, gv[idx], gv[idx + 1]);
             float y0 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb)), rl);
             float y1 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb)), rl);
             if (j == qi) {
-              const int c = half * 64 + idx;
+              const int c = qt * 32 + idx;
               if (c > r) y0 = 0.f;
               if (c + 1 > r) y1 = 0.f;
             }
@@ -542,20 +563,15 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           pc[g] = make_uint4(pw[0], pw[1], pw[2], pw[3]);
           dc[g] = make_uint4(dw[0], dw[1], dw[2], dw[3]);
         }
-        const int col0 = j * kAttnRows + half * 64;
-        store_box(&tmP, pc, col0);
-        store_box(&tmdS, dc, col0);
+        store_quarter(pc, dc, j * kAttnRows + qt * 32);
       }
     }
     // zero tile that completes an odd count of written tiles to a multiple of 256 columns
     if ((ntiles & 1) && ntiles * kAttnRows < p.seq && grp == (ntiles & 1)) {
-      uint4 z[8];
+      uint4 z[4];
 #pragma unroll
-      for (int g = 0; g < 8; ++g) z[g] = make_uint4(0, 0, 0, 0);
-      for (int half = 0; half < 2; ++half) {
-        store_box(&tmP, z, ntiles * kAttnRows + half * 64);
-        store_box(&tmdS, z, ntiles * kAttnRows + half * 64);
-      }
+      for (int g = 0; g < 4; ++g) z[g] = make_uint4(0, 0, 0, 0);
+      for (int qt = 0; qt < 4; ++qt) store_quarter(z, z, ntiles * kAttnRows + qt * 32);
     }
     tc_fence_before();
   }
@@ -605,7 +621,7 @@ block_pad_vec_kernel(uint4* __restrict__ dst, const uint2* __restrict__ src, lon
 }
 
 static int encode_bshd(CUtensorMap* map, uint64_t ptr, int batch, int seq, int heads, int hdp, int box_inner, int box_rows,
-                       bool bf16) {
+                       bool bf16, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return CACTI_B200_ERR_LAUNCH;
   cuuint64_t dims[4] = {(cuuint64_t)hdp, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
@@ -614,7 +630,7 @@ static int encode_bshd(CUtensorMap* map, uint64_t ptr, int batch, int seq, int h
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                   reinterpret_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return CACTI_B200_ERR_LAUNCH; }
   return CACTI_B200_OK;
 }
@@ -656,10 +672,10 @@ static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t
   if (!rc) rc = encode_bshd(&tmK, k, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
   if (!rc) rc = encode_bshd(&tmV, v, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
   if (!rc) rc = encode_bshd(&tmdO, dctx, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
-  // P and dS: [batch, seq, heads, seq] written as [32 rows][64 columns] boxes
+  // P and dS: [batch, seq, heads, seq] written as [32 rows][32 columns] boxes (64-byte rows, 64-byte swizzle)
   CUtensorMap tmP, tmdS;
-  if (!rc) rc = encode_bshd(&tmP, pp, batch, seq, heads, seq, 64, 32, bf16);
-  if (!rc) rc = encode_bshd(&tmdS, ds, batch, seq, heads, seq, 64, 32, bf16);
+  if (!rc) rc = encode_bshd(&tmP, pp, batch, seq, heads, seq, 32, 32, bf16, CU_TENSOR_MAP_SWIZZLE_64B);
+  if (!rc) rc = encode_bshd(&tmdS, ds, batch, seq, heads, seq, 32, 32, bf16, CU_TENSOR_MAP_SWIZZLE_64B);
   if (rc) return rc;
   AttnParams p;
   p.batch = batch; p.seq = seq; p.heads = heads; p.head_dim = head_dim; p.alpha = alpha;
