@@ -64,6 +64,14 @@ __device__ __forceinline__ float2 rounded_scores(float alpha, uint32_t a, uint32
   }
 }
 template <typename T>
+__device__ __forceinline__ float2 rounded_pair(uint32_t a, uint32_t b) {         // the same without the scaling
+  if constexpr (std::is_same<T, __half>::value) {
+    return __half22float2(__floats2half2_rn(__uint_as_float(a), __uint_as_float(b)));
+  } else {
+    return __bfloat1622float2(__floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b)));
+  }
+}
+template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (std::is_same<T, __half>::value) {
     __half2 h = __floats2half2_rn(a, b);
@@ -499,7 +507,8 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     constexpr float kLog2e = 1.4426950408889634f;
     const long long row = (long long)b * p.seq + q0 + r;
     const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
-    const float mb = st[0] * kLog2e, rl = 1.f / st[1];
+    // y = exp(s - m) / l as one exponential: 2^(s log2e - (m log2e + log2 l))
+    const float mb = __fmaf_rn(st[0], kLog2e, __log2f(st[1]));
     const float cdot = st[2];                       // c = dO . O, from attention_rowdot_kernel
     // Output staging: the warp's 4 KB hold one [32 rows][32 columns] box of P and one of dS (2 KB each, 64-byte rows in
     // the TMA unit's 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)).  Both stores of a
@@ -549,9 +558,9 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           for (int i = 0; i < 4; ++i) {
             const int idx = g * 8 + i * 2;
             const float2 s2 = rounded_scores<T>(p.alpha, sv[idx], sv[idx + 1]);
-            const float2 g2 = rounded_scores<T>(1.f, gv[idx], gv[idx + 1]);
-            float y0 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb)), rl);
-            float y1 = __fmul_rn(exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb)), rl);
+            const float2 g2 = rounded_pair<T>(gv[idx], gv[idx + 1]);
+            float y0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+            float y1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
             if (j == qi) {
               const int c = qt * 32 + idx;
               if (c > r) y0 = 0.f;
