@@ -368,32 +368,39 @@ done:
   }
 }
 
-// c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  One warp per
-// (b, s, h) row: lanes read consecutive 8-byte pieces, so both tensors stream coalesced.
+// c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  Eight lanes per
+// (b, s, h) row, four rows per warp, each lane on 8-byte pieces 8 apart: both tensors stream coalesced and every lane
+// has up to eight loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(256)
 attention_rowdot_kernel(float* __restrict__ stats, const T* __restrict__ ctx, const T* __restrict__ dctx_pad, long long rows,
                         int seq, int heads, int head_dim) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane >> 3, l8 = lane & 7;
   const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+  const int pieces = head_dim / 4;
+  for (long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4; row0 < rows; row0 += warps * 4) {
+    const long long row = row0 + sub;
     float acc = 0.f;
-    if (lane < head_dim / 4) {
-      const uint2 a = __ldg(reinterpret_cast<const uint2*>(ctx + row * head_dim) + lane);
-      const uint2 g = __ldg(reinterpret_cast<const uint2*>(dctx_pad + row * kAttnHd) + lane);
-      float2 a0, a1, g0, g1;
-      if constexpr (std::is_same<T, __half>::value) {
-        a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)); a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
-        g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)); g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
-      } else {
-        a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)); a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
-        g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x)); g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+    if (row < rows) {
+      const uint2* o2 = reinterpret_cast<const uint2*>(ctx + row * head_dim);
+      const uint2* g2 = reinterpret_cast<const uint2*>(dctx_pad + row * kAttnHd);
+#pragma unroll 4
+      for (int i = l8; i < pieces; i += 8) {
+        const uint2 a = __ldg(o2 + i), g = __ldg(g2 + i);
+        float2 a0, a1, g0, g1;
+        if constexpr (std::is_same<T, __half>::value) {
+          a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)); a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+          g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x)); g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
+        } else {
+          a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)); a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+          g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x)); g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+        }
+        acc = __fmaf_rn(a0.x, g0.x, __fmaf_rn(a0.y, g0.y, __fmaf_rn(a1.x, g1.x, __fmaf_rn(a1.y, g1.y, acc))));
       }
-      acc = __fmaf_rn(a0.x, g0.x, __fmaf_rn(a0.y, g0.y, __fmaf_rn(a1.x, g1.x, __fmul_rn(a1.y, g1.y))));
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
+    for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (l8 == 0 && row < rows) {
       const long long bs = row / heads;              // row = (b * seq + s) * heads + h
       const int h = (int)(row - bs * heads);
       const long long b = bs / seq;
@@ -693,7 +700,7 @@ static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t
   p.idesc_pv = p.idesc_s;
   {
     const long long rows = (long long)batch * seq * heads;
-    long long grid = (rows + 7) / 8;
+    long long grid = (rows + 31) / 32;
     if (grid > (long long)kNumSMs * 16) grid = (long long)kNumSMs * 16;
     attention_rowdot_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<float*>(stats), reinterpret_cast<const T*>(ctx),
                                                                reinterpret_cast<const T*>(dctx), rows, seq, heads, head_dim);

@@ -642,7 +642,8 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   // Tile shape: the persistent grid runs ceil(tiles / CTAs) waves; pick the shape with the least wave-time.
   // Per-flop cost relative to the one-SM 256-wide tile with K-major operands, from sustained interleaved runs of
   // the projection shapes: 1.08 for 192-wide and 1.3 for 128-wide tiles; one-SM tiles with an MN-major operand
-  // 1.25 (their shared-memory reads conflict more); the two-SM 256 x 256 tile 0.95, or 1.05 with an MN-major operand.
+  // 1.25 (their shared-memory reads conflict more); the two-SM 256 x 256 tile 0.93 with either operand layout (the
+  // 3200 x 3200 x 16384 weight-gradient matmul: 1041 TFLOP/s in 3 waves of 256 x 256 against 963 in 3 waves of 128 x 192).
   int BN = g_gemm_bn;
   bool pair = false;
   if (!BN) {
@@ -658,7 +659,7 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
       }
       if (g_gemm_pair && M > kBM) {
         const long long tiles2 = ((M + kPairBM - 1) / kPairBM) * ((N + kPairBN - 1) / kPairBN) * nbi * nbo;
-        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * (mn ? 1.05 : 0.95);
+        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * 0.93;
         if (cost < best) { best = cost; BN = kPairBN; pair = true; }
       }
     }
