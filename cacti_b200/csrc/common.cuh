@@ -179,6 +179,7 @@ template <typename Op> __device__ __forceinline__ float group_reduce(GroupCtx& g
 constexpr unsigned kDevErrStageTimeout = 1u;
 constexpr unsigned kDevErrGemmTimeout = 2u;
 extern __device__ unsigned g_dev_error;
+constexpr unsigned g_mbar_suspend_ns = 4000u;      // per-poll suspend hint of mbar_try_wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -191,18 +192,22 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One poll.  The suspend-time hint lets the hardware park the thread for up to that long while the phase is
+// incomplete (it resumes at once when the phase completes), so that waiting warps do not take issue slots from the
+// warps that compute on the same scheduler.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
   unsigned ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(g_mbar_suspend_ns) : "memory");
   return ok != 0;
 }
-// Returns false after ~2^22 failed polls (each poll itself blocks for a hardware time slice).
+// Returns false after 2^20 failed polls: at most about 4 s (every poll parked for the full hint), at least a few
+// tens of milliseconds (polls that return at once), far beyond any wait of a healthy kernel.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned err_code) {
-  for (unsigned it = 0; it < (1u << 22); ++it)
+  for (unsigned it = 0; it < (1u << 20); ++it)
     if (mbar_try_wait(bar, parity)) return true;
   atomicMax(&g_dev_error, err_code);
   return false;
