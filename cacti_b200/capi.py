@@ -39,6 +39,7 @@ SIGNATURES = {
     "cacti_b200_softmax_fwd_bwd": (_int, [_p, _p, _p, _p, _i64, _i64, _int, _i64, _i64, _i64, _int, _int, _st]),
     "cacti_b200_rope_tables": (_int, [_p, _p, _i64, _i64, _f32, _int, _st]),
     "cacti_b200_rope_fwd": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _st]),
+    "cacti_b200_rope_fwd_pitched": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _st]),
     "cacti_b200_rope_bwd": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _st]),
     "cacti_b200_rope_fwd_bwd": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _int, _st]),
     "cacti_b200_swiglu_fwd": (_int, [_p, _p, _p, _i64, _int, _st]),

@@ -145,6 +145,38 @@ rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, 
   }
 }
 
+// Forward RoPE whose output rows are head-pitched: y[tok][h][0 .. pitch) with the head's head_dim rotated values
+// followed by zeros, the layout cacti_b200_block_pad would produce from the packed result (the fused attention reads
+// q and k that way).  One thread per 8-byte unit of the output; 16-bit types only (two 4-byte rope units per thread).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_fwd_pitched_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict__ cosT, const T* __restrict__ sinT,
+                        int64_t units /* tokens * heads * pitch / 4 */, int heads, int hd, int pitch, int64_t pos_mod,
+                        int64_t pos_off) {
+  const int upr = pitch >> 2, half = hd >> 1;
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t th = u / upr;                   // token * heads + head
+    const int d = (int)(u - th * upr) * 4;        // first element of this unit inside the head
+    uint2 out = make_uint2(0, 0);
+    if (d < hd) {
+      const int64_t tok = th / heads;
+      const int64_t pos = (tok + pos_off) % pos_mod;
+      const T* xh = X + th * hd;
+      const T* ct = cosT + pos * hd;
+      const T* stb = sinT + pos * hd;
+      uint32_t w[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int j = d + 2 * q;
+        const bool first = j < half;
+        w[q] = rope_unit<T>(ldu(xh + j), ldu(xh + (first ? j + half : j - half)), ldu(ct + j), ldu(stb + j), first, false);
+      }
+      out = make_uint2(w[0], w[1]);
+    }
+    *reinterpret_cast<uint2*>(Y + u * 4) = out;     // plain store: the attention kernel reads it next, from L2
+  }
+}
+
 // Element-wise fallback for shapes/alignments the vector kernel does not take (head_dim not a
 // multiple of 4 for 16-bit types, token rows not a multiple of 16 bytes, unaligned views).
 template <typename T> __device__ __forceinline__ T rope_scalar(T own, T partner, T c, T s, bool first, bool backward) {
@@ -285,5 +317,32 @@ int cacti_b200_rope_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dp
                             int64_t pos_mod, int64_t pos_off, int dtype, int beta_dx, cacti_b200_stream stream) {
   return cb::rope_entry(true, true, y, dx, x, dy, cos, sin, tokens, heads, head_dim, pos_mod, pos_off, dtype, beta_dx,
                         stream);
+}
+int cacti_b200_rope_fwd_pitched(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr cos, cacti_b200_dptr sin,
+                                int64_t n_tokens, int64_t heads, int64_t head_dim, int64_t head_pitch, int64_t pos_mod,
+                                int64_t pos_offset, int dtype, cacti_b200_stream stream) {
+  using namespace cb;
+  if (n_tokens < 0 || heads < 0 || head_dim < 0 || head_pitch < head_dim || head_pitch > 0x3fffffffLL)
+    return CACTI_B200_ERR_INVALID_VALUE;
+  if (dtype != CACTI_B200_R_16F && dtype != CACTI_B200_R_16BF) return CACTI_B200_ERR_DTYPE;
+  if (n_tokens == 0 || heads == 0 || head_pitch == 0) return CACTI_B200_OK;
+  // 8-byte units: the head and its half must be multiples of 4 and 2 elements
+  if ((head_dim & 3) || (head_pitch & 3) || heads > 0x7fffffffLL) return CACTI_B200_ERR_SHAPE;
+  if (pos_mod <= 0 || pos_offset < 0) return CACTI_B200_ERR_INVALID_VALUE;
+  if (!y || (head_dim > 0 && (!x || !cos || !sin)) || (y & 7) || (x & 3) || (cos & 3) || (sin & 3))
+    return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t units = n_tokens * heads * (head_pitch / 4);
+  int64_t grid = (units + 255) / 256;
+  if (grid > (int64_t)kNumSMs * 32) grid = (int64_t)kNumSMs * 32;
+  if (dtype == CACTI_B200_R_16F)
+    rope_fwd_pitched_kernel<__half><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<__half*>(y), reinterpret_cast<const __half*>(x),
+        reinterpret_cast<const __half*>(cos), reinterpret_cast<const __half*>(sin), units, (int)heads, (int)head_dim,
+        (int)head_pitch, pos_mod, pos_offset);
+  else
+    rope_fwd_pitched_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(y),
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(cos),
+        reinterpret_cast<const __nv_bfloat16*>(sin), units, (int)heads, (int)head_dim, (int)head_pitch, pos_mod, pos_offset);
+  return check_launch();
 }
 }

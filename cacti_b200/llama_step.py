@@ -134,16 +134,19 @@ class TrainStep:
                 n1 = ops.rmsnorm_fwd(x, Lw["pre_norm"], cfg.eps)
             else:
                 n1, x = ops.add_rmsnorm_fwd(x, branch, Lw["pre_norm"], cfg.eps)
-            q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
-            k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
-            v = self._mm(n1, Lw["v"], False, True)
             if self.fused:
-                # head dimension zero-padded to 128 once; the padded copies also serve the backward pass
-                q, k, v = (ops.block_pad(t.view(B, S, H, hd), 128) for t in (q, k, v))
+                # q, k, v with the head dimension zero-padded to 128 (RoPE writes q and k that way directly); the
+                # padded copies also serve the backward pass
+                q = ops.rope_fwd_pitched(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
+                k = ops.rope_fwd_pitched(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
+                v = ops.block_pad(self._mm(n1, Lw["v"], False, True).view(B, S, H, hd), 128)
                 ctx, sc = ops.attention_fwd(q, k, v, hd, alpha)               # sc: the row statistics (m, l)
                 ctx = ctx.view(T, D)
-                self.launches += 4
+                self.launches += 2
             else:
+                q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
+                k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
+                v = self._mm(n1, Lw["v"], False, True)
                 sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha, TRI_C_LOWER)   # [B,S,H,S]
                 p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
                 ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)

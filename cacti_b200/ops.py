@@ -136,6 +136,15 @@ def rope_fwd(x, cos, sin, pos_off=0, y=None):
     return y
 
 
+def rope_fwd_pitched(x, cos, sin, head_pitch=128, pos_off=0, y=None):
+    """RoPE whose output heads are head_pitch wide, zeros after head_dim (= rope_fwd then block_pad, in one pass)."""
+    tokens, heads, hd = x.shape
+    y = torch.empty(tokens, heads, head_pitch, dtype=x.dtype, device=x.device) if y is None else y
+    check(lib().cacti_b200_rope_fwd_pitched(_ptr(y), _ptr(x), _ptr(cos), _ptr(sin), tokens, heads, hd, head_pitch,
+                                            cos.shape[0], pos_off, _dt(x), _stream()), "rope_fwd_pitched")
+    return y
+
+
 def rope_bwd(dy, cos, sin, pos_off=0, dx=None, beta=0):
     tokens, heads, hd = dy.shape
     dx = torch.empty_like(dy) if dx is None else dx

@@ -172,6 +172,13 @@ int cacti_b200_rope_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200_dp
                             int64_t tokens, int64_t heads, int64_t head_dim, int64_t pos_mod, int64_t pos_off,
                             int dtype, int beta_dx, cacti_b200_stream stream);
 
+/* Forward RoPE with a head-pitched output: y is [n_tokens, heads, head_pitch], each head's head_dim rotated values
+ * followed by zeros, bit-identical to cacti_b200_rope_fwd followed by cacti_b200_block_pad to head_pitch columns (the
+ * layout the fused attention reads q and k in; saves that pass).  16-bit types, head_dim % 4 == 0, head_pitch % 4 == 0. */
+int cacti_b200_rope_fwd_pitched(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200_dptr cos, cacti_b200_dptr sin,
+                                int64_t n_tokens, int64_t heads, int64_t head_dim, int64_t head_pitch, int64_t pos_mod,
+                                int64_t pos_offset, int dtype, cacti_b200_stream stream);
+
 /* ---- K4 SwiGLU -----------------------------------------------------------------------
  * Replaces StandardSilu (src/thunk/op.rs:2867-2910) + Mul (:2001-2056) of
  * src/librarium/llama.rs:526-527 and their adjoints (Logistic :2821-2865 recomputed).

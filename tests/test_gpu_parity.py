@@ -130,6 +130,23 @@ def test_softmax_golden(cuda, case):
     assert_close(host(ds3)[keep], GOLD[f"c{case}_ds"][keep], "float16", "dS (pre-masked)")
 
 
+@pytest.mark.parametrize("heads,hd,pitch,bf16", [(32, 100, 128, False), (3, 64, 64, False), (2, 20, 32, False), (4, 100, 128, True)])
+def test_rope_fwd_pitched_equals_rope_then_pad(cuda, heads, hd, pitch, bf16):
+    """Head-pitched RoPE output = rope_fwd followed by block_pad, bit for bit; positions wrap and start at an offset."""
+    tokens, seq = 70, 32
+    x = dev(R.normal(95, (tokens, heads, hd), np.float32), bf16=True) if bf16 else dev(R.normal(95, (tokens, heads, hd), np.float16))
+    cos, sin = ops.rope_tables(seq, hd, 10000.0, x.dtype, "cuda")
+    want = ops.block_pad(ops.rope_fwd(x, cos, sin, pos_off=5).view(1, tokens, heads, hd), pitch).view(tokens, heads, pitch)
+    got = torch.full((tokens, heads, pitch), 7.0, dtype=x.dtype, device="cuda")
+    ops.rope_fwd_pitched(x, cos, sin, pitch, pos_off=5, y=got)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    L = capi.lib()
+    P = x.data_ptr()
+    assert L.cacti_b200_rope_fwd_pitched(P, P, P, P, 4, 2, 100, 96, 8, 0, capi.R_16F, None) == capi.ERR_INVALID_VALUE   # pitch < head_dim
+    assert L.cacti_b200_rope_fwd_pitched(P, P, P, P, 4, 2, 102, 128, 8, 0, capi.R_16F, None) == capi.ERR_SHAPE
+    assert L.cacti_b200_rope_fwd_pitched(P, P, P, P, 4, 2, 100, 128, 8, 0, capi.R_32F, None) == capi.ERR_DTYPE
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
 @pytest.mark.parametrize("rows,cols", [(1, 8), (37, 3200), (300, 104), (64, 8192), (5, 20000), (9, 7), (16, 3201)])
 def test_add_rmsnorm_fwd_equals_separate_steps(cuda, dtype, rows, cols):
