@@ -4,7 +4,7 @@
 // inner_softmax, lossy_cast, block_matmul (P V) (src/librarium/llama.rs:501-507), each a full pass over the
 // [B, S, H, S] score tensor in HBM (268 MB per sequence at S = 2048, H = 32).  Here one kernel per 128 query rows
 // keeps the scores in tensor memory and the probabilities in shared memory; HBM sees Q, K, V, the context rows and
-// two floats of row statistics.
+// the row statistics (maximum and sum; 16 bytes per row with two words of scratch for the backward pass).
 //
 // Arithmetic follows the reference chain where it rounds: scores are alpha * (q . k) accumulated in f32 and rounded
 // to the 16-bit type (block_matmul_scale's output), the softmax runs in f32 on those rounded scores with the row
