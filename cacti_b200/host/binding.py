@@ -22,6 +22,7 @@ def lib():
             "cbh_pwrite": (C.c_uint64, [_p, _i64]), "cbh_pin": (None, [_p, _i64]), "cbh_unpin": (None, [_p, _i64]),
             "cbh_in_use": (_sz, [_p]), "cbh_sync": (C.c_int, [_p]), "cbh_stats": (None, [_p, C.POINTER(C.c_long)]),
             "cbh_thunk_rmsnorm_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, C.c_float, _i64, _i64, C.c_int]),
+            "cbh_thunk_add_rmsnorm_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, C.c_float, _i64, _i64, C.c_int]),
             "cbh_thunk_softmax_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
             "cbh_thunk_softmax_bwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
             "cbh_thunk_add": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, C.c_int]),

@@ -257,6 +257,18 @@ int thunk_rmsnorm_fwd(PCtx& p, Mode m, int64_t y, int64_t x, int64_t gamma, floa
   return rc;
 }
 
+// Two-output thunk: sum = a + b and y = rmsnorm(sum) in one kernel (the residual add fused into the norm that follows
+// it, src/librarium/llama.rs:514-516).  Apply only: both outputs are fresh cells of the forward pass.
+int thunk_add_rmsnorm_fwd(PCtx& p, Mode m, int64_t y, int64_t sum, int64_t a, int64_t b_, int64_t gamma, float eps, int64_t rows,
+                          int64_t cols, int dtype) {
+  if (m != kApply) return CACTI_B200_ERR_INVALID_VALUE;
+  Binding b(p);
+  const uint64_t da = b.in(a), db = b.in(b_), dg = b.in(gamma);
+  const uint64_t dy = b.out(y, kApply), ds = b.out(sum, kApply);
+  if (!b.ok) return -1;
+  return cacti_b200_add_rmsnorm_fwd(dy, ds, da, db, dg, eps, rows, cols, dtype, p.stream());
+}
+
 int thunk_softmax_fwd(PCtx& p, Mode m, int64_t prob, int64_t s, int64_t rows, int64_t cols, int64_t q_div, int64_t q_mod, int dtype) {
   if (m != kApply) return CACTI_B200_ERR_INVALID_VALUE;
   Binding b(p);
@@ -326,6 +338,10 @@ void cbh_stats(void* c, long* out5) {   // six values
 }
 int cbh_thunk_rmsnorm_fwd(void* c, int mode, int64_t y, int64_t x, int64_t gamma, float eps, int64_t rows, int64_t cols, int dtype) {
   return cbh::thunk_rmsnorm_fwd(*static_cast<cbh::PCtx*>(c), (cbh::Mode)mode, y, x, gamma, eps, rows, cols, dtype);
+}
+int cbh_thunk_add_rmsnorm_fwd(void* c, int mode, int64_t y, int64_t sum, int64_t a, int64_t b, int64_t gamma, float eps, int64_t rows,
+                              int64_t cols, int dtype) {
+  return cbh::thunk_add_rmsnorm_fwd(*static_cast<cbh::PCtx*>(c), (cbh::Mode)mode, y, sum, a, b, gamma, eps, rows, cols, dtype);
 }
 int cbh_thunk_softmax_fwd(void* c, int mode, int64_t p, int64_t s, int64_t rows, int64_t cols, int64_t q_div, int64_t q_mod, int dtype) {
   return cbh::thunk_softmax_fwd(*static_cast<cbh::PCtx*>(c), (cbh::Mode)mode, p, s, rows, cols, q_div, q_mod, dtype);

@@ -111,6 +111,8 @@ class PCtx {
 // ThunkImpl-shaped wrappers: `out` is bound as pwrite (Apply) or prewrite (Accumulate).  Return the C-ABI code,
 // or -1 for a hard OOM.
 int thunk_rmsnorm_fwd(PCtx& p, Mode m, int64_t y, int64_t x, int64_t gamma, float eps, int64_t rows, int64_t cols, int dtype);
+int thunk_add_rmsnorm_fwd(PCtx& p, Mode m, int64_t y, int64_t sum, int64_t a, int64_t b, int64_t gamma, float eps, int64_t rows,
+                          int64_t cols, int dtype);
 int thunk_softmax_fwd(PCtx& p, Mode m, int64_t prob, int64_t s, int64_t rows, int64_t cols, int64_t q_div, int64_t q_mod, int dtype);
 int thunk_softmax_bwd(PCtx& p, Mode m, int64_t ds, int64_t s, int64_t dp, int64_t rows, int64_t cols, int64_t q_div, int64_t q_mod, int dtype);
 int thunk_add(PCtx& p, Mode m, int64_t out, int64_t a, int64_t b, int64_t n, int dtype);

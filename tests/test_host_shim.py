@@ -113,3 +113,22 @@ def test_reference_style_sync_per_thunk(cuda):
     y, _, _ = R.ref_rmsnorm_fwd(x, g, 1e-6)
     assert_close(ctx.get(cy, x), y + y, "float16", "y accumulated twice", floor_frac=1.0)
     ctx.close()
+
+
+@pytest.mark.gpu
+def test_two_output_fused_thunk_matches_the_two_thunks(cuda):
+    """add + rmsnorm as one two-output thunk through the shim: same bits as thunk_add followed by thunk_rmsnorm_fwd."""
+    rows, cols = 96, 3200
+    f16 = capi.R_16F
+    a, b = R.normal(11, (rows, cols), np.float16), R.normal(12, (rows, cols), np.float16, 0.3)
+    gamma = R.normal(13, (cols,), np.float16, 0.02, 1.0)
+    ctx = H.Ctx(cuda=True, arena_bytes=64 * a.nbytes, soft_limit=64 * a.nbytes)
+    L, h = ctx.L, ctx.h
+    ca, cb, cg = ctx.cell(a), ctx.cell(b), ctx.cell(gamma)
+    cs1, cy1, cs2, cy2 = (ctx.cell(nbytes=a.nbytes) for _ in range(4))
+    assert L.cbh_thunk_add(h, H.APPLY, cs1, ca, cb, rows * cols, f16) == 0
+    assert L.cbh_thunk_rmsnorm_fwd(h, H.APPLY, cy1, cs1, cg, 1e-6, rows, cols, f16) == 0
+    assert L.cbh_thunk_add_rmsnorm_fwd(h, H.APPLY, cy2, cs2, ca, cb, cg, 1e-6, rows, cols, f16) == 0
+    assert L.cbh_thunk_add_rmsnorm_fwd(h, H.ACCUMULATE, cy2, cs2, ca, cb, cg, 1e-6, rows, cols, f16) == capi.ERR_INVALID_VALUE
+    assert np.array_equal(ctx.get(cs1, a).view(np.uint16), ctx.get(cs2, a).view(np.uint16))
+    assert np.array_equal(ctx.get(cy1, a).view(np.uint16), ctx.get(cy2, a).view(np.uint16))
