@@ -8,7 +8,7 @@ __device__ unsigned g_dev_error = 0;
 extern int g_softmax_threads, g_softmax_waves;
 extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_smem_kb;
 extern int g_nll_gpref, g_nll_stages, g_nll_mode, g_nll_smem_threads;
-extern int g_rope_threads, g_rope_ctas_per_sm;
+extern int g_rope_threads, g_rope_ctas_per_sm, g_rope_staged, g_rope_staged_g, g_rope_staged_groups, g_rope_staged_stages;
 extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
 extern int g_gemm_bn, g_gemm_group_m, g_gemm_sms, g_gemm_pair;
 }  // namespace cb
@@ -56,6 +56,8 @@ int cacti_b200_tune(const char* name, int value) {
       {"rmsnorm_smem_kb", &g_rmsnorm_smem_kb, 16, 200},
       {"nll_gpref", &g_nll_gpref, 32, 512},               {"nll_stages", &g_nll_stages, 1, 4}, {"nll_mode", &g_nll_mode, 0, 1}, {"nll_smem_threads", &g_nll_smem_threads, 256, 384},
       {"rope_threads", &g_rope_threads, 32, 256},         {"rope_ctas_per_sm", &g_rope_ctas_per_sm, 1, 64},
+      {"rope_staged", &g_rope_staged, 0, 1},              {"rope_staged_g", &g_rope_staged_g, 32, 512},
+      {"rope_staged_groups", &g_rope_staged_groups, 1, 15}, {"rope_staged_stages", &g_rope_staged_stages, 2, 8},
       {"gemm_bn", &g_gemm_bn, 0, 256}, {"gemm_group_m", &g_gemm_group_m, 0, 4096}, {"gemm_sms", &g_gemm_sms, 0, 148}, {"gemm_pair", &g_gemm_pair, 0, 1},
       {"swiglu_threads", &g_swiglu_threads, 32, 256},     {"swiglu_ctas_per_sm", &g_swiglu_ctas_per_sm, 1, 64},
   };

@@ -20,6 +20,25 @@ inline int check_launch() {
 
 inline bool aligned16(uint64_t p) { return (p & 15u) == 0; }
 
+// Programmatic dependent launch, for a short second kernel that consumes what the kernel before it in the stream
+// wrote (a partial-sum fold): launched this way, its launch and block scheduling overlap the tail of the previous
+// kernel instead of following its completion.  The kernel launched with launch_dependent() must execute
+// dependent_wait() before it reads anything the previous kernel wrote (the wait returns once that kernel has
+// completed and its writes are visible); the previous kernel may call dependents_may_launch() once a CTA has
+// nothing long left to do, otherwise the hand-over happens as its CTAs exit.
+__device__ __forceinline__ void dependent_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kern)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- element traits ------------------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {

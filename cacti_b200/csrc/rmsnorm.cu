@@ -160,6 +160,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
   (void)alive;
 
   if (BWD) {
+    dependents_may_launch();      // the finalize kernel may be scheduled while the last CTAs fold their partials
     // fold the CTA's row groups in group order, then one partial row per CTA
     for (int q = 0; q < groups; ++q) {
       if (g.gid == q) {
@@ -191,6 +192,7 @@ rmsnorm_dgamma_finalize_kernel(TO* __restrict__ dgamma, const float* __restrict_
   const int cx = threadIdx.x & 31, sy = threadIdx.x >> 5;     // 32 columns x 16 slices
   const int j = blockIdx.x * 32 + cx;
   float acc = 0.f;
+  dependent_wait();                                           // the partial rows come from the kernel before this one
   if (j < cols) for (int p = sy; p < nparts; p += 16) acc += partial[(size_t)p * cols + j];
   sm[sy][cx] = acc;
   __syncthreads();
@@ -304,8 +306,8 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
 #undef CB_LAUNCH
         int rc = check_launch();
         if (rc || !BWD) return rc;
-        rmsnorm_dgamma_finalize_kernel<TO><<<(unsigned)((cols + 31) / 32), 512, 0, st>>>(dG, wsf, (int)grid,
-                                                                                        (int)cols, beta_dg);
+        launch_dependent(rmsnorm_dgamma_finalize_kernel<TO>, (unsigned)((cols + 31) / 32), 512u, st, dG,
+                         (const float*)wsf, (int)grid, (int)cols, beta_dg);
         return check_launch();
       }
     }

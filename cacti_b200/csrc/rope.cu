@@ -22,11 +22,29 @@ namespace cb {
 
 int g_rope_threads = 256;
 int g_rope_ctas_per_sm = 8;
+int g_rope_staged = 1;             // 1: staged kernel where it applies; 0: vector kernel (measurement knob)
+int g_rope_staged_g = 160;         // staged kernel: threads per row group
+int g_rope_staged_groups = 2;      // staged kernel: row groups per CTA
+int g_rope_staged_stages = 3;      // staged kernel: rows in the ring of a group
 
 template <typename T> struct Unit;         // one 4-byte unit
 template <> struct Unit<__half> { static constexpr int UPV = 2; };
 template <> struct Unit<__nv_bfloat16> { static constexpr int UPV = 2; };
 template <> struct Unit<float> { static constexpr int UPV = 1; };
+
+// Division by a run-time constant as multiply-high + shift (round-up method), exact for dividends below 2^31.  The
+// index arithmetic of the vector kernels (vector -> token -> position, offset inside the head) otherwise costs two
+// emulated 64-bit divisions per 16-byte vector, which showed as issue-slot pressure in a kernel that should only wait
+// on memory.
+struct FastDiv { uint32_t d, magic, shift; };
+static FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f; f.d = d; f.shift = 0;
+  while ((1ull << f.shift) < d) ++f.shift;
+  f.magic = (uint32_t)(((((1ull << f.shift) - d) << 32) / d) + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) { return (__umulhi(n, f.magic) + n) >> f.shift; }
+__device__ __forceinline__ uint32_t fmod_(uint32_t n, const FastDiv& f) { return n - fdiv(n, f) * f.d; }
 
 template <typename T> __device__ __forceinline__ uint32_t ldu(const T* p) {      // 4-byte aligned
   return __ldg(reinterpret_cast<const unsigned int*>(p));
@@ -83,11 +101,12 @@ template <typename T> __device__ __forceinline__ uint32_t add_unit(uint32_t old,
   }
 }
 
-template <typename T, bool FWD, bool BWD>
+// I32: every index fits 31 bits, divisions go through FastDiv (fd_vpr, fd_hd, fd_pos); otherwise plain 64-bit division.
+template <typename T, bool FWD, bool BWD, bool I32>
 __global__ void __launch_bounds__(256)
 rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, const T* __restrict__ dY,
                 const T* __restrict__ cosT, const T* __restrict__ sinT, int64_t nvec, int vpr /* vectors per token row */,
-                int hd, int64_t pos_mod, int64_t pos_off, int beta) {
+                int hd, int64_t pos_mod, int64_t pos_off, int beta, FastDiv fd_vpr, FastDiv fd_hd, FastDiv fd_pos) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int UPV = Unit<T>::UPV;
   constexpr int NU = 4;                       // units per vector
@@ -111,13 +130,23 @@ rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, 
     for (int u = 0; u < UNR; ++u) {
       const int64_t v = v0 + u * stride;
       if (v >= nvec) break;
-      const int64_t tok = v / vpr;
-      const int r = (int)(v - tok * vpr) * VEC;           // element offset inside the token row
+      int64_t pos;
+      int r;                                               // element offset inside the token row
+      int j;                                               // element offset inside the head
+      if (I32) {
+        const uint32_t tok = fdiv((uint32_t)v, fd_vpr);
+        r = (int)((uint32_t)v - tok * (uint32_t)vpr) * VEC;
+        pos = fmod_(tok + (uint32_t)pos_off, fd_pos);
+        j = (int)fmod_((uint32_t)r, fd_hd);
+      } else {
+        const int64_t tok = v / vpr;
+        r = (int)(v - tok * vpr) * VEC;
+        pos = (tok + pos_off) % pos_mod;
+        j = r % hd;
+      }
       const int64_t e0 = v * VEC;                          // flat element index
-      const int64_t pos = (tok + pos_off) % pos_mod;
       const T* ct = cosT + pos * hd;
       const T* stb = sinT + pos * hd;
-      int j = r % hd;
       uint32_t yo[NU], dout[NU];
       const uint32_t xw[NU] = {xo[u].x, xo[u].y, xo[u].z, xo[u].w};
       const uint32_t gw[NU] = {go[u].x, go[u].y, go[u].z, go[u].w};
@@ -143,6 +172,104 @@ rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, 
       }
     }
   }
+}
+
+// Staged form of the fused kernel, for 16-byte aligned token rows.  A group of G threads owns one token row at a
+// time: the x row and the dy row arrive in shared memory by bulk copies behind an mbarrier (a ring of rows per
+// group, so the next rows are in flight while one is computed); each thread rotates (head, unit) pairs in place --
+// consecutive threads take consecutive 4-byte units, so every shared-memory access of a warp is conflict-free, and
+// a pair is read and written by one thread only -- and the finished rows leave by bulk stores from the same
+// buffer.  The load/store units then carry only the table loads; global memory traffic is moved by the copy engine.
+// A slot is refilled one row late, once the bulk store that read it has finished reading.
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+
+template <typename T, bool FWD, bool BWD>
+__global__ void __launch_bounds__(512)
+rope_staged_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, const T* __restrict__ dY,
+                   const T* __restrict__ cosT, const T* __restrict__ sinT, int64_t tokens, int row_len, int hd,
+                   int items, FastDiv fd_uh, int G, int nstages, int64_t pos_mod, int64_t pos_off) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int UPV = Unit<T>::UPV;
+  const int groups = blockDim.x / G;
+  const int gid = threadIdx.x / G, lane = threadIdx.x - gid * G;
+  const unsigned row_bytes = (unsigned)row_len * sizeof(T);
+  const unsigned stage_bytes = row_bytes * ((FWD && BWD) ? 2 : 1);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * stage_bytes);
+  unsigned char* stage0 = smem_raw + (size_t)gid * nstages * stage_bytes;
+  uint64_t* bar0 = bars + gid * nstages;
+  if (lane < nstages) mbar_init(bar0 + lane, 1);
+  mbar_fence_init();
+  __syncthreads();
+  const int half = hd >> 1;
+  const int64_t stride = (int64_t)gridDim.x * groups;
+  const int64_t row0 = (int64_t)blockIdx.x * groups + gid;
+  const int64_t pstep = stride % pos_mod;
+  int64_t pos = (row0 + pos_off) % pos_mod;
+
+  auto issue = [&](int64_t r, int sl) {       // lane 0 only
+    unsigned char* dst = stage0 + (size_t)sl * stage_bytes;
+    mbar_expect_tx(bar0 + sl, stage_bytes);
+    if (FWD) bulk_g2s(dst, X + r * row_len, row_bytes, bar0 + sl);
+    if (BWD) bulk_g2s(dst + (FWD ? row_bytes : 0), dY + r * row_len, row_bytes, bar0 + sl);
+  };
+  if (lane == 0)
+    for (int sl = 0; sl < nstages; ++sl)
+      if (row0 + sl * stride < tokens) issue(row0 + sl * stride, sl);
+
+  int slot = 0;
+  unsigned phase = 0;
+  int prev_slot = -1;
+  int64_t prev_row = 0;
+  for (int64_t row = row0; row < tokens; row += stride) {
+    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) break;
+    T* sx = reinterpret_cast<T*>(stage0 + (size_t)slot * stage_bytes);
+    T* sg = reinterpret_cast<T*>(stage0 + (size_t)slot * stage_bytes + (FWD ? row_bytes : 0));
+    const T* ct = cosT + pos * hd;
+    const T* stb = sinT + pos * hd;
+#pragma unroll 5
+    for (int n = lane; n < items; n += G) {
+      const uint32_t h = fdiv((uint32_t)n, fd_uh);
+      const int i = (int)((uint32_t)n - h * fd_uh.d) * UPV;          // element offset inside the half head
+      const int e = (int)h * hd + i;                                 // element offset inside the token row
+      const uint32_t c1 = ldu(ct + i), c2 = ldu(ct + i + half), s1 = ldu(stb + i), s2 = ldu(stb + i + half);
+      if (FWD) {
+        uint32_t* p1 = reinterpret_cast<uint32_t*>(sx + e);
+        uint32_t* p2 = reinterpret_cast<uint32_t*>(sx + e + half);
+        const uint32_t x1 = *p1, x2 = *p2;
+        *p1 = rope_unit<T>(x1, x2, c1, s1, true, false);
+        *p2 = rope_unit<T>(x2, x1, c2, s2, false, false);
+      }
+      if (BWD) {
+        uint32_t* p1 = reinterpret_cast<uint32_t*>(sg + e);
+        uint32_t* p2 = reinterpret_cast<uint32_t*>(sg + e + half);
+        const uint32_t g1 = *p1, g2 = *p2;
+        *p1 = rope_unit<T>(g1, g2, c1, s2, true, true);
+        *p2 = rope_unit<T>(g2, g1, c2, s1, false, true);
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the bulk store reads what was just written
+    if (G == 32) __syncwarp();
+    else asm volatile("bar.sync %0, %1;" ::"r"(gid + 1), "r"(G) : "memory");
+    if (lane == 0) {
+      if (FWD) bulk_s2g(Y + row * row_len, sx, row_bytes);
+      if (BWD) bulk_s2g(dX + row * row_len, sg, row_bytes);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      if (prev_slot >= 0) {
+        // the store of the previous row has finished reading its slot: refill it
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        const int64_t next = prev_row + (int64_t)nstages * stride;
+        if (next < tokens) issue(next, prev_slot);
+      }
+    }
+    prev_slot = slot; prev_row = row;
+    if (++slot == nstages) { slot = 0; phase ^= 1; }
+    pos += pstep;
+    if (pos >= pos_mod) pos -= pos_mod;
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
 }
 
 // Forward RoPE whose output rows are head-pitched: y[tok][h][0 .. pitch) with the head's head_dim rotated values
@@ -244,13 +371,47 @@ static int launch_rope(uint64_t y, uint64_t dx, uint64_t x, uint64_t dy, uint64_
                       (!FWD || (aligned16(x) && aligned16(y))) && (!BWD || (aligned16(dy) && aligned16(dx))) &&
                       row_len / VEC <= 0x7fffffffLL;
   const int threads = g_rope_threads;
+  const int64_t units_half = (hd / 2) / UPV;
+  const int64_t items = heads * units_half;
+  const bool staged_ok = g_rope_staged && vec_ok && !beta && items <= 0x7fffffffLL && row_len <= 0x3fffffffLL &&
+                         ((c | s) % 4 == 0);
+  if (staged_ok) {
+    int G = g_rope_staged_g;
+    if (G > items) G = (int)((items + 31) / 32 * 32);
+    int groups = g_rope_staged_groups;
+    if (G * groups > 512) groups = 512 / G;
+    if (groups > kMaxGroupsPerCta) groups = kMaxGroupsPerCta;
+    const size_t stage = (size_t)row_len * sizeof(T) * ((FWD && BWD) ? 2 : 1);
+    int nst = g_rope_staged_stages;
+    auto smem_for = [&](int ns) { return (size_t)groups * ns * (stage + sizeof(uint64_t)); };
+    while (nst > 2 && smem_for(nst) > kMaxDynSmem) --nst;
+    while (groups > 1 && smem_for(nst) > kMaxDynSmem) --groups;
+    const size_t smem = smem_for(nst);
+    if (groups >= 1 && smem <= kMaxDynSmem && G <= 512) {
+      auto kern = rope_staged_kernel<T, FWD, BWD>;
+      const int threads_s = G * groups;
+      int64_t grid = (int64_t)kNumSMs * resident_ctas(kern, threads_s, smem);
+      const int64_t want = (tokens + groups - 1) / groups;
+      if (grid > want) grid = want;
+      kern<<<(unsigned)grid, threads_s, smem, st>>>(Y, dX, X, dY, C, S, tokens, (int)row_len, (int)hd, (int)items,
+                                                   make_fastdiv((uint32_t)units_half), G, nst, pos_mod, pos_off);
+      return check_launch();
+    }
+  }
   if (vec_ok) {
     const int64_t nvec = n / VEC;
     int64_t grid = (nvec + threads - 1) / threads;
     const int64_t cap = (int64_t)kNumSMs * g_rope_ctas_per_sm;
     if (grid > cap) grid = cap;
-    rope_vec_kernel<T, FWD, BWD><<<(unsigned)grid, threads, 0, st>>>(Y, dX, X, dY, C, S, nvec, (int)(row_len / VEC),
-                                                                    (int)hd, pos_mod, pos_off, beta);
+    const int vpr = (int)(row_len / VEC);
+    const bool i32 = nvec < 0x7fffffffLL && pos_mod < 0x7fffffffLL && tokens + pos_off < 0x7fffffffLL;
+    if (i32)
+      rope_vec_kernel<T, FWD, BWD, true><<<(unsigned)grid, threads, 0, st>>>(
+          Y, dX, X, dY, C, S, nvec, vpr, (int)hd, pos_mod, pos_off, beta, make_fastdiv((uint32_t)vpr),
+          make_fastdiv((uint32_t)hd), make_fastdiv((uint32_t)pos_mod));
+    else
+      rope_vec_kernel<T, FWD, BWD, false><<<(unsigned)grid, threads, 0, st>>>(
+          Y, dX, X, dY, C, S, nvec, vpr, (int)hd, pos_mod, pos_off, beta, FastDiv{}, FastDiv{}, FastDiv{});
     return check_launch();
   }
   int64_t grid = (n + threads - 1) / threads;

@@ -294,6 +294,7 @@ nll_loss_sum_kernel(float* __restrict__ loss_sum, const float* __restrict__ loss
                     const float* __restrict__ w_rows, float w_scalar, int64_t rows) {
   __shared__ float sm[1024];
   float acc = 0.f;
+  dependent_wait();                                           // the per-row losses come from the kernel before this one
   for (int64_t i = threadIdx.x; i < rows; i += 1024) acc += (w_rows ? w_rows[i] : w_scalar) * loss_rows[i];
   sm[threadIdx.x] = acc;
   __syncthreads();
@@ -403,7 +404,8 @@ int cacti_b200_softmax_nll_fwd_bwd(cacti_b200_dptr loss_sum, cacti_b200_dptr los
   });
   if (rc) return rc;
   if (loss_sum) {
-    nll_loss_sum_kernel<<<1, 1024, 0, st>>>(reinterpret_cast<float*>(loss_sum), lrows, wr, w_scalar, rows);
+    launch_dependent(nll_loss_sum_kernel, 1u, 1024u, st, reinterpret_cast<float*>(loss_sum), (const float*)lrows,
+                     (const float*)wr, w_scalar, rows);
     return check_launch();
   }
   return CACTI_B200_OK;
