@@ -307,7 +307,7 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
     tok, tgt = torch.empty_like(tok_all[sl]), torch.empty_like(tgt_all[sl])
     nl = cfg.layers
 
-    def one():
+    def body():
         # end to end: token ids come from pinned host memory, the loss goes back to the host
         tok.copy_(h_tok, non_blocking=True); tgt.copy_(h_tgt, non_blocking=True)
         loss = step.forward_backward(tok, tgt, grads, on_layer_done=red.reduce_bucket)
@@ -315,7 +315,23 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
         red.finish()
         if world > 1:
             dist.all_reduce(loss)
-        return loss.cpu()
+        return loss
+
+    # the step is replayed from a CUDA graph (kernels, pinned-memory token copies and the bucketed all-reduces are all
+    # captured); CACTI_B200_STEP_GRAPH=0 launches it eagerly instead
+    launch = "eager"
+    graphed = None
+    if os.environ.get("CACTI_B200_STEP_GRAPH", "1") != "0":
+        try:
+            graphed = LS.GraphedStep(body)
+            launch = "cuda graph"
+        except Exception as e:                         # same kernels either way; the line says which launch it timed
+            graphed = None
+            launch = "eager (graph capture failed: %s)" % (str(e).splitlines()[0][:120] if str(e) else type(e).__name__)
+            torch.cuda.synchronize()
+
+    def one():
+        return (graphed.replay() if graphed is not None else body()).cpu()
 
     for _ in range(2):
         one()
@@ -337,7 +353,7 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
     ops.lib().cacti_b200_tune(b"gemm_sms", 0)
     return {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (benchmark config 5)",
             "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "scaling": "strong", "n_gpus": world,
-            "sequences_per_gpu": count, "loss": float(loss.item()), "gpu_launches_per_step": step.launches,
+            "sequences_per_gpu": count, "loss": float(loss.item()), "gpu_launches_per_step": step.launches, "launch": launch,
             "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
             "h2d_bytes_per_step": 2 * count * cfg.seq * 4, "d2h_bytes_per_step": 4,
             "note": "no optimizer step (the optimizer thunks are outside this path); gradients of all parameters are produced and all-reduced"}

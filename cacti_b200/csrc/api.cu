@@ -6,7 +6,7 @@ namespace cb {
 thread_local int g_last_cuda_error = 0;
 __device__ unsigned g_dev_error = 0;
 extern int g_softmax_threads, g_softmax_waves;
-extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_smem_kb;
+extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_smem_kb, g_rmsnorm_bulk_out;
 extern int g_nll_gpref, g_nll_stages, g_nll_mode, g_nll_smem_threads;
 extern int g_rope_threads, g_rope_ctas_per_sm, g_rope_staged, g_rope_staged_g, g_rope_staged_groups, g_rope_staged_stages;
 extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
@@ -53,7 +53,7 @@ int cacti_b200_tune(const char* name, int value) {
   const Knob knobs[] = {
       {"softmax_threads", &g_softmax_threads, 32, 512},   {"softmax_waves", &g_softmax_waves, 1, 64},
       {"rmsnorm_threads", &g_rmsnorm_threads, 32, 512},   {"rmsnorm_gpref", &g_rmsnorm_gpref, 32, 512},
-      {"rmsnorm_smem_kb", &g_rmsnorm_smem_kb, 16, 200},
+      {"rmsnorm_smem_kb", &g_rmsnorm_smem_kb, 16, 200},    {"rmsnorm_bulk_out", &g_rmsnorm_bulk_out, 0, 1},
       {"nll_gpref", &g_nll_gpref, 32, 512},               {"nll_stages", &g_nll_stages, 1, 4}, {"nll_mode", &g_nll_mode, 0, 1}, {"nll_smem_threads", &g_nll_smem_threads, 256, 384},
       {"rope_threads", &g_rope_threads, 32, 256},         {"rope_ctas_per_sm", &g_rope_ctas_per_sm, 1, 64},
       {"rope_staged", &g_rope_staged, 0, 1},              {"rope_staged_g", &g_rope_staged_g, 32, 512},

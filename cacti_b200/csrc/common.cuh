@@ -236,6 +236,13 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// Bulk store shared -> global (16-byte aligned addresses and size), joined to the thread's current bulk group.
+// Shared memory written by ordinary stores needs fence.proxy.async before the copy engine reads it.
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+
 // ---- block reduction for the element-wise fallback kernels (whole CTA = one row) -----------
 template <typename Op> __device__ __forceinline__ float block_reduce(float v, float* smem /* >= 33 floats */) {
   v = warp_reduce<Op>(v);

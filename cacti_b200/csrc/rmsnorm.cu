@@ -18,6 +18,7 @@ namespace cb {
 int g_rmsnorm_threads = 512;      // target threads per CTA on the vector path
 int g_rmsnorm_gpref = 256;        // preferred threads per row group
 int g_rmsnorm_smem_kb = 96;       // shared memory per CTA spent on the row ring
+int g_rmsnorm_bulk_out = 1;       // 1: outputs leave by bulk stores from shared memory; 0: by per-thread streaming stores
 
 constexpr int kRmsMaxPartials = kNumSMs * 8;
 
@@ -28,8 +29,9 @@ __global__ void __launch_bounds__(512)
 rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
                     const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
                     float eps, int64_t rows, int cols, int G, int nstages, int beta_dx,
-                    const T* __restrict__ R = nullptr, T* __restrict__ SUM = nullptr) {
+                    const T* __restrict__ R = nullptr, T* __restrict__ SUM = nullptr, int bulk_out_arg = 0) {
   static_assert(!ADD || (FWD && !BWD), "the residual add is fused into the forward norm only");
+  const int bulk_out = BWD ? 0 : bulk_out_arg;      // the backward kernels carry no bulk-store code (see launch_rmsnorm)
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
@@ -74,9 +76,20 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
   int slot = 0;
   unsigned phase = 0;
   bool alive = true;
+  // bulk_out: the output rows are assembled in one of two shared-memory buffers of the group and leave by bulk
+  // stores, so that the copy engine carries all the traffic of the row and the threads never wait on a store; a
+  // buffer is reused two rows later, after lane 0 has seen the store that read it finish reading.
+  constexpr int kOutRows = (ADD || (FWD && BWD)) ? 2 : 1;
+  const unsigned out_bytes = row_bytes * kOutRows;
+  unsigned char* outbuf0 = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(colacc + (BWD ? cols : 0)) + 15) & ~(uintptr_t)15) + (size_t)g.gid * 2 * out_bytes;
+  unsigned it = 0;
   for (int64_t row = row0; row < rows; row += stride) {
     if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) { alive = false; break; }
     const unsigned char* stage = stage0 + (size_t)slot * stage_bytes;
+    unsigned char* ob = outbuf0 + (size_t)(it & 1) * out_bytes;
+    ++it;
+    if (bulk_out && g.lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     uint4 xraw[NV], yraw[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -91,7 +104,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
 #pragma unroll
           for (int e = 0; e < VEC; ++e) a[e] = __fadd_rn(a[e], b[e]);
           xraw[k] = pack<T>(a);                  // rounded to T: what a separate add would have stored
-          st_stream(SUM + row * cols + col0, xraw[k]);
+          if (!bulk_out) st_stream(SUM + row * cols + col0, xraw[k]);
         }
       }
     }
@@ -140,7 +153,12 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
           float y[VEC];
 #pragma unroll
           for (int e = 0; e < VEC; ++e) y[e] = __fmul_rn(gm[e], t[e]);
-          st_stream(Y + row * cols + col0, pack<T>(y));
+          if (bulk_out) {
+            if (ADD) *reinterpret_cast<uint4*>(ob + (size_t)col0 * sizeof(T)) = xraw[k];
+            *reinterpret_cast<uint4*>(ob + (ADD ? row_bytes : 0u) + (size_t)col0 * sizeof(T)) = pack<T>(y);
+          } else {
+            st_stream(Y + row * cols + col0, pack<T>(y));
+          }
         }
         if (BWD) {
           float gy[VEC], d[VEC];
@@ -152,12 +170,28 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
           }
           T* o = dX + row * cols + col0;
           if (beta_dx) st_stream(o, pack_accumulate<T>(d, ld_stream(o)));
+          else if (bulk_out) *reinterpret_cast<uint4*>(ob + (FWD ? row_bytes : 0u) + (size_t)col0 * sizeof(T)) = pack<T>(d);
           else st_stream(o, pack<T>(d));
         }
       }
     }
+    if (bulk_out) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      group_barrier(g);
+      if (g.lane == 0) {
+        if (ADD) {
+          bulk_s2g(SUM + row * cols, ob, row_bytes);
+          bulk_s2g(Y + row * cols, ob + row_bytes, row_bytes);
+        } else {
+          if (FWD) bulk_s2g(Y + row * cols, ob, row_bytes);
+          if (BWD) bulk_s2g(dX + row * cols, ob + (FWD ? row_bytes : 0u), row_bytes);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
   }
   (void)alive;
+  if (bulk_out && g.lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 
   if (BWD) {
     dependents_may_launch();      // the finalize kernel may be scheduled while the last CTAs fold their partials
@@ -279,14 +313,21 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
       const size_t stage = (size_t)cols * sizeof(T) * ((BWD || ADD) ? 2 : 1);
+      // measured at [16384, 3200] f16: the forward kernels (four row groups per SM) gain from bulk stores (add + norm
+      // 81 -> 75 us); the backward kernels hold two row groups per SM (registers), where the extra barrier per row
+      // costs more than the stores (fused forward + backward 90 -> 99-108 us), so they keep per-thread stores
+      const int want_bulk = g_rmsnorm_bulk_out && !BWD ? 1 : 0;
+      const size_t out_rows = (ADD || (FWD && BWD)) ? 2 : 1;
       auto smem_for = [&](int ns) {
         return pl.groups * ns * (stage + sizeof(uint64_t)) +
-               ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float);
+               ((size_t)2 * pl.groups * kMaxWarpsPerGroup * 2 + (BWD ? (size_t)cols : 0)) * sizeof(float) +
+               (want_bulk ? 16 + (size_t)pl.groups * 2 * out_rows * cols * sizeof(T) : 0);
       };
       // ring depth: fill about g_rmsnorm_smem_kb of shared memory per CTA, at most 8 rows per group
       int nstages = 8;
       while (nstages > 1 && smem_for(nstages) > (size_t)g_rmsnorm_smem_kb * 1024) --nstages;
       const size_t smem = smem_for(nstages);
+      const int bulk_out = want_bulk;
       int64_t grid = 0;
 #define CB_LAUNCH(NV_)                                                                                      \
   do {                                                                                                      \
@@ -295,7 +336,7 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
     if (grid > max_partials) grid = max_partials;                                                           \
     if (grid > want) grid = want;                                                                           \
     kern<<<(unsigned)grid, threads, smem, st>>>(Y, dX, wsf, X, Gm, dY, eps, rows, (int)cols, pl.G, nstages, beta_dx, \
-                                                Rp, Sp);                                                    \
+                                                Rp, Sp, bulk_out);                                          \
   } while (0)
       if (smem <= kMaxDynSmem) {
         switch (pl.NV) {

@@ -181,10 +181,6 @@ rope_vec_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ X, 
 // a pair is read and written by one thread only -- and the finished rows leave by bulk stores from the same
 // buffer.  The load/store units then carry only the table loads; global memory traffic is moved by the copy engine.
 // A slot is refilled one row late, once the bulk store that read it has finished reading.
-__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, unsigned bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-               ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
-}
 
 template <typename T, bool FWD, bool BWD>
 __global__ void __launch_bounds__(512)

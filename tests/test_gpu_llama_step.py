@@ -75,3 +75,31 @@ def test_fused_attention_step_matches_oracle_and_unfused(cuda, hd, heads, seq):
             for name, g in grads["layers"][li].items():
                 assert_close(host(g), ref_g["layers"][li][name], "float16", f"{mode} layer {li} {name}", rtol=2e-2, floor_frac=1.0)
     assert abs(out["fused"][0] - out["unfused"][0]) < 1e-3 * abs(out["unfused"][0])
+
+
+def test_graphed_step_replays_the_eager_step(cuda):
+    """The step captured in a CUDA graph and replayed twice gives the loss and gradients of the eager step, bit for
+    bit (same kernels, same order), also after the inputs in the captured buffers were replaced."""
+    cfg = LS.LlamaShape(layers=2, d_model=200, heads=2, head_dim=100, ffn=96, vocab=160, seq=128)
+    B = 2
+    P = LS.init_weights(cfg, cuda, seed=1, std=0.08)
+    toks = [R.uniform_int(3 + i, B * cfg.seq, cfg.vocab) for i in range(2)]
+    tgts = [R.uniform_int(13 + i, B * cfg.seq, cfg.vocab) for i in range(2)]
+    eager = []
+    for tok, tgt in zip(toks, tgts):
+        grads = LS.zeros_like_params(P)
+        loss = LS.TrainStep(cfg, P, B).forward_backward(dev(tok), dev(tgt), grads)
+        torch.cuda.synchronize()
+        eager.append((host(loss).copy(), [host(g).copy() for _, g in LS.flat_params(grads)]))
+    grads = LS.zeros_like_params(P)
+    step = LS.TrainStep(cfg, P, B)
+    tok_d, tgt_d = dev(toks[0]).clone(), dev(tgts[0]).clone()
+    gs = LS.GraphedStep(lambda: step.forward_backward(tok_d, tgt_d, grads))
+    for i in (0, 1, 0):
+        tok_d.copy_(dev(toks[i])); tgt_d.copy_(dev(tgts[i]))
+        loss = gs.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(host(loss), eager[i][0])
+        for (_, g), ref in zip(LS.flat_params(grads), eager[i][1]):
+            assert np.array_equal(host(g), ref)
+    assert host(step.status)[0] == 0
