@@ -7,9 +7,15 @@
 // x: dx = dy*cos + R(dy*sin), so the fused form streams x and dy in and y and dx out.
 //
 // head_dim 100 makes a head 200 bytes, so heads are not 16-byte aligned; token rows
-// (heads*head_dim elements) are.  Vectors are therefore taken over the flat token row; the
-// rotate-half partner of each 4-byte unit (a half2 / bf162 / float) sits +-head_dim/2 elements
-// away and is fetched with a 4-byte load that hits lines this CTA already streams.
+// (heads*head_dim elements) are.  Three kernels, chosen per call:
+//  * rope_staged_kernel (16-byte aligned rows, Apply mode): whole token rows travel by bulk copies
+//    into and out of shared memory, where (unit, partner) pairs are rotated in place;
+//  * rope_vec_kernel (16-byte aligned rows, Accumulate mode): 16-byte vectors over the flat token
+//    row; the rotate-half partner of each 4-byte unit (a half2 / bf162 / float) sits
+//    +-head_dim/2 elements away and is fetched with a 4-byte load that hits lines the CTA already
+//    streams;
+//  * rope_generic_kernel: element-wise, any shape and alignment.
+// All three give the same bits.
 //
 // f16 follows the reference's f16 arithmetic (both operands f16 => f16 ops, one rounding per
 // primitive, src/thunk/op.rs:2126-2133) using the non-contracting *_rn intrinsics; f32 uses
