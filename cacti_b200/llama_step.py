@@ -250,6 +250,9 @@ class GraphedStep:
                 body()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        # the capture allocates the step's activations again, in the graph's own pool: hand the warm-up's cached blocks
+        # back first, or both copies stay reserved (2 x 63 GiB at 8 sequences per GPU)
+        torch.cuda.empty_cache()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.result = body()
