@@ -28,6 +28,7 @@ SIGNATURES = {
     "cacti_b200_last_cuda_error": (_int, []),
     "cacti_b200_tune": (_int, [C.c_char_p, _int]),
     "cacti_b200_device_error": (_int, [C.POINTER(C.c_uint)]),
+    "cacti_b200_selftest_bounded_wait": (_int, [_p, _int, _st]),
     "cacti_b200_rmsnorm_workspace_bytes": (_sz, [_i64, _i64]),
     "cacti_b200_rmsnorm_fwd": (_int, [_p, _p, _p, _f32, _i64, _i64, _int, _st]),
     "cacti_b200_add_rmsnorm_fwd": (_int, [_p, _p, _p, _p, _p, _f32, _i64, _i64, _int, _st]),

@@ -218,10 +218,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     constexpr float kLog2e = 1.4426950408889634f;
     float m = -INFINITY;
     const bool neg = p.alpha < 0.f;
-    bool ok = true;   // a wait that ran out ends this thread's work, but it still meets the group barriers below
+    bool ok = true;   // a wait that ran out ends this warp's work (all 32 lanes together: the tcgen05.ld below are
+                      // warp-wide), but the warp still meets the group barriers below
     for (int j = grp; j < ntiles; j += 2) {         // pass 1: row maximum of the rounded, scaled, masked scores
       const int sb = j & 1;
-      if (!mbar_wait_bounded(s_full + sb, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(s_full + sb, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
       tc_fence_after();
       const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
 #pragma unroll 1
@@ -267,7 +268,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     unsigned char* myP = sP + (size_t)grp * kTileBytes;
     for (int j = grp; ok && j < ntiles; j += 2) {   // pass 2: exp, row sum, probabilities to shared memory
       const int n = ntiles + j, sb = n & 1;
-      if (!mbar_wait_bounded(s_full + sb, (unsigned)((n >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(s_full + sb, (unsigned)((n >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
       tc_fence_after();
       const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
       uint4 pk[16];                                 // this row's 128 probabilities, 8 per 16-byte chunk
@@ -305,7 +306,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       l += (lq[0] + lq[1]) + (lq[2] + lq[3]);
       // the P V two tiles back has read this group's probability buffer
-      if (!mbar_wait_bounded(p_empty + grp, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+      if (!mbar_wait_bounded_warp(p_empty + grp, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
 #pragma unroll
       for (int c = 0; c < 16; ++c)                  // chunk c: keys 8c .. 8c+7; key half c >> 3, chunk c & 7 of the 128-byte row
         *reinterpret_cast<uint4*>(myP + (size_t)(c >> 3) * 16384 + (size_t)r * 128 + (((c & 7) ^ (r & 7)) << 4)) = pk[c];
@@ -320,7 +321,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // [128][head_dim] staging area (the probability buffers are free once the last P V has completed); the warps then
     // write whole rows with consecutive lanes on consecutive 8-byte pieces (a thread = row store would touch 32
     // sectors per instruction).
-    const bool fin = ok && mbar_wait_bounded(o_full, 0, kDevErrAttnTimeout);
+    const bool fin = ok && mbar_wait_bounded_warp(o_full, 0, kDevErrAttnTimeout);
     unsigned char* rowbuf = sP;
     if (fin) {
       tc_fence_after();
@@ -543,7 +544,7 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     };
     for (int j = grp; j < ntiles; j += 2) {
       const int sl = j & 1;
-      if (!mbar_wait_bounded(t_full + sl, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) goto done;
+      if (!mbar_wait_bounded_warp(t_full + sl, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) goto done;
       tc_fence_after();
       const uint32_t ts = tmem_base + (uint32_t)sl * 256u + lane_off;
 #pragma unroll 1

@@ -155,6 +155,21 @@ __device__ __forceinline__ GroupCtx make_group(int G, float* red_smem) {
   return g;
 }
 
+// Group barrier that also ORs a per-thread flag over the group: every thread gets the same answer.  Used to turn a
+// per-thread event (a bounded wait that ran out) into a decision the whole group takes together, at a barrier the
+// group meets anyway: threads that left on their own would leave the others waiting at the next barrier for ever.
+__device__ __forceinline__ bool group_any(const GroupCtx& g, bool flag) {
+  if (g.G == 32) return __any_sync(0xffffffffu, flag);
+  unsigned r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"(g.gid + 1), "r"(g.G), "r"((unsigned)flag) : "memory");
+  return r != 0;
+}
+
 struct SumOp { static __device__ __forceinline__ float f(float a, float b) { return a + b; } static __device__ __forceinline__ float id() { return 0.f; } };
 struct MaxOp { static __device__ __forceinline__ float f(float a, float b) { return fmaxf(a, b); } static __device__ __forceinline__ float id() { return -INFINITY; } };
 
@@ -167,15 +182,20 @@ template <typename Op> __device__ __forceinline__ float warp_reduce(float v) {
 // Reduce two values at once (a and b use the same Op).  Stage 1: shuffles inside each warp; lane 0
 // of every warp publishes its pair; stage 2 after the group barrier: lane l of every warp picks up
 // warp l's pair and the warp reduces again with shuffles (a group has at most 32 warps).
-template <typename Op> __device__ __forceinline__ void group_reduce2(GroupCtx& g, float& a, float& b) {
+// `any` (optional): in: this thread's flag; out: the OR over the group, taken at the reduction's own barrier.
+template <typename Op> __device__ __forceinline__ void group_reduce2(GroupCtx& g, float& a, float& b, bool* any = nullptr) {
   a = warp_reduce<Op>(a);
   b = warp_reduce<Op>(b);
-  if (g.G == 32) return;
+  if (g.G == 32) {
+    if (any) *any = __any_sync(0xffffffffu, *any);
+    return;
+  }
   const int groups = blockDim.x / g.G;
   float2* slot = reinterpret_cast<float2*>(g.red) + (size_t)(g.phase * groups + g.gid) * kMaxWarpsPerGroup;
   const int w = g.lane >> 5, l = g.lane & 31;
   if (l == 0) slot[w] = make_float2(a, b);
-  group_barrier(g);
+  if (any) *any = group_any(g, *any);
+  else group_barrier(g);
   float2 v = l < g.nwarps ? slot[l] : make_float2(Op::id(), Op::id());
   a = warp_reduce<Op>(v.x);
   b = warp_reduce<Op>(v.y);
@@ -223,13 +243,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(g_mbar_suspend_ns) : "memory");
   return ok != 0;
 }
-// Returns false after 2^20 failed polls: at most about 4 s (every poll parked for the full hint), at least a few
-// tens of milliseconds (polls that return at once), far beyond any wait of a healthy kernel.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned err_code) {
-  for (unsigned it = 0; it < (1u << 20); ++it)
+// Returns false after `polls` failed polls (default 2^20: at most about 4 s, every poll parked for the full hint; at
+// least a few tens of milliseconds, polls that return at once; far beyond any wait of a healthy kernel).  The answer
+// is per thread: a caller that shares barriers or warp-wide instructions with other threads must agree on it with
+// them (group_any, __all_sync) before acting on it.
+constexpr unsigned kMbarPolls = 1u << 20;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned err_code, unsigned polls = kMbarPolls) {
+  for (unsigned it = 0; it < polls; ++it)
     if (mbar_try_wait(bar, parity)) return true;
   atomicMax(&g_dev_error, err_code);
   return false;
+}
+// The same for a converged warp: true only if every lane saw the phase complete.
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, unsigned parity, unsigned err_code) {
+  return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, err_code));
 }
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -244,10 +271,12 @@ __device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, u
 }
 
 // ---- block reduction for the element-wise fallback kernels (whole CTA = one row) -----------
-template <typename Op> __device__ __forceinline__ float block_reduce(float v, float* smem /* >= 33 floats */) {
+// `any` (optional): in: this thread's flag; out: the OR over the CTA, taken at the reduction's first barrier.
+template <typename Op> __device__ __forceinline__ float block_reduce(float v, float* smem /* >= 33 floats */, bool* any = nullptr) {
   v = warp_reduce<Op>(v);
   const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();                       // protect smem from the previous use
+  if (any) *any = __syncthreads_or(*any) != 0;
+  else __syncthreads();                  // protect smem from the previous use
   if ((threadIdx.x & 31) == 0) smem[w] = v;
   __syncthreads();
   float r = Op::id();

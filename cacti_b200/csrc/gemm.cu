@@ -28,6 +28,7 @@
 // dimension zero-padded to a multiple of 64 elements; the reference pads the same operands to 16 bytes
 // with a separate thunk before calling cuBLAS (src/op.rs:1454-1482).  Outputs need no alignment.
 #include "tc_common.cuh"
+#include <atomic>
 #include <type_traits>
 
 namespace cb {
@@ -47,6 +48,92 @@ struct GemmParams {
   int c_tma;                              // 1: C is written with TMA stores from a swizzled staging buffer
   int group_m;                            // tile rasterisation: m-tiles per group (L2 reuse of the B panel)
   int tri, diag;                          // triangular-structure hint (CACTI_B200_TRI_*) and its diagonal offset
+  // k-split schedule of the two-SM kernel (see WorkIter); sk_tiles == 0: every tile is computed whole
+  long long sk_tiles, sk_units;           // tiles [0, sk_tiles) are shared out in k-blocks: sk_units = sk_tiles * k-blocks
+  float* sk_part;                         // [workers][2 CTAs][256 columns][128 rows] f32 partial accumulators
+  int sk_slot;                            // which row of g_sk_flags this launch signals through
+};
+
+// ---- k-split ("stream-K") schedule ------------------------------------------------------------------------------
+// A persistent grid of W workers over T tiles runs ceil(T / W) waves; when T is not a multiple of W the last wave is
+// partly idle (104 tiles on 74 SM pairs: 2 waves for 1.4 waves of work).  Here the first sk_tiles tiles are treated
+// as one run of sk_tiles * nkb k-blocks that is cut into W equal consecutive ranges; worker w computes range w and
+// then whole tiles sk_tiles + w, sk_tiles + w + W, ...  A range starts inside at most one tile.  That first piece is
+// a *contribution*: its f32 accumulator goes to the worker's slot of `sk_part` and a flag is raised.  The worker
+// whose range holds a tile's first k-block *owns* the tile: it computes its piece last, then adds the
+// contributions in increasing k order and runs the normal epilogue.  Every output element is therefore summed in
+// an order fixed by (shape, W): results do not change from run to run.  Contributions are the first thing a worker
+// computes and owned pieces the last thing of its range, so an owner finds them ready unless the contributing CTA
+// has not been scheduled yet; the wait for it is bounded (kDevErrGemmSplitTimeout).  Waits only ever point from
+// worker w to workers > w, so no cycle exists.
+enum { kItemFull = 0, kItemContrib = 1, kItemOwner = 2 };
+constexpr unsigned kDevErrGemmSplitTimeout = 4u;
+constexpr int kSkSlots = 128;                       // launches in flight at once share flags only 128 launches apart
+constexpr int kSkMaxWorkers = kNumSMs / 2;
+constexpr size_t kSkPartFloats = 256 * 128;         // per (worker, CTA of the pair)
+__device__ unsigned g_sk_flags[kSkSlots][kSkMaxWorkers][2][4];    // zero at load; every flag is cleared by its reader
+
+struct WorkItem { long long tile; int kb0, kb1, kind; };
+struct WorkIter {
+  long long pos, end, dp_next, dp_step, total;
+  int nkb;
+  __device__ __forceinline__ static long long range_begin(const GemmParams& p, long long w, long long nworkers) {
+    return p.sk_units * w / nworkers;
+  }
+  __device__ __forceinline__ void init(const GemmParams& p, long long w, long long nworkers, long long total_tiles, int nkb_) {
+    nkb = nkb_; total = total_tiles; dp_step = nworkers;
+    pos = range_begin(p, w, nworkers); end = range_begin(p, w + 1, nworkers);
+    dp_next = p.sk_tiles + w;
+  }
+  __device__ __forceinline__ bool next(WorkItem& it) {
+    if (pos < end) {
+      const long long t = pos / nkb, tile_end = (t + 1) * nkb;
+      const long long e = end < tile_end ? end : tile_end;
+      it.tile = t; it.kb0 = (int)(pos - t * nkb); it.kb1 = (int)(e - t * nkb);
+      it.kind = it.kb0 ? kItemContrib : (it.kb1 == nkb ? kItemFull : kItemOwner);
+      pos = e;
+      return true;
+    }
+    if (dp_next < total) {
+      it.tile = dp_next; it.kb0 = 0; it.kb1 = nkb; it.kind = kItemFull;
+      dp_next += dp_step;
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Lane 0 polls the flag (acquire) for at most about a second; the whole warp gets the same answer.
+__device__ __forceinline__ bool sk_wait_flag(const unsigned* flag, int lane) {
+  unsigned ok = 1;
+  if (lane == 0) {
+    ok = 0;
+    const unsigned long long t0 = global_timer_ns();
+    for (unsigned it = 1;; ++it) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v) { ok = 1; break; }
+      __nanosleep(100);
+      if ((it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) break;
+    }
+    if (!ok) atomicMax(&g_dev_error, kDevErrGemmSplitTimeout);
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// What the epilogue does with one accumulator (two-SM kernel).
+struct SkEpi {
+  int kind;                 // kItemFull: normal epilogue; kItemContrib: store the accumulator; kItemOwner: add, then normal
+  float* my_part;           // contribution: this CTA's slot
+  unsigned* my_flags;       // contribution: this CTA's four flags (one per epilogue warp)
+  const float* part0;       // owner: slot of the first contributor (the next worker), same CTA rank; next worker 2 slots on
+  unsigned* flags0;         // owner: flags of the first contributor; next worker 8 words on
+  int ncontrib;
 };
 
 // Tile order inside one block: groups of `group_m` m-tiles; inside a group the m index runs fastest, so
@@ -99,7 +186,35 @@ __device__ __forceinline__ void k_block_range(const GemmParams& p, int row0, int
 template <typename T, int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap& tmC, T* __restrict__ C,
                                               uint32_t tmem_base, int acc, int row0, int tn, int bj, int bi, int q, int lane,
-                                              unsigned char* mybuf, uint32_t tempty_addr) {
+                                              unsigned char* mybuf, uint32_t tempty_addr, const SkEpi sk = SkEpi{}) {
+  const int prow = q * 32 + lane;             // this thread's row inside its CTA's 128 rows (partial-slot index)
+  if (sk.kind == kItemContrib) {
+    // this CTA's piece of a tile another worker owns: accumulator -> f32 slot (column-major, so a warp's stores of
+    // one column are 128 contiguous bytes), then the flag
+#pragma unroll 1
+    for (int c = 0; c < BN / 64; ++c) {
+      if (tn * BN + c * 64 >= p.N) break;
+      uint32_t v[2][32];
+      tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64), v[0]);
+      tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64 + 32), v[1]);
+      tc_ld_wait();
+      float* dst = sk.my_part + (size_t)(c * 64) * kBM + prow;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) __stcg(dst + (size_t)i * kBM, __uint_as_float(v[i >> 5][i & 31]));
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(tempty_addr);
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk.my_flags + q), "r"(1u) : "memory");
+    return;
+  }
+  if (sk.kind == kItemOwner) {
+    // the contributions were computed first by their workers; a wait that runs out is recorded and the tile is
+    // finished with what is there (the device error word tells the caller the result is void)
+    for (int ci = 0; ci < sk.ncontrib; ++ci) sk_wait_flag(sk.flags0 + ci * 8 + q, lane);
+  }
   if (p.c_tma) {
     // TMEM -> registers -> swizzled shared staging -> TMA store (clips rows/columns past M, N)
     // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
@@ -124,6 +239,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         if (lane == 0) mbar_arrive_cluster(tempty_addr);
       } else {
         __syncwarp();
+      }
+      if (sk.kind == kItemOwner) {                       // + the other workers' pieces, in increasing k
+        for (int ci = 0; ci < sk.ncontrib; ++ci) {
+          const float* src = sk.part0 + (size_t)ci * 2 * kSkPartFloats + (size_t)(c * 128) * kBM + prow;
+#pragma unroll
+          for (int hh = 0; hh < 4; ++hh) {
+            if (hh * 32 < ncols && col0 + hh * 32 < p.N) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                v[hh][i] = __float_as_uint(__uint_as_float(v[hh][i]) + __ldcg(src + (size_t)(hh * 32 + i) * kBM));
+            }
+          }
+        }
       }
 #pragma unroll
       for (int hb = 0; hb < 2; ++hb) {
@@ -152,6 +280,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
+    if (sk.kind == kItemOwner && lane == 0)
+      for (int ci = 0; ci < sk.ncontrib; ++ci) sk.flags0[ci * 8 + q] = 0;       // ready for the next launch
     return;                                   // the accumulator was released inside the loop
   }
   const int row = row0 + lane;
@@ -163,6 +293,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     uint32_t v[32];
     tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
     tc_ld_wait();
+    if (sk.kind == kItemOwner) {
+      for (int ci = 0; ci < sk.ncontrib; ++ci) {
+        const float* src = sk.part0 + (size_t)ci * 2 * kSkPartFloats + (size_t)(c * 32) * kBM + prow;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(src + (size_t)i * kBM));
+      }
+    }
     if (row < p.M) {
       float f[32];
 #pragma unroll
@@ -208,6 +345,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive_cluster(tempty_addr);
+  if (sk.kind == kItemOwner && lane == 0)
+    for (int ci = 0; ci < sk.ncontrib; ++ci) sk.flags0[ci * 8 + q] = 0;
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN>
@@ -321,7 +460,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
-      if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
+      // all 32 lanes leave together: a wait that ran out on some lanes only must not split the warp before the
+      // warp-wide tcgen05.ld of the epilogue
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) goto done;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kBM + q * 32, tn, bj, bi, q, lane,
                            cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
@@ -431,9 +572,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- TMA producer (both CTAs) ----------------
     int s = 0; unsigned ph = 0;
     const int row_off = (int)rank * kBM;
-    for (long long tile = pair; tile < total; tile += npairs) {
+    WorkIter it; WorkItem wi;
+    it.init(p, pair, npairs, total, nkb);
+    while (it.next(wi)) {
       int blk, tm, tn;
-      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
       // a last column tile with at most 128 columns runs as an N = 128 MMA: each CTA then supplies 64 rows of B
@@ -441,8 +584,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int hb = (p.N - tn * BN <= HB) ? HB / 2 : HB;
       const int m0 = tm * kPairBM + row_off, n0 = tn * BN + (int)rank * hb;
       if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
-      int kb0, kb1;
-      k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
+      int kb0 = wi.kb0, kb1 = wi.kb1;
+      if (p.tri) k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
         unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
@@ -471,10 +614,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- MMA issuer (leader CTA) ----------------
     int s = 0; unsigned ph = 0;
     long long local = 0;
-    for (long long tile = pair; tile < total; tile += npairs) {
-      int kb0 = 0, kb1 = nkb;
+    WorkIter it; WorkItem wi;
+    it.init(p, pair, npairs, total, nkb);
+    while (it.next(wi)) {
+      int kb0 = wi.kb0, kb1 = wi.kb1;
       int blk, tm, tn;
-      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
       if (p.tri) {
         if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
         k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
@@ -504,16 +649,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
     const int q = warp & 3;
     long long local = 0;
-    for (long long tile = pair; tile < total; tile += npairs) {
+    WorkIter it; WorkItem wi;
+    it.init(p, pair, npairs, total, nkb);
+    while (it.next(wi)) {
       int blk, tm, tn;
-      decode_tile(tile, tiles_per_block, p, blk, tm, tn);
+      decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
       if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
-      if (!mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout)) goto done;
+      SkEpi sk{};
+      sk.kind = wi.kind;
+      if (wi.kind == kItemContrib) {
+        sk.my_part = p.sk_part + ((size_t)pair * 2 + rank) * kSkPartFloats;
+        sk.my_flags = &g_sk_flags[p.sk_slot][pair][rank][0];
+      } else if (wi.kind == kItemOwner) {
+        // the rest of this tile lies in the ranges of the next workers
+        const long long tile_end = (wi.tile + 1) * nkb;
+        int n = 0;
+        for (long long w2 = pair + 1; w2 < npairs && WorkIter::range_begin(p, w2, npairs) < tile_end; ++w2) ++n;
+        sk.ncontrib = n;
+        sk.part0 = p.sk_part + ((size_t)(pair + 1) * 2 + rank) * kSkPartFloats;
+        sk.flags0 = &g_sk_flags[p.sk_slot][pair + 1][rank][0];
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) goto done;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kPairBM + (int)rank * kBM + q * 32, tn, bj, bi, q, lane,
-                           cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0));
+                           cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0), sk);
       ++local;
     }
   }
@@ -595,6 +756,43 @@ int g_gemm_bn = 0;   // 0: choose by N; 128 or 256 forces the tile width (measur
 int g_gemm_group_m = 0;
 int g_gemm_sms = 0;   // 0: all 148
 int g_gemm_pair = 1;  // 1: 256-wide tiles may run as two-SM (cta_group::2) 256 x 256 tiles; 0: one-SM tiles only
+// 1: the two-SM kernel may share tiles out in k-blocks when a workspace is given (see WorkIter).  Off unless asked
+// for: timed alone at one sequence per GPU (M = 2048) the schedule brought the forward and input-gradient matmuls to
+// the per-flop rate they have at M = 16384 (2048 x 3200 x 8640: 124 -> 107 us), but a whole training step ran 5 %
+// slower with it (50.8 -> 53.6 ms at M = 2048): these matmuls are power-limited, the SMs a partly filled last wave
+// leaves idle let the others clock higher, and the partial sums displace 19 MB of the L2 per matmul.
+int g_gemm_split = 0;
+
+// Workers and k-split tiles for `tiles` two-SM tiles of `nkb` k-blocks on at most `max_workers` SM pairs.  Splitting
+// pays when the last wave of whole tiles would leave more than about 5 % of the grid idle.
+struct SplitPlan { long long workers, sk_tiles; };
+// `tiles_n`, `group_m`, `N`, `K`: to bound the operand bytes the split tiles touch.  Whole tiles that run at the same
+// time walk k together, so each operand panel is fetched from HBM once and shared through L2; workers of the k-split
+// region sit at different k, and the region's operands must stay in L2 (126 MB) as a whole or every panel is fetched
+// again per tile (measured: the 2048 x 3200 x 32000 input-gradient matmul of the output head, 336 MB of operands,
+// ran 14 % slower split than whole; the 90 MB of the 8640-deep projections 8 to 15 % faster).
+static SplitPlan plan_split(long long tiles, int nkb, long long max_workers, long long tiles_n, long long group_m, long long M,
+                            long long N, long long K) {
+  SplitPlan s{tiles < max_workers ? tiles : max_workers, 0};
+  if (max_workers < 2 || tiles * 2 < max_workers) return s;          // a handful of tiles: not worth the partial traffic
+  const long long rem = tiles % max_workers;
+  if (rem == 0) return s;
+  const long long waves = (tiles + max_workers - 1) / max_workers;
+  if ((double)(max_workers - rem) / (double)(waves * max_workers) <= 0.05) return s;
+  const long long sk_tiles = tiles < max_workers ? tiles : max_workers + rem;
+  if (sk_tiles * nkb / max_workers < 4) return s;                    // pieces shorter than the operand ring
+  const long long per_group = (group_m > 0 ? group_m : 1) * tiles_n;
+  long long rows = (sk_tiles + per_group - 1) / per_group * group_m * 256;
+  if (rows > M) rows = M;
+  if ((rows + N) * K * 2 > 100ll * 1024 * 1024) return s;
+  s.workers = max_workers; s.sk_tiles = sk_tiles;
+  return s;
+}
+static long long pair_group_m(long long tiles_m) {
+  const long long g = g_gemm_group_m > 0 ? g_gemm_group_m : 8;
+  return g > tiles_m ? tiles_m : g;
+}
+static size_t split_bytes() { return (size_t)kSkMaxWorkers * 2 * kSkPartFloats * sizeof(float); }
 
 template <typename T>
 static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long long M, long long N, long long K,
@@ -646,6 +844,14 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   // 3200 x 3200 x 16384 weight-gradient matmul: 1041 TFLOP/s in 3 waves of 256 x 256 against 963 in 3 waves of 128 x 192).
   int BN = g_gemm_bn;
   bool pair = false;
+  const int sms = g_gemm_sms > 0 && g_gemm_sms < kNumSMs ? g_gemm_sms : kNumSMs;
+  const long long pair_workers = sms / 2;
+  const int nkb_host = (int)((K + kBK - 1) / kBK);
+  // the k-split schedule needs room for the partial accumulators behind whatever was repacked; dense matmuls only
+  // (block matmuls bring hundreds of tiles, and their hinted forms promise bits equal to the unhinted ones)
+  const size_t split_off = (ws_off + 255) / 256 * 256;
+  const bool split_ok = g_gemm_split && tri == 0 && nbi == 1 && nbo == 1 && ws && !(ws & 255) &&
+                        split_off + split_bytes() <= ws_bytes;
   if (!BN) {
     if (N <= 128) BN = 128;
     else {
@@ -659,7 +865,11 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
       }
       if (g_gemm_pair && M > kBM) {
         const long long tiles2 = ((M + kPairBM - 1) / kPairBM) * ((N + kPairBN - 1) / kPairBN) * nbi * nbo;
-        const double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * 0.93;
+        double cost = (double)((tiles2 + kNumSMs / 2 - 1) / (kNumSMs / 2)) * kPairBN * 0.93;
+        // with the k-split schedule the two-SM grid has no idle last wave (3 % for the partial sums)
+        const long long tm2 = (M + kPairBM - 1) / kPairBM, tn2 = (N + kPairBN - 1) / kPairBN;
+        if (split_ok && plan_split(tiles2, nkb_host, pair_workers, tn2, pair_group_m(tm2), M, N, K).sk_tiles)
+          cost = (double)tiles2 / (double)pair_workers * kPairBN * 0.93 * 1.03;
         if (cost < best) { best = cost; BN = kPairBN; pair = true; }
       }
     }
@@ -697,18 +907,28 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     }
   }
   // about 16 m-tiles of A (2048 rows) stay hot in L2 while the B panels stream
-  p.group_m = g_gemm_group_m > 0 ? g_gemm_group_m : (pair ? 8 : 16);
+  p.group_m = pair ? (int)pair_group_m(p.tiles_m) : (g_gemm_group_m > 0 ? g_gemm_group_m : 16);
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   const long long total = (long long)p.tiles_m * p.tiles_n * nbi * nbo;
   // g_gemm_sms < 148 leaves SMs free for a concurrent kernel (the gradient all-reduce): a persistent grid that
   // cannot be fully resident would otherwise run its last CTAs as a second wave
-  const int sms = g_gemm_sms > 0 && g_gemm_sms < kNumSMs ? g_gemm_sms : kNumSMs;
   const int grid = (int)(total < sms ? total : sms);
+  p.sk_tiles = 0; p.sk_units = 0; p.sk_part = nullptr; p.sk_slot = 0;
   const int stages = BN >= 192 ? 4 : 6;
   const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
   if (pair) {
-    const long long pairs = total < sms / 2 ? total : sms / 2;
+    long long pairs = total < sms / 2 ? total : sms / 2;
+    if (split_ok) {
+      const SplitPlan sp = plan_split(total, nkb_host, pair_workers, p.tiles_n, p.group_m, M, N, K);
+      if (sp.sk_tiles) {
+        static std::atomic<unsigned> seq{0};
+        pairs = sp.workers;
+        p.sk_tiles = sp.sk_tiles; p.sk_units = sp.sk_tiles * nkb_host;
+        p.sk_part = reinterpret_cast<float*>(ws + split_off);
+        p.sk_slot = (int)(seq.fetch_add(1) % kSkSlots);
+      }
+    }
 #define CB_GEMM2(AM_, BM_)                                                                             \
   do {                                                                                                 \
     auto kern = gemm_tc_pair_kernel<T, AM_, BM_>;                                                      \
@@ -782,7 +1002,7 @@ size_t cacti_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t 
     const size_t x = cb::packed_bytes(r, c, nb), y = cb::packed_bytes(c, r, nb);
     return x > y ? x : y;
   };
-  return worst(m, k) + worst(k, n) + 512;
+  return worst(m, k) + worst(k, n) + 512 + cb::split_bytes() + 256;
 }
 
 int cacti_b200_gemm(cacti_b200_dptr c, cacti_b200_dptr a, cacti_b200_dptr b, int64_t m, int64_t n, int64_t k, int64_t lda,

@@ -85,7 +85,8 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
       (reinterpret_cast<uintptr_t>(colacc + (BWD ? cols : 0)) + 15) & ~(uintptr_t)15) + (size_t)g.gid * 2 * out_bytes;
   unsigned it = 0;
   for (int64_t row = row0; row < rows; row += stride) {
-    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) { alive = false; break; }
+    // a wait that ran out is agreed on by the whole group at the reduction's barrier below: no lane leaves alone
+    bool gave_up = !mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout);
     const unsigned char* stage = stage0 + (size_t)slot * stage_bytes;
     unsigned char* ob = outbuf0 + (size_t)(it & 1) * out_bytes;
     ++it;
@@ -132,7 +133,8 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
     }
     float ss = __fadd_rn(__fadd_rn(sq[0], sq[1]), __fadd_rn(sq[2], sq[3]));
     float c1 = __fadd_rn(__fadd_rn(cq[0], cq[1]), __fadd_rn(cq[2], cq[3]));
-    group_reduce2<SumOp>(g, ss, c1);        // its barrier also orders every lane's reads of the stage slot
+    group_reduce2<SumOp>(g, ss, c1, &gave_up);   // its barrier also orders every lane's reads of the stage slot
+    if (gave_up) { alive = false; break; }
     if (G == 32) __syncwarp();
     if (row + (int64_t)nstages * stride < rows) issue(row + (int64_t)nstages * stride, cur_slot);
     const float s = __fsqrt_rn(__fmaf_rn(ss, inv_cols, eps));

@@ -226,7 +226,7 @@ rope_staged_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ 
   int prev_slot = -1;
   int64_t prev_row = 0;
   for (int64_t row = row0; row < tokens; row += stride) {
-    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) break;
+    const bool gave_up = !mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout);
     T* sx = reinterpret_cast<T*>(stage0 + (size_t)slot * stage_bytes);
     T* sg = reinterpret_cast<T*>(stage0 + (size_t)slot * stage_bytes + (FWD ? row_bytes : 0));
     const T* ct = cosT + pos * hd;
@@ -253,8 +253,11 @@ rope_staged_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ 
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the bulk store reads what was just written
-    if (G == 32) __syncwarp();
-    else asm volatile("bar.sync %0, %1;" ::"r"(gid + 1), "r"(G) : "memory");
+    // the group's barrier also carries the vote on a wait that ran out: the group stops together, nothing is stored
+    {
+      GroupCtx gc; gc.G = G; gc.gid = gid;
+      if (group_any(gc, gave_up)) break;
+    }
     if (lane == 0) {
       if (FWD) bulk_s2g(Y + row * row_len, sx, row_bytes);
       if (BWD) bulk_s2g(dX + row * row_len, sg, row_bytes);

@@ -90,8 +90,9 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
   int active = row < rows ? issue(row) : 0;
   for (; row < rows; row += stride) {
     uint4 sraw[NV], graw[NV];
+    bool gave_up = false;
     if (active > 0) {
-      if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) return;
+      gave_up = !mbar_wait_bounded(bar, phase, kDevErrStageTimeout);
       phase ^= 1;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
@@ -103,7 +104,9 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
         }
       }
     }
-    group_barrier(g);                       // the stage buffer has been consumed by every lane
+    // the stage buffer has been consumed by every lane; a wait that ran out on any lane ends the group's work
+    // here, all lanes together
+    if (group_any(g, gave_up)) return;
     const int cur_active = active;
     active = (row + stride < rows) ? issue(row + stride) : 0;
 

@@ -83,7 +83,9 @@ softmax_nll_rows_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const
       if (w_rows) w_next = w_rows[row + stride];
     }
     const bool tgt_ok = tgt >= 0 && tgt < cols;
-    if (!mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout)) return;
+    // a wait that ran out: a one-warp group agrees at once, a larger one at the group barrier below
+    bool gave_up = !mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout);
+    if (G == 32 && __any_sync(0xffffffffu, gave_up)) return;
     const unsigned char* stage = stage0 + (size_t)slot * row_bytes;
     // the row as f32 in registers; it is overwritten by exp(a - m) in pass 2 and scaled in pass 3
     float a[NV][VEC];
@@ -128,7 +130,7 @@ softmax_nll_rows_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const
       float2* sl = reinterpret_cast<float2*>(g.red) + (size_t)(g.phase * groups_ + g.gid) * kMaxWarpsPerGroup;
       const int wi = g.lane >> 5, l = g.lane & 31;
       if (l == 0) sl[wi] = make_float2(mw, zw);
-      group_barrier(g);                                  // also: every lane has consumed the stage slot
+      if (group_any(g, gave_up)) return;                 // also: every lane has consumed the stage slot
       const float2 v = l < g.nwarps ? sl[l] : make_float2(-INFINITY, 0.f);
       m = warp_reduce<MaxOp>(v.x);
       const float term = v.y * exp_rescale<T>(v.x == -INFINITY ? -INFINITY : v.x - m);
@@ -201,7 +203,7 @@ softmax_nll_smem_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const
     const int64_t nrow = row + gridDim.x;
     if (nrow < rows) { tgt_next = load_index<TI>(targets, nrow); if (w_rows) w_next = w_rows[nrow]; }
     const bool tgt_ok = tgt >= 0 && tgt < cols;
-    if (!mbar_wait_bounded(bar, phase, kDevErrStageTimeout)) return;
+    bool gave_up = !mbar_wait_bounded(bar, phase, kDevErrStageTimeout);   // agreed on by the CTA at the first reduction
     phase ^= 1;
     const uint4* srow = reinterpret_cast<const uint4*>(smem_raw);
     // sweep 1: maximum
@@ -212,7 +214,8 @@ softmax_nll_smem_kernel(float* __restrict__ loss_rows, T* __restrict__ dL, const
 #pragma unroll
       for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[e]);
     }
-    const float m = block_reduce<MaxOp>(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])), red);
+    const float m = block_reduce<MaxOp>(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])), red, &gave_up);
+    if (gave_up) return;
     const float nml = -m * 1.4426950408889634f;
     // sweep 2: Z
     float zq[4] = {0.f, 0.f, 0.f, 0.f};

@@ -103,6 +103,8 @@ class TrainStep:
         nb = max(L.cacti_b200_gemm_workspace_bytes(S, S, hd, batch, H), L.cacti_b200_gemm_workspace_bytes(S, hd, S, batch, H),
                  L.cacti_b200_gemm_workspace_bytes(hd, S, S, batch, H))
         self.gemm_ws = torch.empty(nb, dtype=torch.uint8, device=dev)
+        # dense matmuls: partial sums of the k-split schedule (all operands here are TMA-addressable, nothing is repacked)
+        self.mm_ws = ops.gemm_workspace(0, 0, 0, dev)
         self.norm_ws = ops.rmsnorm_workspace(self.T, cfg.d_model, dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.launches = 0
@@ -110,7 +112,7 @@ class TrainStep:
     # -- small helpers (each is exactly one or two C-ABI calls) -----------------------------------------
     def _mm(self, a, b, ta, tb, c=None, beta=0.0):
         self.launches += 1
-        return ops.gemm(a, b, ta, tb, beta=beta, c=c)
+        return ops.gemm(a, b, ta, tb, beta=beta, c=c, workspace=self.mm_ws)
 
     def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0, b_valid=None):
         self.launches += 3 if b_valid is None else 1       # unaligned operands are repacked first; padded ones are not

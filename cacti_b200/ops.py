@@ -256,7 +256,13 @@ def _scalars(alpha, beta):
     return _C.byref(_C.c_float(alpha)), _C.byref(_C.c_float(beta))
 
 
-def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
+def gemm_workspace(m, n, k, device) -> torch.Tensor:
+    """Workspace of a dense matmul: room to repack operands TMA cannot address, and for the partial sums of the
+    k-split schedule (a matmul given no workspace computes every tile whole)."""
+    return _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, 1, 1), device)
+
+
+def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None, workspace=None):
     """C = alpha * op(A) op(B) + beta * C on 2-d row-major tensors (any row stride, unit column stride)."""
     m = a.shape[1] if trans_a else a.shape[0]
     k = a.shape[0] if trans_a else a.shape[1]
@@ -264,7 +270,9 @@ def gemm(a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, c=None):
     c = torch.empty(m, n, dtype=a.dtype, device=a.device) if c is None else c
     # a repack workspace is only needed when TMA cannot address an operand (16-byte base and row pitch)
     aligned = all(t.data_ptr() % 16 == 0 and (t.stride(0) * t.element_size()) % 16 == 0 for t in (a, b))
-    ws = None if aligned else _ws(lib().cacti_b200_gemm_workspace_bytes(m, n, k, 1, 1), a.device)
+    ws = workspace
+    if ws is None and not aligned:
+        ws = gemm_workspace(m, n, k, a.device)
     al, be = _scalars(alpha, beta)
     check(lib().cacti_b200_gemm(_ptr(c), _ptr(a), _ptr(b), m, n, k, a.stride(0), b.stride(0), c.stride(0), int(trans_a),
                                 int(trans_b), al, be, _dt(a), _ptr(ws), ws.numel() if ws is not None else 0, _stream()),

@@ -76,8 +76,17 @@ int         cacti_b200_version(void);               /* 10000*major + 100*minor +
 const char* cacti_b200_error_string(int code);
 int         cacti_b200_last_cuda_error(void);       /* cudaError_t of the last failed launch on this thread */
 /* Device-side sticky error word (no counterpart in the reference): every wait inside a kernel is bounded; a
- * wait that runs out records a code here instead of hanging.  0 = none.  Reading clears it and synchronises. */
+ * wait that runs out records a code here instead of hanging.  0 = none; 1 a staged row copy, 2 a matmul pipeline,
+ * 3 an attention pipeline, 4 a partial sum of the k-split matmul schedule, 5 the self-test below.  The call
+ * synchronises the whole device (cudaDeviceSynchronize), then reads and clears the word; call it from the device's
+ * one control thread with nothing else being launched. */
 int         cacti_b200_device_error(unsigned* out);
+/* Diagnostic, no counterpart in the reference: launches one small CTA whose threads wait, with a limit of `polls`
+ * polls (1..4096), on a barrier that nothing arms, and then leave the way every kernel of this library leaves when a
+ * wait runs out: together, with their tensor memory released.  result: u32[3] in device memory, written as
+ * {1 = the kernel reached its end, 1 = row group 0 left as one, 1 = row group 1 left as one}.  Afterwards
+ * cacti_b200_device_error reports code 5.  Nothing faults and nothing waits without a limit. */
+int         cacti_b200_selftest_bounded_wait(cacti_b200_dptr result, int polls, cacti_b200_stream stream);
 /* Launch-shape knobs ("softmax_threads", "rmsnorm_gpref", ...) for measurement sweeps.  No counterpart
  * in the reference; results do not depend on them. */
 int         cacti_b200_tune(const char* name, int value);

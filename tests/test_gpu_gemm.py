@@ -122,6 +122,74 @@ def test_gemm_pair_tiles_match_single_sm(cuda):
         assert torch.equal(o, t)
 
 
+@pytest.fixture
+def k_split():
+    """Turn the k-split schedule of the two-SM kernel on for one test (it is off by default)."""
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"gemm_split", 1) == capi.OK
+    yield
+    L.cacti_b200_tune(b"gemm_split", 0)
+
+
+# tiles = ceil(m / 256) * ceil(n / 256) against 74 SM pairs: 60 (every tile split between workers), 104 (one to two
+# tiles per worker: the projection shape at one sequence per GPU), 160 (two waves and a remainder: k-split region plus
+# whole tiles), 52 with a ragged last row and column tile, and a short contraction (8 k-blocks)
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(1536, 2560, 512), (2048, 3200, 3200), (4096, 2560, 640), (3200, 860, 2048), (2048, 3200, 8640)])
+def test_gemm_k_split_schedule(cuda, ta, tb, m, n, k):
+    """With a workspace, and the schedule switched on, the two-SM kernel shares the tiles of a partly filled last wave
+    out in k-blocks: pieces of a tile computed by different CTA pairs are summed in f32 in k order by the pair that
+    owns the tile.  Held to the fp64 oracle like every other matmul; equal from run to run; and within f32 summation
+    noise of the whole-tile schedule (both round the same f32 sum up to its association)."""
+    L = capi.lib()
+    a, b = dev(_stored(51, m, k, ta)), dev(_stored(52, k, n, tb, 0.1))
+    ws = ops.gemm_workspace(m, n, k, a.device)
+    plain = ops.gemm(a, b, ta, tb, alpha=0.5, workspace=ws)         # off by default: every tile computed whole,
+    if m % 8 == 0 and n % 8 == 0 and k % 8 == 0:                    # workspace or not
+        assert torch.equal(plain, ops.gemm(a, b, ta, tb, alpha=0.5))
+    old = dev(R.normal(53, (m, n), np.float16))
+    cacc = old.clone()
+    wide = torch.zeros(m, n + 3, dtype=torch.float16, device=a.device)
+    assert L.cacti_b200_tune(b"gemm_split", 1) == capi.OK
+    try:
+        c1 = ops.gemm(a, b, ta, tb, alpha=0.5, workspace=ws)
+        c2 = ops.gemm(a, b, ta, tb, alpha=0.5, workspace=ws)
+        # Accumulate mode (direct-store epilogue) and an output view TMA cannot store to
+        ops.gemm(a, b, ta, tb, alpha=0.5, beta=1.0, c=cacc, workspace=ws)
+        ops.gemm(a, b, ta, tb, alpha=0.5, c=wide[:, 1:n + 1], workspace=ws)
+    finally:
+        L.cacti_b200_tune(b"gemm_split", 0)
+    assert torch.equal(c1, c2)
+    ref = R.ref_gemm(host(a), host(b), ta, tb, alpha=0.5)
+    assert_close(host(c1), ref, "float16", f"k-split gemm {m}x{n}x{k} ta={ta} tb={tb}", floor_frac=1.0)
+    diff = (c1.float() - plain.float()).abs()
+    assert float(diff.max()) <= 2.0 ** -10 * float(plain.float().abs().max())
+    assert 0 < float((diff > 0).float().mean()) < 0.2       # another summation order, yet mostly the same 16-bit values
+    assert_close(host(cacc), R.ref_gemm(host(a), host(b), ta, tb, alpha=0.5, beta=1.0, c=host(old)), "float16", "k-split beta=1",
+                 floor_frac=1.0)
+    assert torch.equal(wide[:, 1:n + 1], c1) and not wide[:, 0].any() and not wide[:, n + 1:].any()
+    import ctypes as C
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+
+
+def test_gemm_k_split_fewer_sm_pairs(cuda, k_split):
+    """The schedule follows the worker count: with SMs left free for a concurrent kernel (gemm_sms) the ranges are cut
+    for that many pairs."""
+    L = capi.lib()
+    a, b = dev(_stored(61, 2048, 3200, False)), dev(_stored(62, 3200, 3200, True, 0.1))
+    ws = ops.gemm_workspace(2048, 3200, 3200, a.device)
+    ref = R.ref_gemm(host(a), host(b), False, True)
+    for sms in (132, 100, 0):
+        L.cacti_b200_tune(b"gemm_sms", sms)
+        try:
+            c = ops.gemm(a, b, False, True, workspace=ws)
+        finally:
+            L.cacti_b200_tune(b"gemm_sms", 0)
+        assert_close(host(c), ref, "float16", f"k-split on {sms} SMs", floor_frac=1.0)
+
+
 @pytest.mark.parametrize("hd", [100, 128, 64])
 def test_block_gemm_attention_shapes(cuda, hd):
     """The four block matmuls of one attention layer and their adjoints, layout [B, S, H, hd] / [B, Sq, H, Sk]."""
