@@ -2,21 +2,27 @@
 """Benchmark of the fused forward+backward thunks on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case <name> [--launches N] [--batch B] [--tune KNOB=VALUE]   # one small workload, for profilers
 
 Headline workload (N = 1): benchmark config 2 -- causal row softmax forward+backward on scores
-[1, 32, 2048, 2048] fp16 (fp32 accumulation), one fused launch per step.  `value` is the algorithmic
-HBM GB/s of that launch with inputs resident in HBM; `e2e` is the same quantity measured through
-the C-ABI call with HOST buffers (pinned H2D of scores and dP, D2H of P and dScores inside the timed
-region, pipelined per (batch, head) block).  Under torchrun (N > 1) every rank runs its own config-2
-sized batch (weak scaling, no data-path collective: softmax rows are independent).
+[1, 32, 2048, 2048] fp16 (fp32 accumulation), one fused launch per step.  `value` is the HBM GB/s of that launch
+with inputs resident in HBM, counted on the bytes a causal forward+backward has to move (the unmasked prefixes of
+S and dP read, P and dS written: 805 MB); the figure on the dense accounting (all four tensors whole, 1074 MB, of
+which the masked half of the inputs is never read) is reported beside it under `dense_accounting`.  `e2e` is the same
+quantity measured through the C-ABI call with HOST buffers (pinned H2D of scores and dP, D2H of P and dScores inside
+the timed region, pipelined per (batch, head) block).  Under torchrun (N > 1) every rank runs its own config-2 sized
+batch (weak scaling, no data-path collective: softmax rows are independent).
 
-`--impl reference` times the CPU restatement of the reference chain (oracle/ref_chain.c: one OpenMP
-loop per primitive thunk over materialised intermediates, all host threads) on a bounded sample of
-the same workload; the reference itself (Rust + patched Futhark) cannot be built on this image.
+`--impl reference` times the CPU restatement of the reference chain (oracle/ref_chain.c: one OpenMP loop per
+primitive thunk over materialised intermediates, all host threads) on a bounded sample of the same workload, in the
+same unit; the reference itself (Rust + patched Futhark) cannot be built on this image.
+
+`train_step` in the line is benchmark config 5 (see train_step_leg); `thunks` the other kernels at their shapes.
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -31,11 +37,15 @@ sys.path.insert(0, ROOT)
 HEADS, SEQ = 32, 2048                       # config 2: [1, 32, 2048, 2048]
 ROWS, COLS = HEADS * SEQ, SEQ
 ELEMS = ROWS * COLS
-ALGO_BYTES = 4 * ELEMS * 2                  # S, dP read; P, dS written; dense accounting (masked reads not credited)
+DENSE_BYTES = 4 * ELEMS * 2                 # S, dP, P, dS whole
+# what a causal kernel must move: row r reads r + 1 elements of S and of dP and writes whole rows of P and dS
+MOVED_BYTES = HEADS * (2 * (SEQ * (SEQ + 1) // 2) + 2 * SEQ * SEQ) * 2
 METRIC = "fused fwd+bwd thunk HBM GB/s (causal softmax, config 2)"
+CONFIG = {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (benchmark config 2)", "rows": ROWS, "cols": COLS,
+          "bytes_per_step": MOVED_BYTES}
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one softmax_rows_kernel launch on config 2
-# (profiles/softmax_fwd_bwd.md: 276.9 MB read + 477.2 MB written).
+# dram__bytes_read.sum + dram__bytes_write.sum of one softmax_rows_kernel launch on config 2, from an ncu capture of
+# `bench.py --case softmax_full` (276.9 MB read + 477.2 MB written); not re-measured by a bench run
 NCU_TRAFFIC_BYTES = 754140672
 
 
@@ -142,13 +152,11 @@ def run_reference(args, rank, world):
     for _ in range(args.warmup if args.warmup < 2 else 1):
         cpu_reference_time(1, 1, threads)
     sec, rows = cpu_reference_time(sample_heads, max(1, args.steps), threads)
-    gbs = (4 * rows * COLS * 2) / sec / 1e9
+    gbs = MOVED_BYTES * (rows / ROWS) / sec / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3 * (ROWS / rows), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-        "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (benchmark config 2)",
-                   "rows": ROWS, "cols": COLS},
+        "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic", "config": dict(CONFIG),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{sample_heads} of 32 (batch, head) blocks = {rows} rows per step; "
                                    "ms_per_step is scaled to the full 65536 rows"},
@@ -282,10 +290,24 @@ def other_thunks(torch, ops, peak):
     return out
 
 
-def train_step_leg(torch, dist, rank, world, dev, steps):
+def host_max(dist, ctl, value):
+    """Maximum of a host float over the ranks, through the CPU (gloo) control group: the timing scalars stay off NCCL,
+    so NCCL's algorithm for the gradient buckets can be pinned from the environment without touching them."""
+    if ctl is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ctl)
+    return float(t.item())
+
+
+def train_step_leg(torch, dist, ctl, rank, world, dev, steps):
     """benchmark config 5: one OpenLLaMA-3B-shaped forward+backward over 8 sequences of 2048 tokens, the sequences
     split across the ranks (strong scaling), weight gradients summed with bucketed NCCL all-reduces that overlap
-    the backward pass.  Random-init weights, synthetic token ids."""
+    the backward pass.  Random-init weights, synthetic token ids.  Reported beside the step time: the same step
+    replayed with the exchange left out (`compute_ms`; `exposed_comm_ms` is the difference), and the sum and sum of
+    magnitudes of three gradient tensors after the exchange, which must agree between 1, 2, 4 and 8 GPUs up to
+    summation order."""
     from cacti_b200 import dp, llama_step as LS, ops
     cfg = LS.LlamaShape.open_llama_3b()
     n_seq = 8
@@ -294,10 +316,9 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
     grads, buckets = dp.alloc_bucketed_grads(P)
     red = dp.GradReducer(buckets)
     step = LS.TrainStep(cfg, P, count, loss_tokens=n_seq * cfg.seq)
-    if world > 1:
-        # optionally leave SMs for the all-reduce kernels that run beside the backward pass (measured at 8 GPUs:
-        # margins of 16 and 32 SMs were 3-4 % slower than none, so the default is 0)
-        margin = int(os.environ.get("CACTI_B200_GEMM_SM_MARGIN", "0"))
+    # SMs left to the all-reduce kernels that run beside the backward pass (0: none)
+    margin = int(os.environ.get("CACTI_B200_GEMM_SM_MARGIN", "0")) if world > 1 else 0
+    if margin:
         ops.lib().cacti_b200_tune(b"gemm_sms", 148 - margin)
     g = torch.Generator(device=dev).manual_seed(1)
     tok_all = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g)
@@ -307,56 +328,130 @@ def train_step_leg(torch, dist, rank, world, dev, steps):
     tok, tgt = torch.empty_like(tok_all[sl]), torch.empty_like(tgt_all[sl])
     nl = cfg.layers
 
-    def body():
-        # end to end: token ids come from pinned host memory, the loss goes back to the host
-        tok.copy_(h_tok, non_blocking=True); tgt.copy_(h_tgt, non_blocking=True)
-        loss = step.forward_backward(tok, tgt, grads, on_layer_done=red.reduce_bucket)
-        red.reduce_bucket(nl + 1)                      # the embedding gradient, complete last
-        red.finish()
-        if world > 1:
-            dist.all_reduce(loss)
-        return loss
+    def make_body(exchange):
+        def body():
+            # end to end: token ids come from pinned host memory, the loss goes back to the host
+            tok.copy_(h_tok, non_blocking=True); tgt.copy_(h_tgt, non_blocking=True)
+            loss = step.forward_backward(tok, tgt, grads, on_layer_done=red.reduce_bucket if exchange else None)
+            if exchange:
+                red.reduce_bucket(nl + 1)                  # the embedding gradient, complete last
+                red.finish()
+                if world > 1:
+                    dist.all_reduce(loss)
+            return loss
+        return body
 
     # the step is replayed from a CUDA graph (kernels, pinned-memory token copies and the bucketed all-reduces are all
     # captured); CACTI_B200_STEP_GRAPH=0 launches it eagerly instead
-    launch = "eager"
-    graphed = None
-    if os.environ.get("CACTI_B200_STEP_GRAPH", "1") != "0":
-        try:
-            graphed = LS.GraphedStep(body)
-            launch = "cuda graph"
-        except Exception as e:                         # same kernels either way; the line says which launch it timed
-            graphed = None
-            launch = "eager (graph capture failed: %s)" % (str(e).splitlines()[0][:120] if str(e) else type(e).__name__)
-            torch.cuda.synchronize()
+    use_graph = os.environ.get("CACTI_B200_STEP_GRAPH", "1") != "0"
 
-    def one():
-        return (graphed.replay() if graphed is not None else body()).cpu()
+    def timed(exchange, reps):
+        body = make_body(exchange)
+        launch, graphed = "eager", None
+        if use_graph:
+            try:
+                graphed = LS.GraphedStep(body)
+                launch = "cuda graph"
+            except Exception as e:                     # same kernels either way; the line says which launch it timed
+                graphed = None
+                launch = "eager (graph capture failed: %s)" % (str(e).splitlines()[0][:120] if str(e) else type(e).__name__)
+                torch.cuda.synchronize()
 
-    for _ in range(2):
-        one()
+        def one():
+            return (graphed.replay() if graphed is not None else body()).cpu()
+
+        for _ in range(3):
+            one()
+        if world > 1:
+            dist.barrier(group=ctl)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            loss = one()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=ctl)
+        ms = host_max(dist, ctl if world > 1 else None, e0.elapsed_time(e1) / reps)
+        del graphed
+        torch.cuda.empty_cache()
+        return ms, float(loss.item()), launch
+
+    reps = max(10, min(steps, 20))
+    compute_ms = None
     if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        loss = one()
-    e1.record()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
-    ops.lib().cacti_b200_tune(b"gemm_sms", 0)
-    return {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (benchmark config 5)",
-            "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "scaling": "strong", "n_gpus": world,
-            "sequences_per_gpu": count, "loss": float(loss.item()), "gpu_launches_per_step": step.launches, "launch": launch,
-            "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
-            "h2d_bytes_per_step": 2 * count * cfg.seq * 4, "d2h_bytes_per_step": 4,
-            "note": "no optimizer step (the optimizer thunks are outside this path); gradients of all parameters are produced and all-reduced"}
+        compute_ms, _, _ = timed(False, reps)          # before the real step, so that the gradients left behind are the reduced ones
+    ms, loss, launch = timed(True, reps)
+    if margin:
+        ops.lib().cacti_b200_tune(b"gemm_sms", 0)
+    # f64 sum and sum of magnitudes of three gradients after the exchange (torch reductions: verification, not the path)
+    checks = {}
+    for name, t in (("lm_head", grads["lm_head"]), ("layers.0.q", grads["layers"][0]["q"]), ("embed", grads["embed"])):
+        d = t.double()
+        checks[name] = {"sum": float(d.sum().item()), "abs_sum": float(d.abs().sum().item())}
+    out = {"workload": "OpenLLaMA-3B-shaped fwd+bwd, 8 x 2048 tokens, 26 layers, f16 / f32 accumulate (benchmark config 5)",
+           "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "scaling": "strong", "n_gpus": world,
+           "timed_replays": reps, "sequences_per_gpu": count, "loss": loss, "gpu_launches_per_step": step.launches,
+           "launch": launch, "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+           "h2d_bytes_per_step": 2 * count * cfg.seq * 4, "d2h_bytes_per_step": 4, "grad_checksums": checks,
+           "note": "no optimizer step (the optimizer thunks are outside this path); gradients of all parameters are produced and all-reduced"}
+    if compute_ms is not None:
+        out.update({"compute_ms": compute_ms, "exposed_comm_ms": ms - compute_ms, "gemm_sm_margin": margin,
+                    "exchange": {"collective": "ncclAllReduce(sum) per bucket via torch.distributed", "buckets": len(buckets),
+                                 "bytes_per_rank": sum(b.numel() * b.element_size() for b in buckets),
+                                 "env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_")}}})
+    return out
+
+
+def train_step_spill_leg(torch, dev, steps):
+    """benchmark config 5 on one GPU the way the reference would run it: every tensor a cell of one arena, every op a
+    thunk, the arena's soft limit (CACTI_VMEM_SOFT_LIMIT, default 40GiB here) below the step's resident peak of about
+    63 GiB, so that the soft-OOM policy spills cells to page-locked host memory during the forward pass and the
+    backward pass copies them back (cacti_b200/cell_step.py over the C++ shim in cacti_b200/host/).  Same weights,
+    tokens and kernels as `train_step`: the loss must be the same number."""
+    import numpy as np
+    from cacti_b200 import llama_step as LS
+    from cacti_b200.cell_step import CellTrainStep
+    from cacti_b200.host import binding as H
+    cfg = LS.LlamaShape.open_llama_3b()
+    n_seq = 8
+    P = LS.init_weights(cfg, dev, seed=0)
+    W = {k: v.cpu().numpy() for k, v in P.items() if k != "layers"}
+    W["layers"] = [{k: v.cpu().numpy() for k, v in Lw.items()} for Lw in P["layers"]]
+    del P
+    g = torch.Generator(device=dev).manual_seed(1)
+    tok = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g).cpu().numpy()
+    tgt = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g).cpu().numpy()
+    torch.cuda.empty_cache()
+    free_b, total_b = torch.cuda.mem_get_info(dev)
+    text = os.environ.get("CACTI_VMEM_SOFT_LIMIT", "40GiB")
+    limit = H.lib().cbh_parse_vmem_soft_limit(text.encode(), total_b, free_b)
+    if not limit:
+        return {"skipped": f"CACTI_VMEM_SOFT_LIMIT={text!r} is neither a fraction nor a byte size"}
+    ctx = H.Ctx(cuda=True, arena_bytes=min(limit + (4 << 30), free_b - (2 << 30)), soft_limit=limit)
+    try:
+        step = CellTrainStep(ctx, cfg, W, n_seq, loss_tokens=n_seq * cfg.seq)
+        stream = torch.cuda.ExternalStream(H.lib().cbh_stream(ctx.h), device=dev)
+        step.forward_backward(tok, tgt)                       # warm-up: page-locked buffers get allocated here
+        before = ctx.stats()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            loss = step.forward_backward(tok, tgt)
+        e1.record(stream)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        after = ctx.stats()
+        per = {k: (after[k] - before[k]) / steps for k in ("spills", "reloads", "spill_bytes", "reload_bytes", "oom_retries")}
+        return {"workload": "the train_step workload on one GPU, tensors as cells of an arena under the soft-OOM spill policy",
+                "tokens_per_s": n_seq * cfg.seq / (ms * 1e-3), "ms_per_step": ms, "timed_steps": steps, "loss": loss,
+                "soft_limit_bytes": int(limit), "soft_limit_text": text, "arena_peak_bytes": int(after["peak_in_use"]),
+                "per_step": per, "hard_oom": after["hard_oom"], "thunks_per_step": step.launches,
+                "note": "spill and reload copies run on the thunks' own stream, as the reference's do (it synchronises around each); "
+                        "the policy evicts in creation order, so parameters are spilled and reloaded as well as activations"}
+    finally:
+        ctx.close()
 
 
 def run_ours(args, rank, world, local_rank):
@@ -368,8 +463,12 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py needs a CUDA device; the CPU arm is --impl reference")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    ctl = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that dies or never joins ends the others' next collective with an error after this long, not a hang
+        limit = datetime.timedelta(seconds=int(os.environ.get("CACTI_B200_PG_TIMEOUT_S", "300")))
+        dist.init_process_group("nccl", device_id=dev, timeout=limit)
+        ctl = dist.new_group(backend="gloo", timeout=limit)      # host-side control plane: barriers and timing scalars
     peak, peak_kind = measured_peak()
     gen = torch.Generator(device=dev).manual_seed(rank)
     s = (torch.randn(ROWS, COLS, device=dev, generator=gen) * 0.1).half()
@@ -381,9 +480,9 @@ def run_ours(args, rank, world, local_rank):
         ops.softmax_fwd_bwd(s, dp, mask, p=p, ds=ds)
 
     def barrier():
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=ctl)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -403,12 +502,8 @@ def run_ours(args, rank, world, local_rank):
             while time.time() < t_end:
                 step()
             torch.cuda.synchronize()
-    t = torch.tensor([dev_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = t.item()
-    ms_step = ms_total / args.steps
-    value = world * ALGO_BYTES / (ms_step * 1e-3) / 1e9
+    ms_step = host_max(dist, ctl, dev_ms) / args.steps
+    value = world * MOVED_BYTES / (ms_step * 1e-3) / 1e9
 
     # ---- end to end: host buffers through the same call, pipelined per (batch, head) block -------------
     hs, hdp = s.cpu().pin_memory(), dp.cpu().pin_memory()
@@ -452,48 +547,152 @@ def run_ours(args, rank, world, local_rank):
         e2e_step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = t.item() / e2e_steps
+    e2e_ms = host_max(dist, ctl, e0.elapsed_time(e1)) / e2e_steps
     e2e_ok = bool(torch.equal(hp[:SEQ], p[:SEQ].cpu()) and torch.equal(hds[-SEQ:], ds[-SEQ:].cpu()))
     del hs, hdp, hp, hds, bufs
+    unmasked_ms = None
+    if rank == 0 and not args.no_extra:             # the same kernel without the mask: every byte of the four tensors moves
+        unmasked_ms = time_thunk(lambda: ops.softmax_fwd_bwd(s, dp, None, p=p, ds=ds), 10, 3, torch) * 1e3
 
     train = None
     if not args.no_train:
         torch.cuda.empty_cache()
-        train = train_step_leg(torch, dist, rank, world, dev, max(1, min(args.steps, 3)))
+        train = train_step_leg(torch, dist, ctl, rank, world, dev, args.steps)
+        torch.cuda.empty_cache()
+    spill = None
+    if world == 1 and not args.no_train and not args.no_spill:
+        spill = train_step_spill_leg(torch, dev, 2)
         torch.cuda.empty_cache()
     line = None
     if rank == 0:
         thunks = other_thunks(torch, ops, peak) if not args.no_extra else {}
+        if unmasked_ms is not None:
+            thunks["softmax_fwd_bwd, no mask[65536x2048,f16]"] = {
+                "GB/s": round(DENSE_BYTES / unmasked_ms / 1e6, 1), "frac_of_peak": round(DENSE_BYTES / unmasked_ms / 1e6 / peak, 3),
+                "us": round(unmasked_ms * 1e3, 1), "algorithmic_bytes": DENSE_BYTES, "launches_per_step": 1}
         cpu = None
         if world == 1 and not args.no_cpu:
             threads = physical_cores()
             sec, rows = cpu_reference_time(4, 3, threads)
-            cpu = {"value": (4 * rows * COLS * 2) / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            cpu = {"value": MOVED_BYTES * (rows / ROWS) / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                    "sample": f"4 of 32 (batch, head) blocks ({rows} rows), median of 3 passes of oracle/ref_chain.c"}
-        achieved = ALGO_BYTES / (ms_step * 1e-3) / 1e9
+        achieved = MOVED_BYTES / (ms_step * 1e-3) / 1e9
+        dense = DENSE_BYTES / (ms_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 per GPU (benchmark config 2)",
-                       "rows": ROWS, "cols": COLS, "mask": "causal, applied in-kernel",
-                       "l2": "working set 1.07 GB per step, far larger than the 126 MB L2; no flush needed"},
+            "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic", "config": dict(CONFIG),
+            "notes": {"per_gpu": "every rank runs the config's workload (weak scaling)", "mask": "causal, applied in-kernel",
+                      "l2": "working set 0.8 GB per step, far larger than the 126 MB L2; no flush needed",
+                      "bytes": "value, roofline and e2e count the bytes a causal kernel must move (masked inputs are never read); "
+                               "dense_accounting counts all four tensors whole"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / 8000.0, "peak_kind": peak_kind + " copy bandwidth",
-                         "traffic": NCU_TRAFFIC_BYTES, "algorithmic_bytes": ALGO_BYTES,
-                         "kernel": "softmax_rows_kernel<half,8,fwd,bwd>"},
+                         "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu capture of `bench.py --case softmax_full`, one launch",
+                         "algorithmic_bytes": MOVED_BYTES, "kernel": "softmax_rows_kernel<half,8,fwd,bwd>",
+                         "dense_accounting": {"bytes": DENSE_BYTES, "achieved": dense, "frac": dense / peak}},
             "cpu_baseline": cpu,
-            "e2e": {"value": world * ALGO_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+            "e2e": {"value": world * MOVED_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * ELEMS * 2, "d2h_bytes_per_step": 2 * ELEMS * 2, "verified": e2e_ok},
-            "gpu_launches": args.steps, "clocks": clocks.summary(), "thunks": thunks, "train_step": train,
+            "gpu_launches": args.steps, "clocks": clocks.summary(), "thunks": thunks, "train_step": train, "train_step_spill": spill,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        dist.barrier(group=ctl)
         dist.destroy_process_group()
+
+
+def run_case(a):
+    """One small single-kernel workload, a few launches, for a profiler (a few GB at most; inputs larger than the
+    126 MB L2 so that DRAM counters mean something).  Cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16),
+    softmax_full (config 2), nll (2048 x 32000), rmsnorm (16384 x 3200), rope (16384 x 32 x 100), swiglu (4096 x 8640),
+    gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200), qk / pv / attn_fwd / attn_bwd (--batch sequences of config 5),
+    train_step (one config-5 forward+backward over --batch sequences; only for a single-pass launch list)."""
+    import torch
+    from cacti_b200 import ops
+    for kv in a.tune:
+        k, v = kv.split("=")
+        if ops.lib().cacti_b200_tune(k.encode(), int(v)) != 0:
+            raise SystemExit(f"tune {kv} rejected")
+    gen = torch.Generator(device="cuda").manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device="cuda", generator=gen) * scale).half()
+
+    def empty(*shape):
+        return torch.empty(*shape, dtype=torch.float16, device="cuda")
+
+    case = a.case
+    if case in ("softmax", "softmax_full"):
+        heads = 32 if case == "softmax_full" else 8
+        s, dp = rnd(heads * 2048, 2048, scale=0.1), rnd(heads * 2048, 2048)
+        p, ds = torch.empty_like(s), torch.empty_like(s)
+        fn = lambda: ops.softmax_fwd_bwd(s, dp, (1, 2048, 0), p=p, ds=ds)
+    elif case == "nll":
+        lg = rnd(2048, 32000, scale=2.0)
+        tg = torch.randint(0, 32000, (2048,), device="cuda", dtype=torch.int32, generator=gen)
+        dl = torch.empty_like(lg)
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+        fn = lambda: ops.softmax_nll_fwd_bwd(lg, tg, w_scalar=1.0 / 2048, dlogits=dl, status=st)
+    elif case == "rmsnorm":
+        x, dy, g = rnd(16384, 3200), rnd(16384, 3200), rnd(3200)
+        y, dx, dg = torch.empty_like(x), torch.empty_like(x), empty(3200)
+        ws = ops.rmsnorm_workspace(16384, 3200, x.device)
+        fn = lambda: ops.rmsnorm_fwd_bwd(x, g, dy, 1e-6, y=y, dx=dx, dgamma=dg, workspace=ws)
+    elif case == "rope":
+        cos, sin = ops.rope_tables(2048, 100)
+        q, dq = rnd(16384, 32, 100), rnd(16384, 32, 100)
+        yq, dxq = torch.empty_like(q), torch.empty_like(q)
+        fn = lambda: ops.rope_fwd_bwd(q, dq, cos, sin, y=yq, dx=dxq)
+    elif case == "swiglu":
+        ga, up, dh = rnd(4096, 8640), rnd(4096, 8640), rnd(4096, 8640)
+        h, dga, dup = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
+        fn = lambda: ops.swiglu_fwd_bwd(ga, up, dh, h=h, dgate=dga, dup=dup)
+    elif case == "train_step":
+        from cacti_b200 import dp as DP, llama_step as LS
+        cfg = LS.LlamaShape.open_llama_3b()
+        P = LS.init_weights(cfg, torch.device("cuda"))
+        grads, _ = DP.alloc_bucketed_grads(P)
+        step = LS.TrainStep(cfg, P, a.batch)
+        tok = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
+        tgt = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
+        fn = lambda: step.forward_backward(tok, tgt, grads)
+    elif case in ("gemm_nt", "gemm_nn", "gemm_tn"):
+        m, n, k = 4096, 3200, 3200
+        if case == "gemm_nt":          # y = x W^T (forward projection)
+            x, w, c = rnd(m, k), rnd(n, k, scale=0.02), empty(m, n)
+            fn = lambda: ops.gemm(x, w, False, True, c=c)
+        elif case == "gemm_nn":        # dx = dy W
+            x, w, c = rnd(m, n), rnd(n, k, scale=0.02), empty(m, k)
+            fn = lambda: ops.gemm(x, w, False, False, c=c)
+        else:                          # dW = dy^T x
+            x, w, c = rnd(m, n), rnd(m, k), empty(n, k)
+            fn = lambda: ops.gemm(x, w, True, False, c=c)
+    elif case in ("qk", "pv", "attn_fwd", "attn_bwd"):
+        bsz, sq, h, hd = a.batch, 2048, 32, 100
+        if case == "qk":
+            q, kk, c = rnd(bsz, sq, h, hd), rnd(bsz, sq, h, hd), empty(bsz, sq, h, sq)
+            ws = torch.empty(ops.lib().cacti_b200_gemm_workspace_bytes(sq, sq, hd, bsz, h), dtype=torch.uint8, device="cuda")
+            fn = lambda: ops.block_gemm(q, kk, False, True, alpha=0.1, c=c, workspace=ws)
+        elif case == "pv":
+            pr, v, c = rnd(bsz, sq, h, sq, scale=0.02), rnd(bsz, sq, h, hd), empty(bsz, sq, h, hd)
+            ws = torch.empty(ops.lib().cacti_b200_gemm_workspace_bytes(sq, hd, sq, bsz, h), dtype=torch.uint8, device="cuda")
+            fn = lambda: ops.block_gemm(pr, v, False, False, c=c, workspace=ws)
+        else:
+            alpha = hd ** -0.5
+            q, kk, v, do = (ops.block_pad(rnd(bsz, sq, h, hd), 128) for _ in range(4))
+            ctx, st = ops.attention_fwd(q, kk, v, hd, alpha)
+            if case == "attn_fwd":
+                fn = lambda: ops.attention_fwd(q, kk, v, hd, alpha, ctx=ctx, stats=st)
+            else:
+                pp, dss = empty(bsz, sq, h, sq), empty(bsz, sq, h, sq)
+                fn = lambda: ops.attention_bwd_prep(q, kk, v, do, ctx, st, alpha, p=pp, ds=dss)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    for _ in range(a.launches):
+        fn()
+    torch.cuda.synchronize()
+    print("done", case)
 
 
 def main():
@@ -505,7 +704,15 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the per-thunk table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-train", action="store_true", help="skip the config-5 training-step leg")
+    ap.add_argument("--no-spill", action="store_true", help="skip the config-5 leg under the spill policy (N = 1 only)")
+    ap.add_argument("--case", default=None, help="run one small single-kernel workload (see run_case) and exit")
+    ap.add_argument("--launches", type=int, default=3, help="launches of the --case workload")
+    ap.add_argument("--batch", type=int, default=2, help="sequences for the attention / train_step cases")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
+                    help="set a cacti_b200_tune knob before a --case run (repeatable), e.g. gemm_pair=1")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -670,8 +670,8 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   p.idesc_s = common;                       // A, B K-major
   p.idesc_pv = common | (1u << 16);         // B (V) MN-major
   auto kern = attention_fwd_kernel<T>;
-  static bool attr_set = false;
-  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnFwdSmem); attr_set = true; }
+  static bool attr_set[kMaxDevices] = {};
+  ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
   kern<<<(unsigned)grid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
                                                            reinterpret_cast<float*>(stats), p);
@@ -709,8 +709,8 @@ static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t
     if (rc) return rc;
   }
   auto kern = attention_bwd_prep_kernel<T>;
-  static bool attr_set = false;
-  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnBwdSmem); attr_set = true; }
+  static bool attr_set[kMaxDevices] = {};
+  ensure_dynamic_smem(kern, kAttnBwdSmem, attr_set);
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
   kern<<<(unsigned)grid, kAttnThreads, kAttnBwdSmem, st>>>(tmQ, tmK, tmV, tmdO, tmP, tmdS,
                                                            reinterpret_cast<const T*>(ctx), reinterpret_cast<const T*>(dctx),

@@ -20,6 +20,23 @@ inline int check_launch() {
 
 inline bool aligned16(uint64_t p) { return (p & 15u) == 0; }
 
+// Ordinal of the current device, for caches of per-device state (function attributes, occupancy, symbol addresses).
+constexpr int kMaxDevices = 64;
+inline int device_ordinal() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) d = 0;
+  return d;
+}
+// Raise a kernel's dynamic shared memory limit once per device (the attribute belongs to the device's copy of the
+// function: a process that drives a second device must set it there too).
+template <typename K> inline void ensure_dynamic_smem(K kern, size_t smem, bool (&done)[kMaxDevices]) {
+  const int d = device_ordinal();
+  if (!done[d]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    done[d] = true;
+  }
+}
+
 // Programmatic dependent launch, for a short second kernel that consumes what the kernel before it in the stream
 // wrote (a partial-sum fold): launched this way, its launch and block scheduling overlap the tail of the previous
 // kernel instead of following its completion.  The kernel launched with launch_dependent() must execute
@@ -313,26 +330,27 @@ constexpr size_t kMaxDynSmem = 200 * 1024;      // of the 227 KB a CTA may use
 // CTAs of `kern` that fit on one SM with this block size and dynamic shared memory; also raises the
 // kernel's dynamic shared memory limit when needed (never lowers it).  Cached per (kernel, config).
 template <typename K> inline int resident_ctas(K kern, int threads, size_t smem) {
-  struct Key { const void* k; int t; size_t s; int n; };
-  struct Lim { const void* k; size_t s; };
-  static thread_local Key cache[64];
-  static thread_local Lim lim[64];
+  struct Key { const void* k; int dev; int t; size_t s; int n; };
+  struct Lim { const void* k; int dev; size_t s; };
+  static thread_local Key cache[128];
+  static thread_local Lim lim[128];
   static thread_local int used = 0, nlim = 0;
   const void* kp = reinterpret_cast<const void*>(kern);
+  const int dev = device_ordinal();
   if (smem > 48 * 1024) {
     int i = 0;
-    for (; i < nlim; ++i) if (lim[i].k == kp) break;
-    if (i == nlim && nlim < 64) lim[nlim++] = Lim{kp, 0};
-    if (i >= 64 || lim[i].s < smem) {
+    for (; i < nlim; ++i) if (lim[i].k == kp && lim[i].dev == dev) break;
+    if (i == nlim && nlim < 128) lim[nlim++] = Lim{kp, dev, 0};
+    if (i >= 128 || lim[i].s < smem) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (i < 64) lim[i].s = smem;
+      if (i < 128) lim[i].s = smem;
     }
   }
   for (int i = 0; i < used; ++i)
-    if (cache[i].k == kp && cache[i].t == threads && cache[i].s == smem) return cache[i].n;
+    if (cache[i].k == kp && cache[i].dev == dev && cache[i].t == threads && cache[i].s == smem) return cache[i].n;
   int n = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) n = 1;
-  if (used < 64) cache[used++] = Key{kp, threads, smem, n};
+  if (used < 128) cache[used++] = Key{kp, dev, threads, smem, n};
   return n;
 }
 

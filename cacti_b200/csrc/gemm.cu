@@ -932,8 +932,8 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
 #define CB_GEMM2(AM_, BM_)                                                                             \
   do {                                                                                                 \
     auto kern = gemm_tc_pair_kernel<T, AM_, BM_>;                                                      \
-    static bool attr_set = false;                                                                      \
-    if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem); attr_set = true; } \
+    static bool attr_set[kMaxDevices] = {};                                                                      \
+    ensure_dynamic_smem(kern, kPairSmem, attr_set); \
     kern<<<(unsigned)(2 * pairs), kGemmThreads, kPairSmem, st>>>(tmA, tmB, tmC, C, p);                 \
   } while (0)
     if (!a_mn && !b_mn) CB_GEMM2(false, false); else if (!a_mn && b_mn) CB_GEMM2(false, true);
@@ -944,8 +944,8 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
 #define CB_GEMM(BN_, AM_, BM_)                                                                         \
   do {                                                                                                 \
     auto kern = gemm_tc_kernel<T, BN_, AM_, BM_>;                                                      \
-    static bool attr_set = false;                                                                      \
-    if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_set = true; } \
+    static bool attr_set[kMaxDevices] = {};                                                                      \
+    ensure_dynamic_smem(kern, smem, attr_set); \
     kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, tmC, C, p);                                            \
   } while (0)
   if (BN == 256) {

@@ -12,6 +12,7 @@
 // in a fixed order.  No floating-point atomics: results are run-to-run identical, as the
 // reference's cuBLAS setup also demands (cacti_gpu_cu_ffi/src/lib.rs:749).
 #include "common.cuh"
+#include <atomic>
 
 namespace cb {
 
@@ -402,15 +403,17 @@ static __device__ __align__(256) float g_rmsnorm_scratch[kNoAllocFloats];
 
 // `g_rmsnorm_scratch` in host code is only the host-side handle of the symbol, not an address a kernel
 // can use.  The device address is looked up once per device (with that device current) and cached.
+// The address belongs to the device's context: a caller that resets the device (cudaDeviceReset) or releases and
+// retains its primary context must not use this entry point afterwards in the same process.
 static int noalloc_scratch(float** out) {
-  constexpr int kMaxDevices = 64;
-  static float* cache[kMaxDevices] = {};
+  static std::atomic<float*> cache[kMaxDevices] = {};
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
     g_last_cuda_error = (int)cudaGetLastError();
     return CACTI_B200_ERR_LAUNCH;
   }
-  if (!cache[dev]) {
+  float* addr = cache[dev].load(std::memory_order_acquire);
+  if (!addr) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_rmsnorm_scratch);
     if (e != cudaSuccess || !p) {
@@ -418,9 +421,10 @@ static int noalloc_scratch(float** out) {
       (void)cudaGetLastError();
       return CACTI_B200_ERR_LAUNCH;
     }
-    cache[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    cache[dev].store(addr, std::memory_order_release);
   }
-  *out = cache[dev];
+  *out = addr;
   return CACTI_B200_OK;
 }
 

@@ -7,6 +7,8 @@ reference (examples/open_llama_3b_train.rs:161-169).
 """
 from __future__ import annotations
 
+import datetime
+
 import torch
 import torch.distributed as dist
 
@@ -50,10 +52,16 @@ def alloc_bucketed_grads(params):
 
 class GradReducer:
     """Launches one asynchronous all-reduce per bucket as soon as the bucket is complete, so the exchange
-    overlaps the rest of the backward pass; `finish()` waits for all of them."""
+    overlaps the rest of the backward pass; `finish()` waits for all of them.
 
-    def __init__(self, buckets, group=None):
-        self.buckets, self.group, self.pending = buckets, group, []
+    What a caller sees when a rank is lost (it exited, or never reached the exchange): nothing hangs for good.  A
+    collective that cannot complete ends with an exception, from `reduce_bucket` or from `finish`, no later than
+    `timeout_s` seconds after `finish` is called, or after the process group's own timeout where the backend waits
+    on the device rather than on the host (NCCL: the timeout given to init_process_group; its watchdog then ends the
+    communicator).  The reference has no counterpart (single GPU; any error is a panic, src/spine.rs:1856-1865)."""
+
+    def __init__(self, buckets, group=None, timeout_s: float | None = None):
+        self.buckets, self.group, self.pending, self.timeout_s = buckets, group, [], timeout_s
         self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
 
     def reduce_bucket(self, i: int):
@@ -61,6 +69,9 @@ class GradReducer:
             self.pending.append(dist.all_reduce(self.buckets[i], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
 
     def finish(self):
-        for w in self.pending:
-            w.wait()
-        self.pending = []
+        pending, self.pending = self.pending, []
+        for w in pending:
+            if self.timeout_s is None:
+                w.wait()
+            elif not w.wait(timeout=datetime.timedelta(seconds=self.timeout_s)):
+                raise RuntimeError("gradient exchange did not complete")

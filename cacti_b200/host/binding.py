@@ -27,6 +27,27 @@ def lib():
             "cbh_thunk_softmax_bwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
             "cbh_thunk_add": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, C.c_int]),
             "cbh_thunk_matmul": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int, C.c_int, C.c_float, C.c_int]),
+            "cbh_cell_free": (C.c_int, [_p, _i64]), "cbh_soft_limit": (_sz, [_p]), "cbh_stream": (_p, [_p]),
+            "cbh_parse_vmem_soft_limit": (_sz, [C.c_char_p, _sz, _sz]), "cbh_stats_bytes": (None, [_p, C.POINTER(C.c_longlong)]),
+            "cbh_arena_create": (_p, [_sz]), "cbh_arena_destroy": (None, [_p]), "cbh_arena_alloc": (_sz, [_p, _sz, C.c_int]),
+            "cbh_arena_free": (None, [_p, _sz]), "cbh_arena_front": (_sz, [_p]), "cbh_arena_back": (_sz, [_p]),
+            "cbh_arena_in_use": (_sz, [_p]),
+            "cbh_thunk_rmsnorm_bwd": (C.c_int, [_p, C.c_int, C.c_int, _i64, _i64, _i64, _i64, _i64, C.c_float, _i64, _i64, C.c_int, C.c_int]),
+            "cbh_thunk_rope_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
+            "cbh_thunk_rope_bwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
+            "cbh_thunk_swiglu_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, C.c_int]),
+            "cbh_thunk_swiglu_bwd": (C.c_int, [_p, C.c_int, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
+            "cbh_thunk_softmax_nll": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, C.c_int, C.c_float, _i64, _i64, C.c_int, _i64]),
+            "cbh_thunk_gather_rows": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, C.c_int, _i64, _i64, _i64, C.c_int, _i64]),
+            "cbh_thunk_scatter_add_rows": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, C.c_int, _i64, _i64, _i64, C.c_int, _i64]),
+            "cbh_thunk_block_pad": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]),
+            "cbh_thunk_block_matmul": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int, C.c_int,
+                                                 C.c_float, C.c_int, _i64, C.c_int, C.c_int]),
+            "cbh_thunk_attention_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_float, C.c_int]),
+            "cbh_thunk_attention_bwd_prep": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                       _i64, C.c_float, C.c_int]),
+            "cbh_thunk_adamw32_step": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int, C.c_int, C.c_float, C.c_float,
+                                                 C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]),
         }
         for n, (r, a) in sig.items():
             f = getattr(L, n)
@@ -35,7 +56,8 @@ def lib():
     return _lib
 
 
-APPLY, ACCUMULATE = 0, 1
+APPLY, ACCUMULATE, INITIALIZE = 0, 1, 2
+NO_CELL = -1          # an optional cell argument that is not given
 
 
 class Ctx:
@@ -65,7 +87,13 @@ class Ctx:
             raise RuntimeError("cell has no value")
         return out
 
+    def free(self, c):
+        assert self.L.cbh_cell_free(self.h, c) == 0
+
     def stats(self):
         a = (C.c_long * 6)()
         self.L.cbh_stats(self.h, a)
-        return dict(spills=a[0], drops=a[1], reloads=a[2], oom_retries=a[3], hard_oom=a[4], spill_copies=a[5])
+        b = (C.c_longlong * 3)()
+        self.L.cbh_stats_bytes(self.h, b)
+        return dict(spills=a[0], drops=a[1], reloads=a[2], oom_retries=a[3], hard_oom=a[4], spill_copies=a[5],
+                    spill_bytes=b[0], reload_bytes=b[1], peak_in_use=b[2])

@@ -169,6 +169,13 @@ class _StorageType:
 
 
 def _rebuild_tensor_v2(storage, storage_offset, size, stride, *unused):
+    # every value here comes from the file: check the types and signs before anything is computed from them
+    if not isinstance(storage, _StorageRef) or not isinstance(storage_offset, int) or isinstance(storage_offset, bool):
+        raise IngestError("PickleFile", "tensor record does not refer to a storage")
+    if not isinstance(size, (tuple, list)) or not isinstance(stride, (tuple, list)):
+        raise IngestError("PickleFile", "tensor record without a shape")
+    if any(not isinstance(d, int) or isinstance(d, bool) or d < 0 for d in tuple(size) + tuple(stride)) or storage_offset < 0:
+        raise IngestError("PickleFile", "negative or non-integer offset, dimension or stride")
     return _TensorRec(storage, int(storage_offset), tuple(size), tuple(stride))
 
 
@@ -193,6 +200,8 @@ class _InertUnpickler(pickle.Unpickler):
     def persistent_load(self, pid):
         if not (isinstance(pid, tuple) and len(pid) >= 5 and pid[0] == "storage" and isinstance(pid[1], _StorageType)):
             raise IngestError("PickleFile", "unexpected persistent id")
+        if not isinstance(pid[4], int) or isinstance(pid[4], bool) or pid[4] < 0 or not isinstance(pid[2], (str, int)):
+            raise IngestError("PickleFile", "malformed storage record")
         return _StorageRef(pid[1].tag, str(pid[2]), int(pid[4]))
 
 
@@ -241,6 +250,8 @@ class PickleDir(_Dir):
                     info = infos.get(f"{root}data/{t.storage.key}")
                     if info is None:
                         raise IngestError("PickleFile", f"{path}: storage {t.storage.key} of {name} is missing")
+                    if t.storage.dtype not in ST_DTYPES:
+                        raise IngestError("PickleFile", f"{name}: unsupported storage type {t.storage.dtype}")
                     esz = ST_DTYPES[t.storage.dtype][1]
                     # packed layout only (src/util/safepickle.rs:147-156)
                     packed, acc = [], 1
@@ -252,7 +263,7 @@ class PickleDir(_Dir):
                     base = _stored_entry_offset(raw, info)
                     off = base + t.storage_offset * esz
                     eoff = off + acc * esz
-                    if eoff > base + info.file_size or t.storage.numel * esz != info.file_size:
+                    if not (base <= off <= eoff <= base + info.file_size) or t.storage.numel * esz != info.file_size:
                         raise IngestError("PickleFile", f"{name}: tensor does not fit its storage")
                     if base % 64:
                         raise IngestError("PickleFile", f"{name}: storage is not 64-byte aligned in the archive")

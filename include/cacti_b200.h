@@ -130,7 +130,7 @@ int cacti_b200_rmsnorm_fwd_bwd(cacti_b200_dptr y, cacti_b200_dptr dx, cacti_b200
  * workspace the entry point above asks for.  Here the dgamma partials go to an array that is part of the
  * library image (about 4.6 MiB on every device that loads the library, for the life of the process); the
  * function itself calls no cudaMalloc / cudaFree and no allocating library routine.
- * Limits: cols <= 4096 (and rows <= 1212416 for rows that take the element-wise path); larger shapes return
+ * Limits: cols <= 4096 and rows <= 1212416, whichever kernel the shape is routed to; larger shapes return
  * CACTI_B200_ERR_SCRATCH_LIMIT.  The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress, with that device current); make that first call outside any stream capture.
  * All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race on

@@ -74,3 +74,45 @@ def test_gloo_world2_allreduce():
     outs = [p.communicate(timeout=120)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"ok {r}" in o, o
+
+
+LOST_RANK_WORKER = r'''
+import datetime, os, sys, time, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from cacti_b200 import dp
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=int(os.environ["RANK"]), world_size=2,
+                        timeout=datetime.timedelta(seconds=20))
+rank = dist.get_rank()
+buckets = [torch.full((64,), float(rank + 1)) for _ in range(2)]
+red = dp.GradReducer(buckets, timeout_s=5.0)
+red.reduce_bucket(0); red.reduce_bucket(1); red.finish()          # step 1: both ranks take part
+assert torch.all(buckets[0] == 3.0)
+dist.barrier()
+if rank == 1:
+    print("ok 1 (leaving between steps)", flush=True)
+    os._exit(0)                                                     # the rank is gone: no shutdown handshake
+t0 = time.time()
+try:                                                                # step 2: the survivor's exchange must end with an error
+    red.reduce_bucket(0); red.reduce_bucket(1); red.finish()
+    print("exchange completed without its peer", flush=True); sys.exit(3)
+except Exception as e:
+    dt = time.time() - t0
+    assert dt < 15.0, dt
+    print(f"ok 0 (raised {type(e).__name__} after {dt:.1f} s)", flush=True)
+os._exit(0)
+'''
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_exchange_with_an_error():
+    """Failure made on the host: rank 1 exits between two steps.  Rank 0's next gradient exchange raises within the
+    reducer's time-out instead of waiting for ever."""
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), PORT=str(port), REPO=repo)
+        procs.append(subprocess.Popen([sys.executable, "-c", LOST_RANK_WORKER], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"ok {r}" in o, o

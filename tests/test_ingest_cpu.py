@@ -198,3 +198,60 @@ def test_pickle_is_interpreted_never_executed(tmp_path):
     (tmp_path / "pytorch_model.bin").write_bytes(b"not a zip")
     with pytest.raises(ingest.IngestError):
         ingest.PickleDir.open(tmp_path)
+
+
+class _Stor:            # stands for a storage; written as a persistent id, as torch.save does
+    def __init__(self, numel):
+        self.numel = numel
+
+
+class _Rec:             # pickles as a call of torch._utils._rebuild_tensor_v2 with arguments of the test's choosing
+    def __init__(self, *args):
+        self.args = args
+
+    def __reduce__(self):
+        import torch._utils
+        return (torch._utils._rebuild_tensor_v2, self.args)
+
+
+def _crafted_archive(path, record, storage_bytes=64 * 2):
+    import io
+
+    class P(pickle.Pickler):
+        def persistent_id(self, obj):
+            if isinstance(obj, _Stor):
+                return ("storage", torch.HalfStorage, "0", "cpu", obj.numel)
+            return None
+
+    buf = io.BytesIO()
+    P(buf, protocol=2).dump(OrderedDict(w=record))
+    with zipfile.ZipFile(path, "w", zipfile.ZIP_STORED) as z:
+        z.writestr("archive/data.pkl", buf.getvalue())
+        # the storage starts on a 64-byte boundary of the archive, as torch.save writes it (padding in the extra field)
+        info = zipfile.ZipInfo("archive/data/0")
+        pad = -(z.fp.tell() + 30 + len(info.filename) + 4) % 64
+        info.extra = struct.pack("<HH", 0x4246, pad) + bytes(pad)
+        z.writestr(info, bytes(storage_bytes))
+
+
+@pytest.mark.parametrize("what,args", [
+    ("negative offset", (_Stor(64), -8, (4, 4), (4, 1))),
+    ("negative dimension", (_Stor(64), 0, (-4, 4), (4, 1))),
+    ("offset past the storage", (_Stor(64), 60, (4, 4), (4, 1))),
+    ("first argument is not a storage", (7, 0, (4, 4), (4, 1))),
+    ("non-integer dimension", (_Stor(64), 0, (4.0, 4), (4, 1))),
+    ("shape is not a sequence", (_Stor(64), 0, 16, (1,))),
+])
+def test_pickle_records_with_hostile_numbers_are_refused(tmp_path, what, args):
+    """Offsets, dimensions and the storage reference come from the file: a crafted record must end in IngestError,
+    never in a slice of other bytes of the archive or in a Python exception of another kind."""
+    _crafted_archive(tmp_path / "pytorch_model.bin", _Rec(*args))
+    with pytest.raises(ingest.IngestError) as e:
+        ingest.PickleDir.open(tmp_path)
+    assert e.value.kind == "PickleFile", what
+
+
+def test_pickle_record_well_formed_by_hand(tmp_path):
+    _crafted_archive(tmp_path / "pytorch_model.bin", _Rec(_Stor(64), 16, (4, 4), (4, 1)))
+    d = ingest.PickleDir.open(tmp_path)
+    assert d.get("w")[1] == (4, 4) and len(bytes(d.get("w")[2])) == 32

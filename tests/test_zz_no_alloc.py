@@ -54,6 +54,12 @@ def test_noalloc_matches_workspace_entry_twice(cuda):
         (y0, dx0, dg0), (y1, dx1, dg1) = _both(x, gamma, dy, 1e-6)
         assert torch.equal(y0, y1) and torch.equal(dx0, dx1)          # row-local results do not depend on the grid
         assert_close(host(dg1), host(dg0), kind, f"dgamma {shape}")   # column partials may be grouped differently
+        # and against the CPU oracle, like the regular entry point is in the parity tests
+        # (the oracle's single-rounding fp64 form, the one the shape sweep of the regular entry point is held to)
+        ry, rdx, rdg = R.ideal64_rmsnorm(host(x), host(gamma), host(dy), 1e-6)
+        assert_close(host(y1), ry, kind, f"y {shape} vs oracle")
+        assert_close(host(dx1), rdx, kind, f"dx {shape} vs oracle")
+        assert_close(host(dg1), rdg, kind, f"dgamma {shape} vs oracle")
     # fp32 partial output, as a collective would consume it
     x, gamma, dy = dev(R.normal(1, (512, 3200), np.float16)), dev(R.normal(2, (3200,), np.float16)), dev(R.normal(3, (512, 3200), np.float16))
     (_, _, a), (_, _, b) = _both(x, gamma, dy, 1e-6, dgamma_dtype=capi.R_32F)
