@@ -505,6 +505,17 @@ def run_ours(args, rank, world, local_rank):
     ms_step = host_max(dist, ctl, dev_ms) / args.steps
     value = world * MOVED_BYTES / (ms_step * 1e-3) / 1e9
 
+    if args.train_only:                          # sweeps of the multi-GPU step: only the train_step entry is printed
+        del s, dp, p, ds
+        torch.cuda.empty_cache()
+        train = train_step_leg(torch, dist, ctl, rank, world, dev, args.steps)
+        if rank == 0:
+            print(json.dumps({"n_gpus": world, "train_step": train}), flush=True)
+        if world > 1:
+            dist.barrier(group=ctl)
+            dist.destroy_process_group()
+        return
+
     # ---- end to end: host buffers through the same call, pipelined per (batch, head) block -------------
     hs, hdp = s.cpu().pin_memory(), dp.cpu().pin_memory()
     hp, hds = torch.empty_like(hs).pin_memory(), torch.empty_like(hs).pin_memory()
@@ -704,6 +715,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the per-thunk table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-train", action="store_true", help="skip the config-5 training-step leg")
+    ap.add_argument("--train-only", action="store_true", help="print only the config-5 train_step entry (for sweeps; not a bench line)")
     ap.add_argument("--no-spill", action="store_true", help="skip the config-5 leg under the spill policy (N = 1 only)")
     ap.add_argument("--case", default=None, help="run one small single-kernel workload (see run_case) and exit")
     ap.add_argument("--launches", type=int, default=3, help="launches of the --case workload")

@@ -10,7 +10,7 @@ extern int g_rmsnorm_threads, g_rmsnorm_gpref, g_rmsnorm_smem_kb, g_rmsnorm_bulk
 extern int g_nll_gpref, g_nll_stages, g_nll_mode, g_nll_smem_threads;
 extern int g_rope_threads, g_rope_ctas_per_sm, g_rope_staged, g_rope_staged_g, g_rope_staged_groups, g_rope_staged_stages;
 extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
-extern int g_gemm_bn, g_gemm_group_m, g_gemm_sms, g_gemm_pair, g_gemm_split;
+extern int g_gemm_bn, g_gemm_group_m, g_gemm_sms, g_gemm_pair, g_gemm_split, g_gemm_dynamic;
 }  // namespace cb
 
 extern "C" {
@@ -102,7 +102,7 @@ int cacti_b200_tune(const char* name, int value) {
       {"rope_threads", &g_rope_threads, 32, 256},         {"rope_ctas_per_sm", &g_rope_ctas_per_sm, 1, 64},
       {"rope_staged", &g_rope_staged, 0, 1},              {"rope_staged_g", &g_rope_staged_g, 32, 512},
       {"rope_staged_groups", &g_rope_staged_groups, 1, 15}, {"rope_staged_stages", &g_rope_staged_stages, 2, 8},
-      {"gemm_bn", &g_gemm_bn, 0, 256}, {"gemm_group_m", &g_gemm_group_m, 0, 4096}, {"gemm_sms", &g_gemm_sms, 0, 148}, {"gemm_pair", &g_gemm_pair, 0, 1}, {"gemm_split", &g_gemm_split, 0, 1},
+      {"gemm_bn", &g_gemm_bn, 0, 256}, {"gemm_group_m", &g_gemm_group_m, 0, 4096}, {"gemm_sms", &g_gemm_sms, 0, 148}, {"gemm_pair", &g_gemm_pair, 0, 1}, {"gemm_split", &g_gemm_split, 0, 1}, {"gemm_dynamic", &g_gemm_dynamic, 0, 1},
       {"swiglu_threads", &g_swiglu_threads, 32, 256},     {"swiglu_ctas_per_sm", &g_swiglu_ctas_per_sm, 1, 64},
   };
   if (!name) return CACTI_B200_ERR_INVALID_VALUE;

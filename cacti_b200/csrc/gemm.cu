@@ -52,6 +52,7 @@ struct GemmParams {
   long long sk_tiles, sk_units;           // tiles [0, sk_tiles) are shared out in k-blocks: sk_units = sk_tiles * k-blocks
   float* sk_part;                         // [workers][2 CTAs][256 columns][128 rows] f32 partial accumulators
   int sk_slot;                            // which row of g_sk_flags this launch signals through
+  int dyn;                                // 1: tiles beyond a worker's first come from g_tile_next[sk_slot] (dynamic schedule)
 };
 
 // ---- k-split ("stream-K") schedule ------------------------------------------------------------------------------
@@ -124,6 +125,113 @@ __device__ __forceinline__ bool sk_wait_flag(const unsigned* flag, int lane) {
     if (!ok) atomicMax(&g_dev_error, kDevErrGemmSplitTimeout);
   }
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// ---- dynamic tile schedule ---------------------------------------------------------------------------------------
+// A persistent grid that walks tiles with a fixed stride (worker w takes tiles w, w + W, ...) assumes all W workers
+// run at once.  When another kernel holds some SMs (the gradient all-reduce beside the backward pass) the CTAs that
+// find no SM start only when others have finished, and then still compute their whole share: the matmul takes two
+// rounds instead of one and a fraction.  Here a worker's first tile is its own index and every further tile comes
+// from a global counter, so the tiles go to whichever workers are running; a worker that starts late finds the
+// counter exhausted and leaves.  Every tile is still computed whole by one worker in the same k order, so the
+// results are bit-identical to the fixed-stride walk.
+// The producer thread draws the tile indices and hands them to the other roles of its CTA (and, in the two-SM
+// kernel, of the peer CTA) through a ring of kSchedDepth entries in shared memory guarded by mbarriers; -1 ends the
+// walk.  The counter of a launch is g_tile_next[slot]; the last worker to finish (g_tile_done[slot]) puts both back
+// to zero for the next launch that uses the slot.
+constexpr int kSchedDepth = 4;
+__device__ unsigned g_tile_next[kSkSlots];
+__device__ unsigned g_tile_done[kSkSlots];
+
+struct SchedSmem {
+  uint64_t full[kSchedDepth];          // an entry has been published (1 arrival: the scheduling thread)
+  uint64_t empty[kSchedDepth];         // this CTA's consumers have read it
+  uint64_t empty_peer[kSchedDepth];    // two-SM kernel, leader only: the peer CTA's consumers have read theirs
+  int ring[kSchedDepth];
+};
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, unsigned parity) {   // acquire at cluster scope
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(g_mbar_suspend_ns) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, unsigned parity, unsigned err_code) {
+  for (unsigned it = 0; it < kMbarPolls; ++it)
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+  atomicMax(&g_dev_error, err_code);
+  return false;
+}
+// Consumer side of the ring for one thread (n: entries read so far).  Returns the tile, -1 at the end of the walk, -2
+// when the wait ran out.  `arrive`: this thread reports the read (one thread per consuming warp does).
+// CLUSTER: the entry was written by the other CTA of the pair, and the read is reported to that CTA's barrier.
+template <bool CLUSTER>
+__device__ __forceinline__ int sched_take(SchedSmem* sm, unsigned& n, bool arrive, uint32_t leader_empty_peer0) {
+  const int sl = (int)(n % kSchedDepth);
+  const unsigned ph = (n / kSchedDepth) & 1u;
+  const bool ok = CLUSTER ? mbar_wait_bounded_cluster(sm->full + sl, ph, kDevErrGemmTimeout)
+                          : mbar_wait_bounded(sm->full + sl, ph, kDevErrGemmTimeout);
+  if (!ok) return -2;
+  const int tile = *reinterpret_cast<volatile int*>(&sm->ring[sl]);
+  if (arrive) {
+    if (CLUSTER) mbar_arrive_cluster(leader_empty_peer0 + (uint32_t)sl * 8u);
+    else mbar_arrive(sm->empty + sl);
+  }
+  ++n;
+  return tile;
+}
+// The same for a whole warp (all lanes get the tile; lane 0 reports the read after every lane has it).
+template <bool CLUSTER>
+__device__ __forceinline__ int sched_take_warp(SchedSmem* sm, unsigned& n, int lane, uint32_t leader_empty_peer0) {
+  const int sl = (int)(n % kSchedDepth);
+  const unsigned ph = (n / kSchedDepth) & 1u;
+  const bool ok = CLUSTER ? mbar_wait_bounded_cluster(sm->full + sl, ph, kDevErrGemmTimeout)
+                          : mbar_wait_bounded(sm->full + sl, ph, kDevErrGemmTimeout);
+  if (!__all_sync(0xffffffffu, ok)) return -2;
+  const int tile = *reinterpret_cast<volatile int*>(&sm->ring[sl]);
+  __syncwarp();
+  if (lane == 0) {
+    if (CLUSTER) mbar_arrive_cluster(leader_empty_peer0 + (uint32_t)sl * 8u);
+    else mbar_arrive(sm->empty + sl);
+  }
+  ++n;
+  return tile;
+}
+// Scheduling thread: publish `tile` (or -1) as entry n.  PAIR: also into the peer CTA's ring.
+template <bool PAIR>
+__device__ __forceinline__ bool sched_publish(SchedSmem* sm, unsigned& n, int tile) {
+  const int sl = (int)(n % kSchedDepth);
+  const unsigned ph = (n / kSchedDepth) & 1u;
+  if (!mbar_wait_bounded(sm->empty + sl, ph ^ 1u, kDevErrGemmTimeout)) return false;
+  if (PAIR && !mbar_wait_bounded_cluster(sm->empty_peer + sl, ph ^ 1u, kDevErrGemmTimeout)) return false;
+  sm->ring[sl] = tile;
+  mbar_arrive(sm->full + sl);                                  // release: the entry is visible to who sees the arrival
+  if (PAIR) {
+    uint32_t peer_ring, peer_full;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_ring) : "r"(smem_u32(&sm->ring[sl])), "r"(1u));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_full) : "r"(smem_u32(sm->full + sl)), "r"(1u));
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_ring), "r"((uint32_t)tile) : "memory");
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_full) : "memory");
+  }
+  ++n;
+  return true;
+}
+// Next tile for the scheduling thread: workers' first tiles are their own indices, the rest come from the counter.
+__device__ __forceinline__ long long sched_draw(int slot, long long nworkers, long long total) {
+  const long long t = nworkers + (long long)atomicAdd(&g_tile_next[slot], 1u);
+  return t < total ? t : -1;
+}
+// Called once per worker by its scheduling thread when it is done drawing.
+__device__ __forceinline__ void sched_retire(int slot, long long nworkers) {
+  __threadfence();
+  if (atomicAdd(&g_tile_done[slot], 1u) == (unsigned)(nworkers - 1)) {
+    __threadfence();
+    g_tile_next[slot] = 0;
+    g_tile_done[slot] = 0;
+  }
 }
 
 // What the epilogue does with one accumulator (two-SM kernel).
@@ -362,6 +470,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  SchedSmem* sched = reinterpret_cast<SchedSmem*>(tmem_slot + 4);
   // epilogue staging: per epilogue warp two [32 rows][64 cols] buffers in the 128-byte-swizzled layout of a
   // TMA box (4 KB each), 1024-byte aligned
   unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
@@ -370,6 +479,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+    // schedule ring: read by the MMA thread and by the four epilogue warps
+    for (int i = 0; i < kSchedDepth; ++i) { mbar_init(sched->full + i, 1); mbar_init(sched->empty + i, 5); mbar_init(sched->empty_peer + i, 5); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -387,18 +498,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const long long total = tiles_per_block * p.nb_inner * p.nb_outer;
 
   if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer (and, with the dynamic schedule, the thread that draws the tiles) ----------------
     int s = 0; unsigned ph = 0;
-    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    auto produce = [&](long long tile) -> bool {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int aj = p.a_j ? bj : 0, ai = p.a_i ? bi : 0, bjj = p.b_j ? bj : 0, bii = p.b_i ? bi : 0;
-      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
+      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) return true;
       int kb0, kb1;
       k_block_range(p, tm * kBM, kBM, nkb, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) return false;
         unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
         mbar_expect_tx(full + s, STAGE_BYTES);
@@ -414,28 +525,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
+      return true;
+    };
+    if (p.dyn) {
+      unsigned sn = 0;
+      long long tile = blockIdx.x;                       // the grid never exceeds the tile count
+      for (;;) {
+        if (!sched_publish<false>(sched, sn, (int)tile)) break;
+        if (tile < 0) break;
+        const long long nxt = sched_draw(p.sk_slot, gridDim.x, total);     // in flight while this tile's loads are issued
+        if (!produce(tile)) break;
+        tile = nxt;
+      }
+    } else {
+      for (long long tile = blockIdx.x; tile < total; tile += gridDim.x)
+        if (!produce(tile)) break;
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
     int s = 0; unsigned ph = 0;
     long long local = 0;
-    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    auto mma_tile = [&](long long tile) -> bool {
       int kb0 = 0, kb1 = nkb;
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
       if (p.tri) {
-        if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
+        if (tile_skipped(p, tm * kBM, kBM, tn * BN)) return true;
         k_block_range(p, tm * kBM, kBM, nkb, kb0, kb1);
       }
       // the last column tile multiplies only the columns that exist (rounded up to the MMA's granularity of 16)
       const int nvalid = p.N - tn * BN;
       const uint32_t idesc = nvalid >= BN ? p.idesc : idesc_with_n(p.idesc, (nvalid + 15) & ~15);
       const int acc = (int)(local & 1);
-      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
+      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) return false;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
+        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) return false;
         tc_fence_after();
         const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
@@ -449,27 +575,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_commit(tfull + acc);                 // accumulator complete
       ++local;
+      return true;
+    };
+    if (p.dyn) {
+      unsigned sn = 0;
+      for (;;) {
+        const int tile = sched_take<false>(sched, sn, true, 0);
+        if (tile < 0 || !mma_tile(tile)) break;
+      }
+    } else {
+      for (long long tile = blockIdx.x; tile < total; tile += gridDim.x)
+        if (!mma_tile(tile)) break;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue ----------------
     const int q = warp & 3;                   // TMEM lane quarter this warp may read
     long long local = 0;
-    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    auto epi_tile = [&](long long tile) -> bool {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
-      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) continue;
+      if (tile_skipped(p, tm * kBM, kBM, tn * BN)) return true;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
       // all 32 lanes leave together: a wait that ran out on some lanes only must not split the warp before the
       // warp-wide tcgen05.ld of the epilogue
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) goto done;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) return false;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kBM + q * 32, tn, bj, bi, q, lane,
                            cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
       ++local;
+      return true;
+    };
+    if (p.dyn) {
+      unsigned sn = 0;
+      for (;;) {
+        const int tile = sched_take_warp<false>(sched, sn, lane, 0);
+        if (tile < 0 || !epi_tile(tile)) break;
+      }
+    } else {
+      for (long long tile = blockIdx.x; tile < total; tile += gridDim.x)
+        if (!epi_tile(tile)) break;
     }
   }
-done:
+  if (p.dyn && warp == 0 && lane == 0) sched_retire(p.sk_slot, gridDim.x);     // on every path, or the counter stays dirty
   if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
@@ -543,6 +691,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  SchedSmem* sched = reinterpret_cast<SchedSmem*>(tmem_slot + 4);
   unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -551,6 +700,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 8); }
+    // schedule ring: in the leader read by the MMA thread and four epilogue warps (empty), in the peer by the producer
+    // thread and four epilogue warps, which report to the leader's empty_peer
+    for (int i = 0; i < kSchedDepth; ++i) { mbar_init(sched->full + i, 1); mbar_init(sched->empty + i, 5); mbar_init(sched->empty_peer + i, 5); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -568,13 +720,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const long long tiles_per_block = (long long)p.tiles_m * p.tiles_n;
   const long long total = tiles_per_block * p.nb_inner * p.nb_outer;
 
+  // the leader's barriers on which the peer CTA's consumers report their reads of the schedule ring
+  const uint32_t leader_empty_peer0 = map_to_rank(smem_u32(sched->empty_peer), 0);
+
   if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer (both CTAs) ----------------
+    // ---------------- TMA producer (both CTAs); the leader's also draws the tiles of the dynamic schedule ----------------
     int s = 0; unsigned ph = 0;
     const int row_off = (int)rank * kBM;
-    WorkIter it; WorkItem wi;
-    it.init(p, pair, npairs, total, nkb);
-    while (it.next(wi)) {
+    auto produce = [&](const WorkItem& wi) -> bool {
       int blk, tm, tn;
       decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
@@ -583,11 +736,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // (the first 64 of the box it loads), so the CTAs' boxes start 64 rows apart instead of 128
       const int hb = (p.N - tn * BN <= HB) ? HB / 2 : HB;
       const int m0 = tm * kPairBM + row_off, n0 = tn * BN + (int)rank * hb;
-      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
+      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) return true;
       int kb0 = wi.kb0, kb1 = wi.kb1;
       if (p.tri) k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+        if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) return false;
         unsigned char* sa = tiles + (size_t)s * STAGE_BYTES;
         unsigned char* sb = sa + A_BYTES;
         const uint32_t fb = map_to_rank(smem_u32(full + s), 0);
@@ -604,33 +757,60 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
+      return true;
+    };
+    bool ok = true;
+    WorkItem wi;
+    if (p.dyn) {
+      unsigned sn = 0;
+      wi.kb0 = 0; wi.kb1 = nkb; wi.kind = kItemFull;
+      if (rank == 0) {
+        long long tile = pair;                             // the grid never has more pairs than tiles
+        for (;;) {
+          if (!sched_publish<true>(sched, sn, (int)tile)) { ok = false; break; }
+          if (tile < 0) break;
+          const long long nxt = sched_draw(p.sk_slot, npairs, total);    // in flight while this tile's loads are issued
+          wi.tile = tile;
+          if (!produce(wi)) { ok = false; break; }
+          tile = nxt;
+        }
+      } else {
+        for (;;) {
+          const int tile = sched_take<true>(sched, sn, true, leader_empty_peer0);
+          if (tile < 0) { ok = tile == -1; break; }
+          wi.tile = tile;
+          if (!produce(wi)) { ok = false; break; }
+        }
+      }
+    } else {
+      WorkIter it;
+      it.init(p, pair, npairs, total, nkb);
+      while (ok && it.next(wi)) ok = produce(wi);
     }
     // the leader's last commits still arrive on this CTA's empty barriers: wait for them before leaving
-    for (int i = 0; i < STAGES; ++i) {
-      if (!mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout)) goto done;
+    for (int i = 0; ok && i < STAGES; ++i) {
+      ok = mbar_wait_bounded(empty + s, ph ^ 1, kDevErrGemmTimeout);
       if (++s == STAGES) { s = 0; ph ^= 1; }
     }
   } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---------------- MMA issuer (leader CTA) ----------------
     int s = 0; unsigned ph = 0;
     long long local = 0;
-    WorkIter it; WorkItem wi;
-    it.init(p, pair, npairs, total, nkb);
-    while (it.next(wi)) {
+    auto mma_item = [&](const WorkItem& wi) -> bool {
       int kb0 = wi.kb0, kb1 = wi.kb1;
       int blk, tm, tn;
       decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
       if (p.tri) {
-        if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
+        if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) return true;
         k_block_range(p, tm * kPairBM, kPairBM, nkb, kb0, kb1);
       }
       const uint32_t idesc = (p.N - tn * BN <= HB) ? idesc_with_n(p.idesc, HB) : p.idesc;      // see the producer
       const int acc = (int)(local & 1);
-      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) goto done;
+      if (!mbar_wait_bounded(tempty + acc, (unsigned)((local >> 1) & 1) ^ 1, kDevErrGemmTimeout)) return false;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) goto done;
+        if (!mbar_wait_bounded(full + s, ph, kDevErrGemmTimeout)) return false;
         tc_fence_after();
         const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
@@ -644,17 +824,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_commit_pair(tfull + acc);
       ++local;
+      return true;
+    };
+    WorkItem wi;
+    if (p.dyn) {
+      unsigned sn = 0;
+      wi.kb0 = 0; wi.kb1 = nkb; wi.kind = kItemFull;
+      for (;;) {
+        const int tile = sched_take<false>(sched, sn, true, 0);
+        if (tile < 0) break;
+        wi.tile = tile;
+        if (!mma_item(wi)) break;
+      }
+    } else {
+      WorkIter it;
+      it.init(p, pair, npairs, total, nkb);
+      while (it.next(wi))
+        if (!mma_item(wi)) break;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
     const int q = warp & 3;
     long long local = 0;
-    WorkIter it; WorkItem wi;
-    it.init(p, pair, npairs, total, nkb);
-    while (it.next(wi)) {
+    auto epi_item = [&](const WorkItem& wi) -> bool {
       int blk, tm, tn;
       decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
-      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) continue;
+      if (tile_skipped(p, tm * kPairBM, kPairBM, tn * BN)) return true;
       const int bi = blk / p.nb_inner, bj = blk - bi * p.nb_inner;
       const int acc = (int)(local & 1);
       SkEpi sk{};
@@ -671,14 +866,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         sk.part0 = p.sk_part + ((size_t)(pair + 1) * 2 + rank) * kSkPartFloats;
         sk.flags0 = &g_sk_flags[p.sk_slot][pair + 1][rank][0];
       }
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) goto done;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) return false;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kPairBM + (int)rank * kBM + q * 32, tn, bj, bi, q, lane,
                            cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0), sk);
       ++local;
+      return true;
+    };
+    WorkItem wi;
+    if (p.dyn) {
+      unsigned sn = 0;
+      wi.kb0 = 0; wi.kb1 = nkb; wi.kind = kItemFull;
+      for (;;) {
+        const int tile = rank == 0 ? sched_take_warp<false>(sched, sn, lane, 0) : sched_take_warp<true>(sched, sn, lane, leader_empty_peer0);
+        if (tile < 0) break;
+        wi.tile = tile;
+        if (!epi_item(wi)) break;
+      }
+    } else {
+      WorkIter it;
+      it.init(p, pair, npairs, total, nkb);
+      while (it.next(wi))
+        if (!epi_item(wi)) break;
     }
   }
-done:
+  if (p.dyn && warp == 0 && lane == 0 && rank == 0) sched_retire(p.sk_slot, npairs);   // on every path, or the counter stays dirty
   if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
@@ -762,6 +974,7 @@ int g_gemm_pair = 1;  // 1: 256-wide tiles may run as two-SM (cta_group::2) 256 
 // slower with it (50.8 -> 53.6 ms at M = 2048): these matmuls are power-limited, the SMs a partly filled last wave
 // leaves idle let the others clock higher, and the partial sums displace 19 MB of the L2 per matmul.
 int g_gemm_split = 0;
+int g_gemm_dynamic = 1;  // 1: tiles beyond a worker's first are drawn from a global counter (see "dynamic tile schedule")
 
 // Workers and k-split tiles for `tiles` two-SM tiles of `nkb` k-blocks on at most `max_workers` SM pairs.  Splitting
 // pays when the last wave of whole tiles would leave more than about 5 % of the grid idle.
@@ -914,6 +1127,9 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
   // cannot be fully resident would otherwise run its last CTAs as a second wave
   const int grid = (int)(total < sms ? total : sms);
   p.sk_tiles = 0; p.sk_units = 0; p.sk_part = nullptr; p.sk_slot = 0;
+  static std::atomic<unsigned> launch_seq{0};       // flag / counter slot of a launch: consecutive launches use different ones
+  p.dyn = (g_gemm_dynamic && total < 0x7fffffffLL) ? 1 : 0;
+  if (p.dyn) p.sk_slot = (int)(launch_seq.fetch_add(1) % kSkSlots);
   const int stages = BN >= 192 ? 4 : 6;
   const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 1024 /*barriers*/ + 4 * 8192;
   T* C = reinterpret_cast<T*>(c);
@@ -921,12 +1137,12 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
     long long pairs = total < sms / 2 ? total : sms / 2;
     if (split_ok) {
       const SplitPlan sp = plan_split(total, nkb_host, pair_workers, p.tiles_n, p.group_m, M, N, K);
-      if (sp.sk_tiles) {
-        static std::atomic<unsigned> seq{0};
+      if (sp.sk_tiles) {                                // the k-split walk is static: it replaces the dynamic one
         pairs = sp.workers;
         p.sk_tiles = sp.sk_tiles; p.sk_units = sp.sk_tiles * nkb_host;
         p.sk_part = reinterpret_cast<float*>(ws + split_off);
-        p.sk_slot = (int)(seq.fetch_add(1) % kSkSlots);
+        if (!p.dyn) p.sk_slot = (int)(launch_seq.fetch_add(1) % kSkSlots);
+        p.dyn = 0;
       }
     }
 #define CB_GEMM2(AM_, BM_)                                                                             \

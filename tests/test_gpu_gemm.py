@@ -122,6 +122,50 @@ def test_gemm_pair_tiles_match_single_sm(cuda):
         assert torch.equal(o, t)
 
 
+def test_dynamic_schedule_gives_the_same_bits(cuda):
+    """Tiles drawn from the global counter (the default) or walked with a fixed stride: every tile is computed whole by
+    one CTA (pair) in the same k order either way, so the results are bit-identical.  Dense on the two-SM and the
+    one-SM kernel, several tiles per CTA, a grid smaller than the machine, block form with and without the causal
+    hints; and the counters are left clean (the same calls repeat with the same result)."""
+    L = capi.lib()
+    x, w = dev(R.normal(71, (2304, 1024), np.float16)), dev(R.normal(72, (3200, 1024), np.float16, 0.05))
+    q, k = dev(R.normal(73, (2, 512, 3, 128), np.float16)), dev(R.normal(74, (2, 512, 3, 128), np.float16))
+    pl = torch.tril(torch.ones(512, 512, device="cuda", dtype=torch.float16))[None, :, None, :].expand(2, 512, 3, 512).contiguous()
+
+    def run_all():
+        out = [ops.gemm(x, w, False, True), ops.gemm(x, w[:, :1024].contiguous(), False, True, beta=0.0),
+               ops.block_gemm(q, k, False, True, alpha=0.1), ops.block_gemm(q, k, False, True, alpha=0.1, tri=capi.TRI_C_LOWER),
+               ops.block_gemm(pl, k, False, False, tri=capi.TRI_A_LOWER), ops.block_gemm(pl, k, True, False, tri=capi.TRI_A_UPPER)]
+        for knob, val in ((b"gemm_pair", 0), (b"gemm_sms", 100), (b"gemm_bn", 128)):
+            L.cacti_b200_tune(knob, val)
+            try:
+                out.append(ops.gemm(x, w, False, True))
+                out.append(ops.block_gemm(q, k, False, True, alpha=0.1))
+            finally:
+                L.cacti_b200_tune(knob, 1 if knob == b"gemm_pair" else 0)
+        return out
+
+    dyn1 = run_all()
+    dyn2 = run_all()
+    assert L.cacti_b200_tune(b"gemm_dynamic", 0) == capi.OK
+    try:
+        fixed = run_all()
+    finally:
+        L.cacti_b200_tune(b"gemm_dynamic", 1)
+    tri_c = 3                                       # C_LOWER leaves tiles above the diagonal unwritten: compare what is specified
+    low = torch.tril(torch.ones(512, 512, device="cuda", dtype=torch.bool))[None, :, None, :]
+    for i, (a, b, c) in enumerate(zip(dyn1, dyn2, fixed)):
+        if i == tri_c:
+            a, b, c = (torch.where(low, t, 0) for t in (a, b, c))
+        assert torch.equal(a, c), i
+        assert torch.equal(a, b), i
+    assert_close(host(dyn1[0]), R.ref_gemm(host(x), host(w), False, True), "float16", "dynamic schedule vs oracle", floor_frac=1.0)
+    import ctypes as C
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+
+
 @pytest.fixture
 def k_split():
     """Turn the k-split schedule of the two-SM kernel on for one test (it is off by default)."""
