@@ -320,6 +320,9 @@ def train_step_leg(torch, dist, ctl, rank, world, dev, steps):
     margin = int(os.environ.get("CACTI_B200_GEMM_SM_MARGIN", "0")) if world > 1 else 0
     if margin:
         ops.lib().cacti_b200_tune(b"gemm_sms", 148 - margin)
+    fixed_walk = os.environ.get("CACTI_B200_FIXED_WALK", "0") == "1"     # A/B: the matmuls' fixed-stride tile walk
+    if fixed_walk:
+        ops.lib().cacti_b200_tune(b"gemm_dynamic", 0)
     g = torch.Generator(device=dev).manual_seed(1)
     tok_all = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g)
     tgt_all = torch.randint(0, cfg.vocab, (n_seq * cfg.seq,), device=dev, dtype=torch.int32, generator=g)
@@ -385,6 +388,8 @@ def train_step_leg(torch, dist, ctl, rank, world, dev, steps):
     ms, loss, launch = timed(True, reps)
     if margin:
         ops.lib().cacti_b200_tune(b"gemm_sms", 0)
+    if fixed_walk:
+        ops.lib().cacti_b200_tune(b"gemm_dynamic", 1)
     # f64 sum and sum of magnitudes of three gradients after the exchange (torch reductions: verification, not the path)
     checks = {}
     for name, t in (("lm_head", grads["lm_head"]), ("layers.0.q", grads["layers"][0]["q"]), ("embed", grads["embed"])):
@@ -397,7 +402,7 @@ def train_step_leg(torch, dist, ctl, rank, world, dev, steps):
            "h2d_bytes_per_step": 2 * count * cfg.seq * 4, "d2h_bytes_per_step": 4, "grad_checksums": checks,
            "note": "no optimizer step (the optimizer thunks are outside this path); gradients of all parameters are produced and all-reduced"}
     if compute_ms is not None:
-        out.update({"compute_ms": compute_ms, "exposed_comm_ms": ms - compute_ms, "gemm_sm_margin": margin,
+        out.update({"compute_ms": compute_ms, "exposed_comm_ms": ms - compute_ms, "gemm_sm_margin": margin, "matmul_tile_walk": "fixed stride" if fixed_walk else "dynamic",
                     "exchange": {"collective": "ncclAllReduce(sum) per bucket via torch.distributed", "buckets": len(buckets),
                                  "bytes_per_rank": sum(b.numel() * b.element_size() for b in buckets),
                                  "env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_")}}})

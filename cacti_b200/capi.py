@@ -62,6 +62,7 @@ SIGNATURES = {
                                                _i64, _i64, _int, _p, _sz, _st]),
     "cacti_b200_block_pad": (_int, [_p, _p, _i64, _i64, _i64, _i64, _i64, _int, _st]),
     "cacti_b200_attention_fwd": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _st]),
+    "cacti_b200_attention_bwd": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _st]),
     "cacti_b200_attention_bwd_prep": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _st]),
     "cacti_b200_gemm_strided_batched_tri": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int,
                                                    C.POINTER(_f32), C.POINTER(_f32), _i64, _i64, _i64, _i64, _i64, _i64,

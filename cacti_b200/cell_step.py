@@ -37,8 +37,10 @@ class CellTrainStep:
     moved to the host).  Parameters and gradients are stable cells (they survive the step; spilled rather than dropped),
     everything else lives for part of one step."""
 
-    def __init__(self, ctx: H.Ctx, cfg, weights, batch: int, loss_tokens: int | None = None):
+    def __init__(self, ctx: H.Ctx, cfg, weights, batch: int, loss_tokens: int | None = None, fused_bwd: bool = False):
         self.ctx, self.L, self.h, self.cfg, self.B = ctx, ctx.L, ctx.h, cfg, batch
+        # False (llama_step's default): P and dS are cells, three block-matmul thunks; True: one attention_bwd thunk
+        self.fused_bwd = fused_bwd
         self.T = batch * cfg.seq
         self.loss_tokens = loss_tokens or self.T
         assert cfg.seq % 128 == 0 and cfg.head_dim <= 128 and cfg.head_dim % 4 == 0, "the fused attention path needs these"
@@ -174,16 +176,20 @@ class CellTrainStep:
             dctxp = self.new(T, H_, 128)
             self.call("block_pad", APPLY, dctxp, dctx, B, S, H_, hd, 128, R_16F)
             self.free(dctx)
-            p, ds = self.new(B, S, H_, S), self.new(B, S, H_, S)
-            self.call("attention_bwd_prep", APPLY, p, ds, qp, kp, vp, dctxp, ctxc, stats, B, S, H_, hd, alpha, R_16F)
-            self.free(ctxc, stats, vp)
             dv, dq, dk = self.new(T, D), self.new(T, D), self.new(T, D)
-            # P^T dO, dS K, dS^T Q on the reference's block layout; the right-hand operands are the 128-wide padded copies
-            self.call("block_matmul", APPLY, dv, p, dctxp, B, H_, S, hd, S, S, 128, True, False, 1.0, TRI_A_UPPER, 0, OPERAND_B_PADDED, R_16F)
-            self.free(p, dctxp)
-            self.call("block_matmul", APPLY, dq, ds, kp, B, H_, S, hd, S, S, 128, False, False, alpha, TRI_A_LOWER, 0, OPERAND_B_PADDED, R_16F)
-            self.call("block_matmul", APPLY, dk, ds, qp, B, H_, S, hd, S, S, 128, True, False, alpha, TRI_A_UPPER, 0, OPERAND_B_PADDED, R_16F)
-            self.free(ds, qp, kp)
+            if self.fused_bwd:
+                self.call("attention_bwd", APPLY, dq, dk, dv, qp, kp, vp, dctxp, ctxc, stats, B, S, H_, hd, alpha, R_16F)
+                self.free(ctxc, stats, vp, dctxp, qp, kp)
+            else:
+                p, ds = self.new(B, S, H_, S), self.new(B, S, H_, S)
+                self.call("attention_bwd_prep", APPLY, p, ds, qp, kp, vp, dctxp, ctxc, stats, B, S, H_, hd, alpha, R_16F)
+                self.free(ctxc, stats, vp)
+                # P^T dO, dS K, dS^T Q on the reference's block layout; the right-hand operands are the 128-wide padded copies
+                self.call("block_matmul", APPLY, dv, p, dctxp, B, H_, S, hd, S, S, 128, True, False, 1.0, TRI_A_UPPER, 0, OPERAND_B_PADDED, R_16F)
+                self.free(p, dctxp)
+                self.call("block_matmul", APPLY, dq, ds, kp, B, H_, S, hd, S, S, 128, False, False, alpha, TRI_A_LOWER, 0, OPERAND_B_PADDED, R_16F)
+                self.call("block_matmul", APPLY, dk, ds, qp, B, H_, S, hd, S, S, 128, True, False, alpha, TRI_A_UPPER, 0, OPERAND_B_PADDED, R_16F)
+                self.free(ds, qp, kp)
             unrot = []
             for d in (dq, dk):
                 t = self.new(T, D)

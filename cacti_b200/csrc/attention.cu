@@ -513,7 +513,6 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const int r = qq * 32 + lane;
     const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
     constexpr float kLog2e = 1.4426950408889634f;
-    const long long row = (long long)b * p.seq + q0 + r;
     const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
     // y = exp(s - m) / l as one exponential: 2^(s log2e - (m log2e + log2 l))
     const float mb = __fmaf_rn(st[0], kLog2e, __log2f(st[1]));
@@ -594,6 +593,488 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   }
 done:
   if (warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- backward, fully fused: dQ, dK, dV without P or dS in HBM ------------------------------------------------------
+// attention_bwd_prep writes P and dS (2 x 2 bytes per unmasked score) for three block matmuls to read back.  The two
+// kernels below keep them on chip instead.  Both rebuild S = Q K^T and dP = dO V^T per tile on the tensor cores and form
+//   y = exp(s - m) / l,   P = T(y),   dS = T(y * T(dP) - c * y)       (s, dP rounded to the storage type; c = dO . O)
+// exactly as attention_bwd_prep does (same rounding points), stage the 16-bit P / dS in shared memory in the layout
+// of an MMA operand, and contract them at once:
+//   attention_bwd_dq_kernel   one CTA per 128 query rows, over the key tiles at or before it:  dQ  = alpha dS K
+//   attention_bwd_dkv_kernel  one CTA per 128 keys, over the query rows at or after it:        dV  = P^T dO,
+//                                                                                              dK  = alpha dS^T Q
+// Each output element is accumulated by one CTA in a fixed order (no floating-point atomics; dQ is not scattered from
+// the key-tile kernel but recomputed per query tile, which costs S and dP a second time).  The f32 accumulators of the
+// products live in tensor memory for the whole CTA; their operands differ from the block matmuls' only in that P and
+// dS never left the SM, so the results agree with the three hinted block matmuls over attention_bwd_prep's output up
+// to the summation order inside the tensor cores.
+//
+// Work is cut in units of 128 x 64 scores so that two softmax groups (4 warps each, one thread per TMEM lane) alternate
+// and 512 tensor-memory columns hold everything: per group S (64) and dP (64), plus the 128-column accumulators (one in
+// the dQ kernel, two in the dK / dV kernel).
+constexpr int kBwdCols = 64;                                  // scores per TMEM lane and unit
+constexpr uint32_t kUnitBytes = kAttnRows * kBwdCols * 2;     // 16 KB: a [128][64] 16-bit operand tile (128-byte rows)
+
+// K-major operand with 128-byte rows stored as boxes of `box_bytes` (one per 64 contraction elements): step k16 of 16
+__device__ __forceinline__ uint64_t kmajor_box_desc(uint32_t base, int k16, uint32_t box_bytes) {
+  return make_desc(base + (uint32_t)(k16 >> 2) * box_bytes + (uint32_t)(k16 & 3) * 32u, 1, 64);
+}
+// The same stored tile read as an MN-major B operand [64 contraction rows][128 columns]: rows 128 bytes apart, the
+// second 64 columns one box further (leading-dimension offset), 16 rows per step
+__device__ __forceinline__ uint64_t mnmajor_box_desc(uint32_t base, int k16, uint32_t box_bytes) {
+  return make_desc(base + (uint32_t)k16 * 2048u, box_bytes >> 4, 64);
+}
+
+// One thread's 32 scores of a unit: y and dS from the accumulators sv (S) and gv (dP).  col0: key (dQ kernel) or query
+// (dK / dV kernel) index of element 0 relative to the thread's own row index `self`; masked when key > query.
+template <typename T, bool WANT_P, bool ROW_IS_QUERY>
+__device__ __forceinline__ void bwd_unit_math(const uint32_t (&sv)[32], const uint32_t (&gv)[32], float alpha, const float2* colstat,
+                                              float mb_row, float c_row, bool diag, int col0, int self,
+                                              uint4 (&pc)[4], uint4 (&dc)[4]) {
+  constexpr float kLog2e = 1.4426950408889634f;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t pw[4], dw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = g * 8 + i * 2;
+      const float2 s2 = rounded_scores<T>(alpha, sv[idx], sv[idx + 1]);
+      const float2 g2 = rounded_pair<T>(gv[idx], gv[idx + 1]);
+      // statistics belong to the query: the thread's own row, or the column's (shared memory: one 16-byte broadcast
+      // load brings (mb, c) of two neighbouring queries)
+      float mb0 = mb_row, mb1 = mb_row, c0 = c_row, c1 = c_row;
+      if (!ROW_IS_QUERY) {
+        const float4 st2 = *reinterpret_cast<const float4*>(colstat + idx);
+        mb0 = st2.x; c0 = st2.y; mb1 = st2.z; c1 = st2.w;
+      }
+      float y0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb0));
+      float y1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb1));
+      if (diag) {
+        const int c = col0 + idx;
+        // ROW_IS_QUERY: column = key, masked when key > query (self); else column = query, masked when key (self) > query
+        if (ROW_IS_QUERY ? (c > self) : (self > c)) y0 = 0.f;
+        if (ROW_IS_QUERY ? (c + 1 > self) : (self > c + 1)) y1 = 0.f;
+      }
+      if (WANT_P) pw[i] = pack2<T>(y0, y1);
+      dw[i] = pack2<T>(__fmaf_rn(y0, g2.x, -__fmul_rn(c0, y0)), __fmaf_rn(y1, g2.y, -__fmul_rn(c1, y1)));
+    }
+    if (WANT_P) pc[g] = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+    dc[g] = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+  }
+}
+
+// ---- dQ: one CTA per (batch, head, 128 query rows) -------------------------------------------------------------------
+// warp 0 producer (Q and dO once, then K and V tiles through a two-slot ring), warp 1 MMA issuer, warps 2..9 two
+// softmax groups; group g works on keys [64 g, 64 g + 64) of every 128-key tile.
+// Tensor memory: group g: S at columns 128 g, dP at 128 g + 64; dQ at 256.
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                        T* __restrict__ dq, const float* __restrict__ stats, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = base;                        // 32 KB
+  unsigned char* sdO = sQ + kTileBytes;            // 32 KB
+  unsigned char* sK = sdO + kTileBytes;            // 2 x 32 KB
+  unsigned char* sV = sK + 2 * kTileBytes;         // 2 x 32 KB
+  unsigned char* sDS = sV + 2 * kTileBytes;        // 2 x 16 KB, one per group: dS [128 queries][64 keys], K-major
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * kUnitBytes);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* kv_full = bars + 1;                    // 2
+  uint64_t* kv_empty = bars + 3;                   // 2
+  uint64_t* t_full = bars + 5;                     // 2 (per group): S and dP of the group's unit are complete
+  uint64_t* t_empty = bars + 7;                    // 2: the group has them in registers
+  uint64_t* ds_full = bars + 9;                    // 2: the group's dS is staged
+  uint64_t* ds_empty = bars + 11;                  // 2: the dQ product has read it
+  uint64_t* acc_full = bars + 13;                  // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int nq = p.seq / kAttnRows;                // launch order as in the forward kernel
+  const int b = (int)(blockIdx.x / (nq * p.heads));
+  const int rem = (int)(blockIdx.x % (nq * p.heads));
+  const int qi = nq - 1 - rem / p.heads;
+  const int h = rem % p.heads;
+  const int ntiles = qi + 1;
+  const int q0 = qi * kAttnRows;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(acc_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1);
+      mbar_init(t_full + s, 1); mbar_init(t_empty + s, 4); mbar_init(ds_full + s, 4); mbar_init(ds_empty + s, 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tAcc = tmem_base + 256u;
+
+  if (warp == 0 && lane == 0) {
+    mbar_expect_tx(q_full, 2 * kTileBytes);
+    tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+    tma_load_4d(sQ + 16384, &tmQ, q_full, 64, q0, h, b);
+    tma_load_4d(sdO, &tmdO, q_full, 0, q0, h, b);
+    tma_load_4d(sdO + 16384, &tmdO, q_full, 64, q0, h, b);
+    for (int j = 0; j < ntiles; ++j) {
+      const int sl = j & 1;
+      if (!mbar_wait_bounded(kv_empty + sl, (unsigned)((j >> 1) & 1) ^ 1, kDevErrAttnTimeout)) break;
+      unsigned char* dk = sK + (size_t)sl * kTileBytes;
+      unsigned char* dv = sV + (size_t)sl * kTileBytes;
+      mbar_expect_tx(kv_full + sl, 2 * kTileBytes);
+      tma_load_4d(dk, &tmK, kv_full + sl, 0, j * kAttnRows, h, b);
+      tma_load_4d(dk + 16384, &tmK, kv_full + sl, 64, j * kAttnRows, h, b);
+      tma_load_4d(dv, &tmV, kv_full + sl, 0, j * kAttnRows, h, b);
+      tma_load_4d(dv + 16384, &tmV, kv_full + sl, 64, j * kAttnRows, h, b);
+    }
+  } else if (warp == 1 && lane == 0) {
+    bool ok = mbar_wait_bounded(q_full, 0, kDevErrAttnTimeout);
+    const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
+    // dQ += dS_g K[64 g ..] of tile jj, for both groups; then the tile's K / V slot is free
+    auto finish = [&](int jj) -> bool {
+      const int sl = jj & 1;
+      const uint32_t aK = smem_u32(sK + (size_t)sl * kTileBytes);
+      for (int g = 0; g < 2; ++g) {
+        if (!mbar_wait_bounded(ds_full + g, (unsigned)(jj & 1), kDevErrAttnTimeout)) return false;
+        tc_fence_after();
+        const uint32_t aDS = smem_u32(sDS + (size_t)g * kUnitBytes);
+#pragma unroll
+        for (int k16 = 0; k16 < kBwdCols / 16; ++k16)
+          tc_mma_f16(tAcc, kmajor_box_desc(aDS, k16, kUnitBytes), mnmajor_box_desc(aK + (uint32_t)g * 8192u, k16, 16384u), p.idesc_pv,
+                     (jj | g | k16) ? 1u : 0u);
+        tc_commit(ds_empty + g);
+      }
+      tc_commit(kv_empty + sl);
+      return true;
+    };
+    for (int j = 0; ok && j < ntiles; ++j) {
+      const int sl = j & 1;
+      if (!mbar_wait_bounded(kv_full + sl, (unsigned)((j >> 1) & 1), kDevErrAttnTimeout)) { ok = false; break; }
+      const uint32_t aK = smem_u32(sK + (size_t)sl * kTileBytes), aV = smem_u32(sV + (size_t)sl * kTileBytes);
+      for (int g = 0; g < 2; ++g) {
+        if (!mbar_wait_bounded(t_empty + g, (unsigned)(j & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tS = tmem_base + (uint32_t)g * 128u, tdP = tS + 64u;
+#pragma unroll
+        for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+          tc_mma_f16(tS, kmajor_desc(aQ, k16), kmajor_box_desc(aK + (uint32_t)g * 8192u, k16, 16384u), p.idesc_s, k16 ? 1u : 0u);
+#pragma unroll
+        for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+          tc_mma_f16(tdP, kmajor_desc(adO, k16), kmajor_box_desc(aV + (uint32_t)g * 8192u, k16, 16384u), p.idesc_s, k16 ? 1u : 0u);
+        tc_commit(t_full + g);
+      }
+      if (ok && j > 0) ok = finish(j - 1);
+    }
+    if (ok) ok = finish(ntiles - 1);
+    if (ok) tc_commit(acc_full);
+  } else if (warp >= 2) {
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;
+    const int r = qq * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
+    const float mb = __fmaf_rn(st[0], kLog2e, __log2f(st[1]));      // y = 2^(s log2e - mb)
+    const float cdot = st[2];
+    unsigned char* myDS = sDS + (size_t)grp * kUnitBytes;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (!mbar_wait_bounded_warp(t_full + grp, (unsigned)(j & 1), kDevErrAttnTimeout)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tmem_base + (uint32_t)grp * 128u + lane_off;
+      // the dQ product of the previous tile has read this group's staging buffer (issued a whole unit ago)
+      if (!mbar_wait_bounded_warp(ds_empty + grp, (unsigned)(j & 1) ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {              // 32 keys at a time
+        uint32_t sv[32], gv[32];
+        tc_ld32(ts + (uint32_t)(hh * 32), sv);
+        tc_ld32(ts + 64u + (uint32_t)(hh * 32), gv);
+        tc_ld_wait();
+        if (hh == 1) {                              // the unit is in registers: the next S / dP may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(t_empty + grp);
+        }
+        uint4 unused[4], dc[4];
+        bwd_unit_math<T, false, true>(sv, gv, p.alpha, nullptr, mb, cdot, j == qi, grp * kBwdCols + hh * 32, r, unused, dc);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)                 // chunk hh * 4 + c: keys 8 (hh * 4 + c) .. + 7 of the unit
+          *reinterpret_cast<uint4*>(myDS + (size_t)r * 128 + ((((hh * 4 + c) ^ (r & 7))) << 4)) = dc[c];
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full + grp);
+    }
+    // dQ rows: alpha * accumulator, rounded once; staged packed [128][head_dim] (the K ring is free by then) and
+    // written with consecutive lanes on consecutive 8-byte pieces
+    const bool fin = ok && mbar_wait_bounded_warp(acc_full, 0, kDevErrAttnTimeout);
+    unsigned char* rowbuf = sK;
+    if (fin) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tAcc + lane_off + (uint32_t)c0, v);
+        tc_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int c = c0 + g * 4;
+          if (c + 4 <= p.head_dim) {
+            uint2 w;
+            w.x = pack2<T>(__uint_as_float(v[g * 4]) * p.alpha, __uint_as_float(v[g * 4 + 1]) * p.alpha);
+            w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * p.alpha, __uint_as_float(v[g * 4 + 3]) * p.alpha);
+            *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    named_barrier(1, 256);
+    if (fin) {
+      const int cw = warp - 2;
+      for (int rr = cw * 16; rr < cw * 16 + 16; ++rr) {
+        T* out = dq + (((long long)b * p.seq + q0 + rr) * p.heads + h) * p.head_dim;
+        if (lane < p.head_dim / 4)
+          reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
+      }
+    }
+    tc_fence_before();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- dK, dV: one CTA per (batch, head, 128 keys) -------------------------------------------------------------------
+// K and V of the tile stay in shared memory; Q, dO (64 query rows at a time) and those rows' statistics come through a
+// two-slot ring.  The scores are built transposed, S^T = K Q^T (TMEM lane = key, column = query), so that P^T and dS^T
+// come out of the softmax threads in the layout of an A operand.  Unit t (query rows 128 j + 64 t ...) belongs to group
+// t & 1 and ring slot t & 1.  Tensor memory: group g: S^T at 128 g, dP^T at 128 g + 64; dV at 256, dK at 384.
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO64,
+                         T* __restrict__ dk, T* __restrict__ dv, const float* __restrict__ stats, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sK = base;                        // 32 KB
+  unsigned char* sV = sK + kTileBytes;             // 32 KB
+  unsigned char* sQ = sV + kTileBytes;             // 2 x 16 KB: [64 queries][128 hd] as two boxes of 8 KB
+  unsigned char* sdO = sQ + 2 * kUnitBytes;        // 2 x 16 KB
+  unsigned char* sPT = sdO + 2 * kUnitBytes;       // 2 x 16 KB, one per group: P^T [128 keys][64 queries], K-major
+  unsigned char* sDST = sPT + 2 * kUnitBytes;      // 2 x 16 KB: dS^T likewise
+  float2* sStat = reinterpret_cast<float2*>(sDST + 2 * kUnitBytes);       // 2 x 64 x (mb, c)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 2 * kBwdCols);
+  uint64_t* kv_full = bars;                        // 1
+  uint64_t* qd_full = bars + 1;                    // 2
+  uint64_t* qd_empty = bars + 3;                   // 2
+  uint64_t* t_full = bars + 5;                     // 2 (per group)
+  uint64_t* t_empty = bars + 7;                    // 2
+  uint64_t* st_full = bars + 9;                    // 2: the group's P^T and dS^T are staged
+  uint64_t* st_empty = bars + 11;                  // 2
+  uint64_t* acc_full = bars + 13;                  // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // launch order: batch slowest, then key tile (tile 0 has the most query rows after it: heaviest first), then head
+  const int nk = p.seq / kAttnRows;
+  const int b = (int)(blockIdx.x / (nk * p.heads));
+  const int rem = (int)(blockIdx.x % (nk * p.heads));
+  const int kj = rem / p.heads;
+  const int h = rem % p.heads;
+  const int k0 = kj * kAttnRows;
+  const int nunits = (p.seq - k0) / kBwdCols;      // query rows k0 .. seq in steps of 64
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(acc_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(qd_full + s, 1); mbar_init(qd_empty + s, 1);
+      mbar_init(t_full + s, 1); mbar_init(t_empty + s, 4); mbar_init(st_full + s, 4); mbar_init(st_empty + s, 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tdV = tmem_base + 256u, tdK = tmem_base + 384u;
+
+  if (warp == 0) {
+    // ---------------- producer warp: lane 0 issues the bulk copies, all lanes stage the rows' statistics ----------------
+    constexpr float kLog2e = 1.4426950408889634f;
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_4d(sK, &tmK, kv_full, 0, k0, h, b);
+      tma_load_4d(sK + 16384, &tmK, kv_full, 64, k0, h, b);
+      tma_load_4d(sV, &tmV, kv_full, 0, k0, h, b);
+      tma_load_4d(sV + 16384, &tmV, kv_full, 64, k0, h, b);
+    }
+    for (int t = 0; t < nunits; ++t) {
+      const int sl = t & 1;
+      const int qrow = k0 + t * kBwdCols;
+      if (!mbar_wait_bounded_warp(qd_empty + sl, (unsigned)((t >> 1) & 1) ^ 1, kDevErrAttnTimeout)) break;
+      // y = 2^(s log2e - mb) with mb = m log2e + log2 l; c = dO . O (word 2, from attention_rowdot_kernel)
+      for (int i = lane; i < kBwdCols; i += 32) {
+        const float4 sv = *reinterpret_cast<const float4*>(stats + (((long long)b * p.heads + h) * p.seq + qrow + i) * 4);
+        sStat[sl * kBwdCols + i] = make_float2(__fmaf_rn(sv.x, kLog2e, __log2f(sv.y)), sv.z);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        unsigned char* dq_ = sQ + (size_t)sl * kUnitBytes;
+        unsigned char* do_ = sdO + (size_t)sl * kUnitBytes;
+        mbar_expect_tx(qd_full + sl, 2 * kUnitBytes);            // its release also publishes the statistics above
+        tma_load_4d(dq_, &tmQ64, qd_full + sl, 0, qrow, h, b);
+        tma_load_4d(dq_ + 8192, &tmQ64, qd_full + sl, 64, qrow, h, b);
+        tma_load_4d(do_, &tmdO64, qd_full + sl, 0, qrow, h, b);
+        tma_load_4d(do_ + 8192, &tmdO64, qd_full + sl, 64, qrow, h, b);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    bool ok = mbar_wait_bounded(kv_full, 0, kDevErrAttnTimeout);
+    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+    // dV += P^T dO, dK += dS^T Q for unit u; then its ring slot and staging buffers are free
+    auto finish = [&](int u) -> bool {
+      const int g = u & 1;
+      if (!mbar_wait_bounded(st_full + g, (unsigned)((u >> 1) & 1), kDevErrAttnTimeout)) return false;
+      tc_fence_after();
+      const uint32_t aPT = smem_u32(sPT + (size_t)g * kUnitBytes), aDST = smem_u32(sDST + (size_t)g * kUnitBytes);
+      const uint32_t aQ = smem_u32(sQ + (size_t)g * kUnitBytes), adO = smem_u32(sdO + (size_t)g * kUnitBytes);
+#pragma unroll
+      for (int k16 = 0; k16 < kBwdCols / 16; ++k16)
+        tc_mma_f16(tdV, kmajor_box_desc(aPT, k16, kUnitBytes), mnmajor_box_desc(adO, k16, 8192u), p.idesc_pv, (u | k16) ? 1u : 0u);
+#pragma unroll
+      for (int k16 = 0; k16 < kBwdCols / 16; ++k16)
+        tc_mma_f16(tdK, kmajor_box_desc(aDST, k16, kUnitBytes), mnmajor_box_desc(aQ, k16, 8192u), p.idesc_pv, (u | k16) ? 1u : 0u);
+      tc_commit(st_empty + g);
+      tc_commit(qd_empty + g);
+      return true;
+    };
+    for (int t = 0; ok && t < nunits; ++t) {
+      const int g = t & 1;
+      const unsigned ph = (unsigned)((t >> 1) & 1);
+      if (!mbar_wait_bounded(qd_full + g, ph, kDevErrAttnTimeout)) { ok = false; break; }
+      if (!mbar_wait_bounded(t_empty + g, ph ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t aQ = smem_u32(sQ + (size_t)g * kUnitBytes), adO = smem_u32(sdO + (size_t)g * kUnitBytes);
+      const uint32_t tS = tmem_base + (uint32_t)g * 128u, tdP = tS + 64u;
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)       // S^T = K Q^T: 128 keys x 64 queries
+        tc_mma_f16(tS, kmajor_desc(aK, k16), kmajor_box_desc(aQ, k16, 8192u), p.idesc_s, k16 ? 1u : 0u);
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)       // dP^T = V dO^T
+        tc_mma_f16(tdP, kmajor_desc(aV, k16), kmajor_box_desc(adO, k16, 8192u), p.idesc_s, k16 ? 1u : 0u);
+      tc_commit(t_full + g);
+      if (t > 0) ok = finish(t - 1);
+    }
+    if (ok) ok = finish(nunits - 1);
+    if (ok) tc_commit(acc_full);
+  } else if (warp >= 2) {
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;
+    const int r = qq * 32 + lane;                   // key row inside the tile
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    unsigned char* myPT = sPT + (size_t)grp * kUnitBytes;
+    unsigned char* myDST = sDST + (size_t)grp * kUnitBytes;
+    bool ok = true;
+    for (int t = grp; t < nunits; t += 2) {
+      const unsigned ph = (unsigned)((t >> 1) & 1);
+      if (!mbar_wait_bounded_warp(t_full + grp, ph, kDevErrAttnTimeout)) { ok = false; break; }
+      // complete long since (the products waited for it); taken here for the statistics the producer warp staged with it
+      if (!mbar_wait_bounded_warp(qd_full + grp, ph, kDevErrAttnTimeout)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tmem_base + (uint32_t)grp * 128u + lane_off;
+      const float2* stq = sStat + grp * kBwdCols;   // slot = group: this unit's 64 query rows
+      // the products of the group's previous unit have read its staging buffers (issued a whole unit ago)
+      if (!mbar_wait_bounded_warp(st_empty + grp, ph ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {              // 32 queries at a time
+        uint32_t sv[32], gv[32];
+        tc_ld32(ts + (uint32_t)(hh * 32), sv);
+        tc_ld32(ts + 64u + (uint32_t)(hh * 32), gv);
+        tc_ld_wait();
+        if (hh == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(t_empty + grp);
+        }
+        // queries of units 0 and 1 overlap the key tile's own rows: key k0 + r is masked for query k0 + 64 t + c when r > 64 t + c
+        uint4 pc[4], dc[4];
+        bwd_unit_math<T, true, false>(sv, gv, p.alpha, stq + hh * 32, 0.f, 0.f, t < 2, t * kBwdCols + hh * 32, r, pc, dc);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const size_t off = (size_t)r * 128 + ((((hh * 4 + c) ^ (r & 7))) << 4);
+          *reinterpret_cast<uint4*>(myPT + off) = pc[c];
+          *reinterpret_cast<uint4*>(myDST + off) = dc[c];
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(st_full + grp);
+    }
+    // group 0 writes dV, group 1 alpha * dK: rows staged packed [128][head_dim] (P^T / dS^T buffers are free), then
+    // consecutive lanes on consecutive 8-byte pieces
+    const bool fin = ok && mbar_wait_bounded_warp(acc_full, 0, kDevErrAttnTimeout);
+    unsigned char* rowbuf = grp == 0 ? sPT : sDST;          // 32 KB each: 128 rows x up to 256 bytes
+    const float scale = grp == 0 ? 1.f : p.alpha;
+    if (fin) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.head_dim; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32((grp == 0 ? tdV : tdK) + lane_off + (uint32_t)c0, v);
+        tc_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int c = c0 + g * 4;
+          if (c + 4 <= p.head_dim) {
+            uint2 w;
+            w.x = pack2<T>(__uint_as_float(v[g * 4]) * scale, __uint_as_float(v[g * 4 + 1]) * scale);
+            w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * scale, __uint_as_float(v[g * 4 + 3]) * scale);
+            *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    named_barrier(1 + grp, 128);                    // the group's 128 rows are staged
+    if (fin) {
+      T* outp = grp == 0 ? dv : dk;
+      const int cw = qq;                            // 4 warps of the group, 32 rows each
+      for (int rr = cw * 32; rr < cw * 32 + 32; ++rr) {
+        T* out = outp + (((long long)b * p.seq + k0 + rr) * p.heads + h) * p.head_dim;
+        if (lane < p.head_dim / 4)
+          reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
+      }
+    }
+    tc_fence_before();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -718,6 +1199,53 @@ static int attention_bwd_prep_run(uint64_t pp, uint64_t ds, uint64_t q, uint64_t
   return check_launch();
 }
 
+constexpr size_t kAttnBwdDqSmem = 1024 + 6 * (size_t)kTileBytes + 2 * (size_t)kUnitBytes + 256;
+constexpr size_t kAttnBwdDkvSmem = 1024 + 2 * (size_t)kTileBytes + 8 * (size_t)kUnitBytes + 2 * kBwdCols * sizeof(float2) + 256;
+
+template <typename T>
+static int attention_bwd_run(uint64_t dq, uint64_t dk, uint64_t dv, uint64_t q, uint64_t k, uint64_t v, uint64_t dctx, uint64_t ctx,
+                             uint64_t stats, int batch, int seq, int heads, int head_dim, float alpha, cudaStream_t st) {
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  CUtensorMap tmQ, tmK, tmV, tmdO, tmQ64, tmdO64;
+  int rc = encode_bshd(&tmQ, q, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmK, k, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmV, v, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmdO, dctx, batch, seq, heads, kAttnHd, 64, kAttnRows, bf16);
+  if (!rc) rc = encode_bshd(&tmQ64, q, batch, seq, heads, kAttnHd, 64, kBwdCols, bf16);
+  if (!rc) rc = encode_bshd(&tmdO64, dctx, batch, seq, heads, kAttnHd, 64, kBwdCols, bf16);
+  if (rc) return rc;
+  AttnParams p;
+  p.batch = batch; p.seq = seq; p.heads = heads; p.head_dim = head_dim; p.alpha = alpha;
+  const uint32_t kind = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(128 >> 4) << 24);
+  p.idesc_s = kind | ((uint32_t)(kBwdCols >> 3) << 17);                  // 128 x 64, both operands K-major
+  p.idesc_pv = kind | ((uint32_t)(128 >> 3) << 17) | (1u << 16);        // 128 x 128, B MN-major
+  {
+    const long long rows = (long long)batch * seq * heads;
+    long long grid = (rows + 31) / 32;
+    if (grid > (long long)kNumSMs * 16) grid = (long long)kNumSMs * 16;
+    attention_rowdot_kernel<T><<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<float*>(stats), reinterpret_cast<const T*>(ctx),
+                                                               reinterpret_cast<const T*>(dctx), rows, seq, heads, head_dim);
+    rc = check_launch();
+    if (rc) return rc;
+  }
+  const long long grid = (long long)batch * heads * (seq / kAttnRows);
+  {
+    auto kern = attention_bwd_dkv_kernel<T>;
+    static bool attr_set[kMaxDevices] = {};
+    ensure_dynamic_smem(kern, kAttnBwdDkvSmem, attr_set);
+    kern<<<(unsigned)grid, kAttnThreads, kAttnBwdDkvSmem, st>>>(tmQ64, tmK, tmV, tmdO64, reinterpret_cast<T*>(dk), reinterpret_cast<T*>(dv),
+                                                                reinterpret_cast<const float*>(stats), p);
+    rc = check_launch();
+    if (rc) return rc;
+  }
+  auto kern = attention_bwd_dq_kernel<T>;
+  static bool attr_set[kMaxDevices] = {};
+  ensure_dynamic_smem(kern, kAttnBwdDqSmem, attr_set);
+  kern<<<(unsigned)grid, kAttnThreads, kAttnBwdDqSmem, st>>>(tmQ, tmK, tmV, tmdO, reinterpret_cast<T*>(dq),
+                                                             reinterpret_cast<const float*>(stats), p);
+  return check_launch();
+}
+
 }  // namespace cb
 
 extern "C" {
@@ -768,6 +1296,25 @@ int cacti_b200_attention_fwd(cacti_b200_dptr ctx, cacti_b200_dptr stats, cacti_b
   if (dtype == CACTI_B200_R_16F)
     return attention_fwd_run<__half>(ctx, stats, q, k, v, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha, st);
   return attention_fwd_run<__nv_bfloat16>(ctx, stats, q, k, v, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha, st);
+}
+
+int cacti_b200_attention_bwd(cacti_b200_dptr dq, cacti_b200_dptr dk, cacti_b200_dptr dv, cacti_b200_dptr q, cacti_b200_dptr k,
+                             cacti_b200_dptr v, cacti_b200_dptr dctx, cacti_b200_dptr ctx, cacti_b200_dptr stats, int64_t batch,
+                             int64_t seq, int64_t heads, int64_t head_dim, float alpha, int dtype, cacti_b200_stream stream) {
+  using namespace cb;
+  if (batch < 0 || seq < 0 || heads < 0 || head_dim <= 0) return CACTI_B200_ERR_INVALID_VALUE;
+  if (dtype != CACTI_B200_R_16F && dtype != CACTI_B200_R_16BF) return CACTI_B200_ERR_DTYPE;
+  if (head_dim > kAttnHd || head_dim % 4 || seq % kAttnRows || batch * heads * (seq / kAttnRows) > 0x7fffffffLL)
+    return CACTI_B200_ERR_SHAPE;
+  if (batch == 0 || seq == 0 || heads == 0) return CACTI_B200_OK;
+  if (!dq || !dk || !dv || !q || !k || !v || !dctx || !ctx || !stats || ((q | k | v | dctx) & 15) || ((dq | dk | dv | ctx) & 7) ||
+      (stats & 15))
+    return CACTI_B200_ERR_INVALID_VALUE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == CACTI_B200_R_16F)
+    return attention_bwd_run<__half>(dq, dk, dv, q, k, v, dctx, ctx, stats, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha, st);
+  return attention_bwd_run<__nv_bfloat16>(dq, dk, dv, q, k, v, dctx, ctx, stats, (int)batch, (int)seq, (int)heads, (int)head_dim, alpha,
+                                          st);
 }
 
 int cacti_b200_attention_bwd_prep(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b200_dptr q, cacti_b200_dptr k,

@@ -46,6 +46,8 @@ def lib():
             "cbh_thunk_attention_fwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, C.c_float, C.c_int]),
             "cbh_thunk_attention_bwd_prep": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                                        _i64, C.c_float, C.c_int]),
+            "cbh_thunk_attention_bwd": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                  _i64, C.c_float, C.c_int]),
             "cbh_thunk_adamw32_step": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int, C.c_int, C.c_float, C.c_float,
                                                  C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]),
         }

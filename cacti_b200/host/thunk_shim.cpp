@@ -554,6 +554,17 @@ int thunk_attention_bwd_prep(PCtx& p, Mode m, int64_t prob, int64_t ds, int64_t 
   return cacti_b200_attention_bwd_prep(dp, dds, dq, dk, dv, ddc, dc, dst, batch, seq, heads, hd, alpha, dtype, p.stream());
 }
 
+int thunk_attention_bwd(PCtx& p, Mode m, int64_t dq, int64_t dk, int64_t dv, int64_t q, int64_t k, int64_t v, int64_t dctx, int64_t ctx,
+                        int64_t stats, int64_t batch, int64_t seq, int64_t heads, int64_t hd, float alpha, int dtype) {
+  if (m != kApply) return CACTI_B200_ERR_INVALID_VALUE;
+  Binding b(p);
+  const uint64_t pq = b.in(q), pk = b.in(k), pv = b.in(v), pdc = b.in(dctx), pc = b.in(ctx);
+  const uint64_t pst = b.out(stats, kInitialize);        // two of its words are scratch of this thunk
+  const uint64_t o1 = b.out(dq, kApply), o2 = b.out(dk, kApply), o3 = b.out(dv, kApply);
+  if (!b.ok) return -1;
+  return cacti_b200_attention_bwd(o1, o2, o3, pq, pk, pv, pdc, pc, pst, batch, seq, heads, hd, alpha, dtype, p.stream());
+}
+
 int thunk_adamw32_step(PCtx& p, Mode m, int64_t master, int64_t grad1_avg, int64_t grad2_avg, int64_t param_out, int64_t grad, int64_t n,
                        int grad_dtype, int param_dtype, float grad_unscale, float lr, float wd, float a1, float a2, float eps, int iter_nr) {
   if (m != kInitialize) return CACTI_B200_ERR_INVALID_VALUE;
@@ -672,6 +683,10 @@ int cbh_thunk_attention_fwd(void* c, int mode, int64_t ctx, int64_t stats, int64
 int cbh_thunk_attention_bwd_prep(void* c, int mode, int64_t prob, int64_t ds, int64_t q, int64_t k, int64_t v, int64_t dctx, int64_t ctx,
                                  int64_t stats, int64_t batch, int64_t seq, int64_t heads, int64_t hd, float alpha, int dtype) {
   return cbh::thunk_attention_bwd_prep(CBH_P, CBH_M(mode), prob, ds, q, k, v, dctx, ctx, stats, batch, seq, heads, hd, alpha, dtype);
+}
+int cbh_thunk_attention_bwd(void* c, int mode, int64_t dq, int64_t dk, int64_t dv, int64_t q, int64_t k, int64_t v, int64_t dctx,
+                            int64_t ctx, int64_t stats, int64_t batch, int64_t seq, int64_t heads, int64_t hd, float alpha, int dtype) {
+  return cbh::thunk_attention_bwd(CBH_P, CBH_M(mode), dq, dk, dv, q, k, v, dctx, ctx, stats, batch, seq, heads, hd, alpha, dtype);
 }
 int cbh_thunk_adamw32_step(void* c, int mode, int64_t master, int64_t g1, int64_t g2, int64_t param_out, int64_t grad, int64_t n,
                            int grad_dtype, int param_dtype, float grad_unscale, float lr, float wd, float a1, float a2, float eps, int iter_nr) {

@@ -169,6 +169,9 @@ int thunk_attention_fwd(PCtx& p, Mode m, int64_t ctx, int64_t stats, int64_t q, 
                         int64_t heads, int64_t hd, float alpha, int dtype);
 int thunk_attention_bwd_prep(PCtx& p, Mode m, int64_t prob, int64_t ds, int64_t q, int64_t k, int64_t v, int64_t dctx, int64_t ctx,
                              int64_t stats, int64_t batch, int64_t seq, int64_t heads, int64_t hd, float alpha, int dtype);
+// three outputs (dq, dk, dv); P and dS never exist as cells
+int thunk_attention_bwd(PCtx& p, Mode m, int64_t dq, int64_t dk, int64_t dv, int64_t q, int64_t k, int64_t v, int64_t dctx, int64_t ctx,
+                        int64_t stats, int64_t batch, int64_t seq, int64_t heads, int64_t hd, float alpha, int dtype);
 // Initialize mode only: master, grad1_avg, grad2_avg are read and overwritten, param_out rewritten (AdamW32::step,
 // src/librarium/adamw.rs:46-61)
 int thunk_adamw32_step(PCtx& p, Mode m, int64_t master, int64_t grad1_avg, int64_t grad2_avg, int64_t param_out, int64_t grad, int64_t n,

@@ -15,8 +15,11 @@ arithmetic step is a `cacti_b200_*` call.  Differences from the reference graph,
     every value that is used is bit-identical to the full product.  The softmax zero-fills the masked tails of P
     and dS only as far as those matmuls read (CACTI_B200_MASK_CAUSAL_TRIM).
   * by default attention runs fused (cacti_b200_attention_fwd / _bwd_prep): scores and probabilities stay on chip in
-    the forward, and the backward rebuilds P and dS per tile instead of reading stored scores; `attention="unfused"`
-    keeps the reference's op sequence.
+    the forward, and the backward rebuilds P and dS per tile instead of reading stored scores, materialises them once
+    and multiplies them with the three hinted block matmuls.  `attention="fused-bwd"` keeps P and dS on chip in the
+    backward too (cacti_b200_attention_bwd: measured slower, 2.10 ms against 1.42 ms per layer at 8 sequences, because
+    the exponentials, which bound these kernels, are then evaluated once for dQ and once for dK / dV);
+    `attention="unfused"` keeps the reference's op sequence.
 Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the reference.
 """
 from __future__ import annotations
@@ -90,9 +93,12 @@ class TrainStep:
         # "fused": attention_fwd / attention_bwd_prep (scores never reach HBM); "unfused": the reference's op sequence,
         # block matmul - softmax - block matmul; "auto": fused when the shape allows it
         can_fuse = cfg.seq % 128 == 0 and cfg.head_dim <= 128 and cfg.head_dim % 4 == 0
-        if attention == "fused" and not can_fuse:
+        if attention not in ("auto", "fused", "fused-bwd", "unfused"):
+            raise ValueError(f"attention={attention!r}")
+        if attention in ("fused", "fused-bwd") and not can_fuse:
             raise ValueError("fused attention needs seq % 128 == 0, head_dim <= 128 and head_dim % 4 == 0")
-        self.fused = can_fuse if attention == "auto" else attention == "fused"
+        self.fused = can_fuse if attention == "auto" else attention in ("fused", "fused-bwd")
+        self.fused_bwd = attention == "fused-bwd"       # the backward keeps P and dS on chip as well
         dev = params["embed"].device
         self.dev = dev
         self.T = batch * cfg.seq
@@ -196,7 +202,14 @@ class TrainStep:
             # attention branch: x_mid = x_in + ctx Wo^T
             self._mm(dx, ctx, True, False, c=G["o"])
             dctx = self._mm(dx, Lw["o"], False, False)
-            if self.fused:
+            if self.fused_bwd:
+                # dq, dk, dv straight from q, k, v (the padded copies), dctx and the row statistics
+                dctx = ops.block_pad(dctx.view(B, S, H, hd), 128)
+                dq, dk, dv = ops.attention_bwd(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha)
+                dq, dk, dv = dq.view(T, H, hd), dk.view(T, H, hd), dv.view(T, D)
+                del dctx, sc
+                self.launches += 4
+            elif self.fused:
                 # P and dS are rebuilt from q, k, v, dctx and the row statistics; q, k, v here are the padded copies
                 dctx = ops.block_pad(dctx.view(B, S, H, hd), 128)
                 p, ds = ops.attention_bwd_prep(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha)
@@ -209,12 +222,13 @@ class TrainStep:
                 del dp
                 self.launches += 1
                 dctx, q, k, bv = dctx.view(B, S, H, hd), q.view(B, S, H, hd), k.view(B, S, H, hd), None
-            del sc
-            dv = self._bmm(p.view(B, S, H, S), dctx, True, False, tri=TRI_A_UPPER, b_valid=bv).view(T, D)      # P^T dctx
-            del p, dctx
-            dq = self._bmm(ds.view(B, S, H, S), k, False, False, alpha, TRI_A_LOWER, b_valid=bv)               # dS K
-            dk = self._bmm(ds.view(B, S, H, S), q, True, False, alpha, TRI_A_UPPER, b_valid=bv)                # dS^T Q
-            del ds
+            if not self.fused_bwd:
+                del sc
+                dv = self._bmm(p.view(B, S, H, S), dctx, True, False, tri=TRI_A_UPPER, b_valid=bv).view(T, D)      # P^T dctx
+                del p, dctx
+                dq = self._bmm(ds.view(B, S, H, S), k, False, False, alpha, TRI_A_LOWER, b_valid=bv)               # dS K
+                dk = self._bmm(ds.view(B, S, H, S), q, True, False, alpha, TRI_A_UPPER, b_valid=bv)                # dS^T Q
+                del ds
             dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
             dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)
             self._mm(dq, n1, True, False, c=G["q"])

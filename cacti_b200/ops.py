@@ -347,3 +347,13 @@ def attention_bwd_prep(q_pad, k_pad, v_pad, dctx_pad, ctx, stats, alpha, p=None,
                                               _ptr(ctx), _ptr(stats), b, s, h, ctx.shape[-1], alpha, _dt(q_pad), _stream()),
           "attention_bwd_prep")
     return p, ds
+
+
+def attention_bwd(q_pad, k_pad, v_pad, dctx_pad, ctx, stats, alpha, dq=None, dk=None, dv=None):
+    """(dq, dk, dv) [B, S, H, head_dim]: the whole adjoint of attention_fwd, P and dS never leaving the SMs."""
+    b, s, h, _ = q_pad.shape
+    hd = ctx.shape[-1]
+    dq, dk, dv = (torch.empty(b, s, h, hd, dtype=q_pad.dtype, device=q_pad.device) if t is None else t for t in (dq, dk, dv))
+    check(lib().cacti_b200_attention_bwd(_ptr(dq), _ptr(dk), _ptr(dv), _ptr(q_pad), _ptr(k_pad), _ptr(v_pad), _ptr(dctx_pad), _ptr(ctx),
+                                         _ptr(stats), b, s, h, hd, alpha, _dt(q_pad), _stream()), "attention_bwd")
+    return dq, dk, dv

@@ -365,6 +365,22 @@ int cacti_b200_attention_bwd_prep(cacti_b200_dptr p, cacti_b200_dptr ds, cacti_b
                                   int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha, int dtype,
                                   cacti_b200_stream stream);
 
+/* Whole adjoint of the fused attention in one call: dq, dk, dv [batch, seq, heads, head_dim] from q, k, v, dctx (padded
+ * to 128 columns as above), ctx and stats of cacti_b200_attention_fwd.  Same arithmetic and rounding points as
+ * cacti_b200_attention_bwd_prep followed by the three hinted block matmuls (dV = P^T dO, dQ = alpha dS K,
+ * dK = alpha dS^T Q), but P and dS stay in shared memory: one kernel per 128 query rows accumulates dQ over the key
+ * tiles before it, one kernel per 128 keys accumulates dK and dV over the query rows after it, each output element by
+ * one CTA in a fixed order (no floating-point atomics; S and dP are formed once per kernel).  Three launches (c = dO . O
+ * first, into word 2 of stats).  Results agree with the chain above to the summation order inside the tensor cores.
+ * It needs no [batch, seq, heads, seq] buffers (4.3 GB for P and dS at 8 sequences of 2048), but evaluates the
+ * exponentials twice, which is what bounds these kernels: measured 2.10 ms against 1.42 ms for the chain at
+ * [8, 2048, 32, 100].  A caller short of memory takes this one, a caller short of time the chain.
+ * dq, dk, dv, ctx 8-byte aligned; same shape limits as cacti_b200_attention_fwd.  No counterpart in the reference. */
+int cacti_b200_attention_bwd(cacti_b200_dptr dq, cacti_b200_dptr dk, cacti_b200_dptr dv, cacti_b200_dptr q, cacti_b200_dptr k,
+                             cacti_b200_dptr v, cacti_b200_dptr dctx, cacti_b200_dptr ctx, cacti_b200_dptr stats,
+                             int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, float alpha, int dtype,
+                             cacti_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

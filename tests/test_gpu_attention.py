@@ -137,3 +137,66 @@ def test_attention_bwd_prep(cuda, bsz, s, h, hd):
         scale = np.sqrt((ex ** 2).mean())
         assert rms_f <= 1.5 * rms_u + 1e-4 * scale, (name, rms_f, rms_u)
         assert np.abs(e_f).max() <= 3 * np.abs(e_u).max() + 2e-3 * scale, (name, np.abs(e_f).max(), np.abs(e_u).max())
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(1, 128, 1, 128), (2, 256, 3, 100), (1, 640, 2, 64), (2, 1024, 2, 100), (1, 2048, 2, 100)])
+def test_attention_bwd_fused(cuda, bsz, s, h, hd):
+    """dQ, dK, dV from the two fused kernels against (a) the chain they replace, attention_bwd_prep plus the three hinted
+    block matmuls (same arithmetic and rounding points: the difference is the summation order inside the tensor
+    cores, bounded at twice the block matmul's tolerance against the magnitude of the summed terms), and (b) the exact
+    adjoint in float64 from the definition (tests/torch_defs.py), at the tolerance the chain itself is held to."""
+    from tests import torch_defs as TD
+    q, k, v, do = (dev(R.normal(110 + i, (bsz, s, h, hd), np.float16)) for i in range(4))
+    alpha = float(1.0 / np.sqrt(hd))
+    qp, kp, vp, dop = (ops.block_pad(t, 128) for t in (q, k, v, do))
+    ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    dq, dk, dv = ops.attention_bwd(qp, kp, vp, dop, ctx, stats, alpha)
+    dq2, dk2, dv2 = ops.attention_bwd(qp, kp, vp, dop, ctx, stats, alpha)
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert capi.lib().cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)          # fixed summation order
+    p, ds = ops.attention_bwd_prep(qp, kp, vp, dop, ctx, stats, alpha)
+    chain = {"dv": ops.block_gemm(p, dop, True, False, tri=capi.TRI_A_UPPER, b_valid=hd),
+             "dq": ops.block_gemm(ds, kp, False, False, alpha=alpha, tri=capi.TRI_A_LOWER, b_valid=hd),
+             "dk": ops.block_gemm(ds, qp, True, False, alpha=alpha, tri=capi.TRI_A_UPPER, b_valid=hd)}
+    # magnitudes of the summed terms: dS = y (dP - c) is a difference, good to a few 2^-11 of y (|dP| + |c|) (c is dO . O
+    # in both chains, dP and the scores are rounded to 16 bits), so dQ and dK are bounded against sums of that, not of |dS|
+    qh, kh, vh, doh = (t.double().transpose(1, 2) for t in (q, k, v, do))                 # [B, H, S, hd]
+    sc = alpha * qh @ kh.transpose(-1, -2)
+    smax = float(sc.abs().max())
+    causal = torch.ones(s, s, dtype=torch.bool, device="cuda").tril()
+    pr = torch.softmax(sc.masked_fill(~causal, float("-inf")), -1)
+    dpr = doh @ vh.transpose(-1, -2)
+    terms = pr * (dpr.abs() + (pr * dpr).sum(-1, keepdim=True).abs())
+    mag = {"dv": (pr.transpose(-1, -2) @ doh.abs()).transpose(1, 2), "dq": alpha * (terms @ kh.abs()).transpose(1, 2),
+           "dk": alpha * (terms.transpose(-1, -2) @ qh.abs()).transpose(1, 2)}
+    _, edq, edk, edv = TD.causal_attention(q, k, v, do, alpha)
+    exact = {"dq": edq, "dk": edk, "dv": edv}
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert_close(host(got), host(chain[name]).astype(np.float64), "float16", f"fused {name} vs chain", rtol=4e-3,
+                     floor_abs=host(mag[name]))
+        assert_close(host(got), host(exact[name]), "float16", f"fused {name} vs float64 adjoint", rtol=2e-3 * max(1.0, smax),
+                     floor_abs=2 * host(mag[name]))
+
+
+def test_attention_bwd_fused_bf16_and_errors(cuda):
+    from tests import torch_defs as TD
+    bsz, s, h, hd = 1, 256, 2, 100
+    q, k, v, do = (dev(R.bf16_round(R.normal(120 + i, (bsz, s, h, hd))), bf16=True) for i in range(4))
+    alpha = 0.1
+    qp, kp, vp, dop = (ops.block_pad(t, 128) for t in (q, k, v, do))
+    ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    dq, dk, dv = ops.attention_bwd(qp, kp, vp, dop, ctx, stats, alpha)
+    _, edq, edk, edv = TD.causal_attention(q, k, v, do, alpha)
+    # scores, dP, P and dS each rounded to bfloat16 (2^-8): bounded against the tensor's rms at a few of those
+    for name, got, ex in (("dq", dq, edq), ("dk", dk, edk), ("dv", dv, edv)):
+        assert_close(host(got), host(ex), "bfloat16", f"bf16 fused {name}", rtol=2.0 ** -4, floor_frac=1.0)
+    L = capi.lib()
+    P = qp.data_ptr()
+    args = (P, P, P, P, P, P, P, P, P)
+    assert L.cacti_b200_attention_bwd(*args, 1, 200, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_SHAPE
+    assert L.cacti_b200_attention_bwd(*args, 1, 256, 2, 130, 0.1, capi.R_16F, None) == capi.ERR_SHAPE
+    assert L.cacti_b200_attention_bwd(*args, 1, 256, 2, 100, 0.1, capi.R_32F, None) == capi.ERR_DTYPE
+    assert L.cacti_b200_attention_bwd(*args, 0, 256, 2, 100, 0.1, capi.R_16F, None) == capi.OK
+    assert L.cacti_b200_attention_bwd(0, P, P, P, P, P, P, P, P, 1, 256, 2, 100, 0.1, capi.R_16F, None) == capi.ERR_INVALID_VALUE

@@ -57,15 +57,16 @@ def test_fused_attention_step_matches_oracle_and_unfused(cuda, hd, heads, seq):
     tok = R.uniform_int(3, B * cfg.seq, cfg.vocab)
     tgt = R.uniform_int(4, B * cfg.seq, cfg.vocab)
     out = {}
-    for mode in ("fused", "unfused"):
+    for mode in ("fused", "fused-bwd", "unfused"):
         grads = LS.zeros_like_params(P)
         step = LS.TrainStep(cfg, P, B, attention=mode)
-        assert step.fused == (mode == "fused")
+        assert step.fused == (mode != "unfused") and step.fused_bwd == (mode == "fused-bwd")
         loss = step.forward_backward(dev(tok), dev(tgt), grads)
         torch.cuda.synchronize()
         assert host(step.status)[0] == 0
         out[mode] = (float(host(loss)[0]), grads)
-    assert LS.TrainStep(cfg, P, B).fused                     # "auto" picks the fused path for this shape
+    auto = LS.TrainStep(cfg, P, B)
+    assert auto.fused and not auto.fused_bwd                # "auto": fused forward, P and dS materialised once in the backward
     ref_loss, ref_g = llama_oracle.step(_np_params(P), tok, tgt, cfg)
     for mode, (loss, grads) in out.items():
         assert abs(loss - float(ref_loss)) < 2e-3 * abs(float(ref_loss)), mode
@@ -75,6 +76,7 @@ def test_fused_attention_step_matches_oracle_and_unfused(cuda, hd, heads, seq):
             for name, g in grads["layers"][li].items():
                 assert_close(host(g), ref_g["layers"][li][name], "float16", f"{mode} layer {li} {name}", rtol=2e-2, floor_frac=1.0)
     assert abs(out["fused"][0] - out["unfused"][0]) < 1e-3 * abs(out["unfused"][0])
+    assert out["fused"][0] == out["fused-bwd"][0]            # the forward passes are the same kernels
 
 
 def test_graphed_step_replays_the_eager_step(cuda):

@@ -207,7 +207,8 @@ def _small_llama():
 
 
 @pytest.mark.gpu
-def test_training_step_through_cells_with_and_without_spilling(cuda):
+@pytest.mark.parametrize("fused_bwd", [True, False])
+def test_training_step_through_cells_with_and_without_spilling(cuda, fused_bwd):
     """The config-5 step (reduced size) driven through cells and thunks: with the soft limit above the step's peak
     nothing spills; with it below, activations go to page-locked host memory during the forward pass and come back
     in the backward pass.  Loss and every gradient are bit-identical between the two, and bit-identical to the same
@@ -221,7 +222,8 @@ def test_training_step_through_cells_with_and_without_spilling(cuda):
     tok = torch.randint(0, cfg.vocab, (batch * cfg.seq,), device=cuda, dtype=torch.int32, generator=g)
     tgt = torch.randint(0, cfg.vocab, (batch * cfg.seq,), device=cuda, dtype=torch.int32, generator=g)
     grads, _ = dp.alloc_bucketed_grads(P)
-    loss_t = float(LS.TrainStep(cfg, P, batch).forward_backward(tok, tgt, grads).item())
+    mode = "fused-bwd" if fused_bwd else "fused"        # attention adjoint in one thunk, or P and dS as cells + block matmuls
+    loss_t = float(LS.TrainStep(cfg, P, batch, attention=mode).forward_backward(tok, tgt, grads).item())
     flat_t = {k: v.cpu().numpy() for k, v in LS.flat_params(grads)}
     W = {k: v.cpu().numpy() for k, v in P.items() if k != "layers"}
     W["layers"] = [{k: v.cpu().numpy() for k, v in Lw.items()} for Lw in P["layers"]]
@@ -231,7 +233,7 @@ def test_training_step_through_cells_with_and_without_spilling(cuda):
         if limit is None:                      # below the peak of the roomy run, above what one thunk pins at once
             limit = int(results["roomy"][2]["peak_in_use"] * 0.45)
         ctx = H.Ctx(cuda=True, arena_bytes=arena, soft_limit=limit)
-        step = CellTrainStep(ctx, cfg, W, batch)
+        step = CellTrainStep(ctx, cfg, W, batch, fused_bwd=fused_bwd)
         loss = step.forward_backward(tok.cpu().numpy(), tgt.cpu().numpy())
         grads_c = {k: step.gradient(k) for k in flat_t}
         results[name] = (loss, grads_c, ctx.stats())
