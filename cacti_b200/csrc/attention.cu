@@ -31,6 +31,9 @@
 
 namespace cb {
 
+int pitched_rows_staged(bool rotate, uint64_t y, uint64_t x, uint64_t cos, uint64_t sin, int64_t n_tokens, int64_t heads,
+                        int64_t head_dim, int64_t head_pitch, int64_t pos_mod, int64_t pos_offset, int dtype, cudaStream_t st);   // rope.cu
+
 constexpr unsigned kDevErrAttnTimeout = 3u;
 constexpr int kAttnRows = 128;      // query rows per CTA = keys per tile
 constexpr int kAttnHd = 128;        // padded head dimension
@@ -1259,6 +1262,12 @@ int cacti_b200_block_pad(cacti_b200_dptr dst, cacti_b200_dptr src, int64_t nrow,
   if (groups == 0 || cols_pad == 0) return CACTI_B200_OK;
   if (!dst || (!src && cols > 0)) return CACTI_B200_ERR_INVALID_VALUE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // rows of whole blocks that are multiples of 16 bytes on both sides: staged copy (rows in by bulk copy, spread to the
+  // padded pitch in shared memory, out by bulk store)
+  if (cols > 0 && ncol > 0) {
+    const int staged = pitched_rows_staged(false, dst, src, 0, 0, nrow * rows, ncol, cols, cols_pad, 1, 0, dtype, st);
+    if (staged >= 0) return staged;
+  }
   if (cols % 4 == 0 && cols_pad % 8 == 0 && dst % 16 == 0 && src % 8 == 0) {
     const long long total = groups * (cols_pad / 8);
     long long grid = (total + 255) / 256;

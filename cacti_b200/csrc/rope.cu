@@ -277,6 +277,98 @@ rope_staged_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ 
   if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
 }
 
+// Staged form of the head-pitched forward (below), for 16-byte aligned token rows: the x row arrives by a bulk copy and
+// is rotated in place exactly as in rope_staged_kernel; the group then spreads it into an output row of `pitch`
+// elements per head (zeros after head_dim) in a second shared-memory buffer, 8 bytes per thread and step, and the
+// padded row leaves by one bulk store.  Two output buffers per group: a buffer is written again two rows later, after
+// the store that read it has finished reading.  Same bits as the per-thread kernel.
+// ROTATE = false: the copy alone, which is block_pad on rows of whole heads (pad_rows_staged below).
+template <typename T, bool ROTATE>
+__global__ void __launch_bounds__(512)
+rope_pitched_staged_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict__ cosT, const T* __restrict__ sinT,
+                           int64_t tokens, int row_len, int hd, int pitch, int items, FastDiv fd_uh, FastDiv fd_po, int G,
+                           int nstages, int64_t pos_mod, int64_t pos_off) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int UPV = Unit<T>::UPV;
+  const int groups = blockDim.x / G;
+  const int gid = threadIdx.x / G, lane = threadIdx.x - gid * G;
+  const int heads = row_len / hd;
+  const unsigned row_bytes = (unsigned)row_len * sizeof(T);
+  const unsigned out_bytes = (unsigned)heads * (unsigned)pitch * sizeof(T);
+  const size_t per_group = (size_t)nstages * row_bytes + 2 * (size_t)out_bytes;
+  unsigned char* stage0 = smem_raw + (size_t)gid * per_group;
+  unsigned char* out0 = stage0 + (size_t)nstages * row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * per_group);
+  uint64_t* bar0 = bars + gid * nstages;
+  if (lane < nstages) mbar_init(bar0 + lane, 1);
+  mbar_fence_init();
+  __syncthreads();
+  const int half = hd >> 1;
+  const int64_t stride = (int64_t)gridDim.x * groups;
+  const int64_t row0 = (int64_t)blockIdx.x * groups + gid;
+  const int64_t pstep = stride % pos_mod;
+  int64_t pos = (row0 + pos_off) % pos_mod;
+  const int in_u8 = hd >> 2, out_u8 = pitch >> 2;        // 8-byte units per head, stored and pitched
+  const int out_units = heads * out_u8;
+  GroupCtx gc; gc.G = G; gc.gid = gid;
+
+  auto issue = [&](int64_t r, int sl) {       // lane 0 only
+    mbar_expect_tx(bar0 + sl, row_bytes);
+    bulk_g2s(stage0 + (size_t)sl * row_bytes, X + r * row_len, row_bytes, bar0 + sl);
+  };
+  if (lane == 0)
+    for (int sl = 0; sl < nstages; ++sl)
+      if (row0 + sl * stride < tokens) issue(row0 + sl * stride, sl);
+
+  int slot = 0;
+  unsigned phase = 0, it = 0;
+  for (int64_t row = row0; row < tokens; row += stride, ++it) {
+    const bool gave_up = !mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout);
+    // the store of two rows back has read the output buffer this row is about to fill
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    T* sx = reinterpret_cast<T*>(stage0 + (size_t)slot * row_bytes);
+    if (ROTATE) {
+      const T* ct = cosT + pos * hd;
+      const T* stb = sinT + pos * hd;
+#pragma unroll 5
+      for (int n = lane; n < items; n += G) {
+        const uint32_t h = fdiv((uint32_t)n, fd_uh);
+        const int i = (int)((uint32_t)n - h * fd_uh.d) * UPV;
+        const int e = (int)h * hd + i;
+        const uint32_t c1 = ldu(ct + i), c2 = ldu(ct + i + half), s1 = ldu(stb + i), s2 = ldu(stb + i + half);
+        uint32_t* p1 = reinterpret_cast<uint32_t*>(sx + e);
+        uint32_t* p2 = reinterpret_cast<uint32_t*>(sx + e + half);
+        const uint32_t x1 = *p1, x2 = *p2;
+        *p1 = rope_unit<T>(x1, x2, c1, s1, true, false);
+        *p2 = rope_unit<T>(x2, x1, c2, s2, false, false);
+      }
+    }
+    // rotation complete (and lane 0 has seen the old store finish); a wait that ran out stops the group here, together
+    if (group_any(gc, gave_up)) break;
+    unsigned char* ob = out0 + (size_t)(it & 1) * out_bytes;
+    const uint2* in8 = reinterpret_cast<const uint2*>(sx);
+    uint2* out8 = reinterpret_cast<uint2*>(ob);
+    for (int u = lane; u < out_units; u += G) {
+      const uint32_t h = fdiv((uint32_t)u, fd_po);
+      const int k = (int)((uint32_t)u - h * fd_po.d);
+      out8[u] = k < in_u8 ? in8[(int)h * in_u8 + k] : make_uint2(0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the bulk store reads what was just written
+    group_barrier(gc);
+    if (lane == 0) {
+      bulk_s2g(Y + row * (int64_t)heads * pitch, ob, out_bytes);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // every lane has read the input slot: refill it
+      const int64_t next = row + (int64_t)nstages * stride;
+      if (next < tokens) issue(next, slot);
+    }
+    if (++slot == nstages) { slot = 0; phase ^= 1; }
+    pos += pstep;
+    if (pos >= pos_mod) pos -= pos_mod;
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
+}
+
 // Forward RoPE whose output rows are head-pitched: y[tok][h][0 .. pitch) with the head's head_dim rotated values
 // followed by zeros, the layout cacti_b200_block_pad would produce from the packed result (the fused attention reads
 // q and k that way).  One thread per 8-byte unit of the output; 16-bit types only (two 4-byte rope units per thread).
@@ -447,6 +539,49 @@ static int rope_entry(bool fwd, bool bwd, uint64_t y, uint64_t dx, uint64_t x, u
 
 }  // namespace cb
 
+namespace cb {
+// Launches rope_pitched_staged_kernel when the shape allows it (16-byte aligned rows on both sides, head and pitch in
+// whole 8-byte units); returns -1 when it does not, else the launch's return code.  rotate = false: the padded copy
+// alone (cos, sin unused).
+int pitched_rows_staged(bool rotate, uint64_t y, uint64_t x, uint64_t cos, uint64_t sin, int64_t n_tokens, int64_t heads,
+                        int64_t head_dim, int64_t head_pitch, int64_t pos_mod, int64_t pos_offset, int dtype, cudaStream_t st) {
+  const int64_t row_len = heads * head_dim;
+  if (!g_rope_staged || head_dim <= 0 || (head_dim & 3) || (head_pitch & 3) || (x & 15) || (y & 15) || (row_len * 2) % 16 ||
+      (heads * head_pitch * 2) % 16 || row_len > 0x3fffffffLL || heads * head_pitch > 0x3fffffffLL)
+    return -1;
+  const int64_t items = heads * ((head_dim / 2) / 2);
+  int G = g_rope_staged_g;
+  if (G > items) G = (int)((items + 31) / 32 * 32);
+  int groups = g_rope_staged_groups;
+  if (G * groups > 512) groups = 512 / G;
+  if (groups > kMaxGroupsPerCta) groups = kMaxGroupsPerCta;
+  int nst = g_rope_staged_stages;
+  auto smem_for = [&](int gr, int ns) {
+    return (size_t)gr * ((size_t)ns * row_len * 2 + 2 * (size_t)heads * head_pitch * 2 + (size_t)ns * sizeof(uint64_t));
+  };
+  while (nst > 2 && smem_for(groups, nst) > kMaxDynSmem) --nst;
+  while (groups > 1 && smem_for(groups, nst) > kMaxDynSmem) --groups;
+  const size_t smem = smem_for(groups, nst);
+  if (G < 32 || G > 512 || smem > kMaxDynSmem) return -1;
+  const int threads_s = G * groups;
+  const int64_t want = (n_tokens + groups - 1) / groups;
+#define CB_ROPE_PITCHED(T_, R_)                                                                                               \
+  do {                                                                                                                        \
+    auto kern = rope_pitched_staged_kernel<T_, R_>;                                                                           \
+    int64_t grid_s = (int64_t)kNumSMs * resident_ctas(kern, threads_s, smem);                                                 \
+    if (grid_s > want) grid_s = want;                                                                                         \
+    kern<<<(unsigned)grid_s, threads_s, smem, st>>>(reinterpret_cast<T_*>(y), reinterpret_cast<const T_*>(x),                 \
+        reinterpret_cast<const T_*>(cos), reinterpret_cast<const T_*>(sin), n_tokens, (int)row_len, (int)head_dim,            \
+        (int)head_pitch, (int)items, make_fastdiv((uint32_t)((head_dim / 2) / 2)), make_fastdiv((uint32_t)(head_pitch / 4)),  \
+        G, nst, pos_mod, pos_offset);                                                                                         \
+  } while (0)
+  if (dtype == CACTI_B200_R_16F) { if (rotate) CB_ROPE_PITCHED(__half, true); else CB_ROPE_PITCHED(__half, false); }
+  else { if (rotate) CB_ROPE_PITCHED(__nv_bfloat16, true); else CB_ROPE_PITCHED(__nv_bfloat16, false); }
+#undef CB_ROPE_PITCHED
+  return check_launch();
+}
+}  // namespace cb
+
 extern "C" {
 int cacti_b200_rope_tables(cacti_b200_dptr cos, cacti_b200_dptr sin, int64_t seq, int64_t head_dim, float theta,
                            int dtype, cacti_b200_stream stream) {
@@ -498,6 +633,8 @@ int cacti_b200_rope_fwd_pitched(cacti_b200_dptr y, cacti_b200_dptr x, cacti_b200
   if (!y || (head_dim > 0 && (!x || !cos || !sin)) || (y & 7) || (x & 3) || (cos & 3) || (sin & 3))
     return CACTI_B200_ERR_INVALID_VALUE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int staged = pitched_rows_staged(true, y, x, cos, sin, n_tokens, heads, head_dim, head_pitch, pos_mod, pos_offset, dtype, st);
+  if (staged >= 0) return staged;
   const int64_t units = n_tokens * heads * (head_pitch / 4);
   int64_t grid = (units + 255) / 256;
   if (grid > (int64_t)kNumSMs * 32) grid = (int64_t)kNumSMs * 32;

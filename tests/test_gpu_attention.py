@@ -22,14 +22,17 @@ pytestmark = pytest.mark.gpu
 ref_attention = R.ref_causal_attention
 
 
+@pytest.mark.parametrize("ncol,rows", [(3, 37), (32, 700)])
 @pytest.mark.parametrize("cols,cols_pad", [(100, 128), (64, 128), (7, 16), (128, 128), (30, 33)])
-def test_block_pad(cuda, cols, cols_pad):
-    x = dev(R.normal(70, (2, 37, 3, cols), np.float16))
+def test_block_pad(cuda, cols, cols_pad, ncol, rows):
+    """Rows of whole blocks that are multiples of 16 bytes take the staged kernel (32 blocks of 100: 6400-byte rows, 1400
+    of them: every ring slot is reused), the others the per-thread kernels."""
+    x = dev(R.normal(70, (2, rows, ncol, cols), np.float16))
     y = ops.block_pad(x, cols_pad)
     assert torch.equal(y[..., :cols], x) and (y[..., cols:] == 0).all()
     L = capi.lib()
-    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, 37, 3, cols, cols - 1, capi.R_16F, None) == capi.ERR_INVALID_VALUE
-    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, 37, 3, cols, cols_pad, capi.R_32F, None) == capi.ERR_DTYPE
+    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, rows, ncol, cols, cols - 1, capi.R_16F, None) == capi.ERR_INVALID_VALUE
+    assert L.cacti_b200_block_pad(y.data_ptr(), x.data_ptr(), 2, rows, ncol, cols, cols_pad, capi.R_32F, None) == capi.ERR_DTYPE
 
 
 @pytest.mark.parametrize("bsz,s,h,hd", [(1, 128, 1, 128), (2, 256, 3, 100), (1, 640, 2, 64), (2, 1024, 2, 100)])

@@ -130,10 +130,14 @@ def test_softmax_golden(cuda, case):
     assert_close(host(ds3)[keep], GOLD[f"c{case}_ds"][keep], "float16", "dS (pre-masked)")
 
 
-@pytest.mark.parametrize("heads,hd,pitch,bf16", [(32, 100, 128, False), (3, 64, 64, False), (2, 20, 32, False), (4, 100, 128, True)])
-def test_rope_fwd_pitched_equals_rope_then_pad(cuda, heads, hd, pitch, bf16):
-    """Head-pitched RoPE output = rope_fwd followed by block_pad, bit for bit; positions wrap and start at an offset."""
-    tokens, seq = 70, 32
+@pytest.mark.parametrize("tokens", [70, 2500])
+@pytest.mark.parametrize("heads,hd,pitch,bf16", [(32, 100, 128, False), (3, 64, 64, False), (2, 20, 32, False), (4, 100, 128, True),
+                                                 (1, 20, 28, False)])
+def test_rope_fwd_pitched_equals_rope_then_pad(cuda, heads, hd, pitch, bf16, tokens):
+    """Head-pitched RoPE output = rope_fwd followed by block_pad, bit for bit; positions wrap and start at an offset.
+    Token rows of a multiple of 16 bytes take the staged kernel (2500 tokens: every ring slot and output buffer of a
+    group is reused many times), the last shape (40-byte rows) the per-thread one."""
+    seq = 32
     x = dev(R.normal(95, (tokens, heads, hd), np.float32), bf16=True) if bf16 else dev(R.normal(95, (tokens, heads, hd), np.float16))
     cos, sin = ops.rope_tables(seq, hd, 10000.0, x.dtype, "cuda")
     want = ops.block_pad(ops.rope_fwd(x, cos, sin, pos_off=5).view(1, tokens, heads, hd), pitch).view(tokens, heads, pitch)
