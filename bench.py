@@ -621,8 +621,9 @@ def run_ours(args, rank, world, local_rank):
 def run_case(a):
     """One small single-kernel workload, a few launches, for a profiler (a few GB at most; inputs larger than the
     126 MB L2 so that DRAM counters mean something).  Cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16),
-    softmax_full (config 2), nll (2048 x 32000), rmsnorm (16384 x 3200), rope (16384 x 32 x 100), swiglu (4096 x 8640),
-    gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200), qk / pv / attn_fwd / attn_bwd (--batch sequences of config 5),
+    softmax_full (config 2), nll (2048 x 32000), rmsnorm (16384 x 3200), rope (16384 x 32 x 100), rope_pitched (the same
+    rows written 128 wide), block_pad (the same shape), swiglu (4096 x 8640), gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200),
+    qk / pv / attn_fwd / attn_bwd (P and dS for the block matmuls) / attn_bwd_fused (--batch sequences of config 5),
     train_step (one config-5 forward+backward over --batch sequences; only for a single-pass launch list)."""
     import torch
     from cacti_b200 import ops
@@ -660,6 +661,14 @@ def run_case(a):
         q, dq = rnd(16384, 32, 100), rnd(16384, 32, 100)
         yq, dxq = torch.empty_like(q), torch.empty_like(q)
         fn = lambda: ops.rope_fwd_bwd(q, dq, cos, sin, y=yq, dx=dxq)
+    elif case in ("rope_pitched", "block_pad"):
+        q, out = rnd(16384, 32, 100), empty(16384, 32, 128)
+        if case == "rope_pitched":
+            cos, sin = ops.rope_tables(2048, 100)
+            fn = lambda: ops.rope_fwd_pitched(q, cos, sin, 128, y=out)
+        else:
+            q4, out4 = q.view(8, 2048, 32, 100), out.view(8, 2048, 32, 128)
+            fn = lambda: ops.block_pad(q4, 128, out=out4)
     elif case == "swiglu":
         ga, up, dh = rnd(4096, 8640), rnd(4096, 8640), rnd(4096, 8640)
         h, dga, dup = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
@@ -684,7 +693,7 @@ def run_case(a):
         else:                          # dW = dy^T x
             x, w, c = rnd(m, n), rnd(m, k), empty(n, k)
             fn = lambda: ops.gemm(x, w, True, False, c=c)
-    elif case in ("qk", "pv", "attn_fwd", "attn_bwd"):
+    elif case in ("qk", "pv", "attn_fwd", "attn_bwd", "attn_bwd_fused"):
         bsz, sq, h, hd = a.batch, 2048, 32, 100
         if case == "qk":
             q, kk, c = rnd(bsz, sq, h, hd), rnd(bsz, sq, h, hd), empty(bsz, sq, h, sq)
@@ -700,9 +709,12 @@ def run_case(a):
             ctx, st = ops.attention_fwd(q, kk, v, hd, alpha)
             if case == "attn_fwd":
                 fn = lambda: ops.attention_fwd(q, kk, v, hd, alpha, ctx=ctx, stats=st)
-            else:
+            elif case == "attn_bwd":
                 pp, dss = empty(bsz, sq, h, sq), empty(bsz, sq, h, sq)
                 fn = lambda: ops.attention_bwd_prep(q, kk, v, do, ctx, st, alpha, p=pp, ds=dss)
+            else:
+                dq, dk, dv = empty(bsz, sq, h, hd), empty(bsz, sq, h, hd), empty(bsz, sq, h, hd)
+                fn = lambda: ops.attention_bwd(q, kk, v, do, ctx, st, alpha, dq=dq, dk=dk, dv=dv)
     else:
         raise SystemExit(f"unknown case {case}")
     for _ in range(a.launches):

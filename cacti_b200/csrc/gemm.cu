@@ -290,11 +290,13 @@ __device__ __forceinline__ void k_block_range(const GemmParams& p, int row0, int
 // Epilogue of one accumulator for one warp: TMEM lanes [q*32, q*32+32) x BN columns of accumulator `acc` become
 // rows row0 .. row0+31 of the output tile whose first column is tn * BN.  `tempty_addr` is the shared::cluster
 // address of the barrier that frees the accumulator: the warp arrives on it once, as soon as its last
-// tcgen05.ld has completed.
+// tcgen05.ld has completed.  `cbar` / `cpar`: this warp's barrier and phase for the TMA loads that bring the old
+// C boxes into the staging buffers when beta != 0 (Accumulate mode, src/thunk/mod.rs:347-351).
 template <typename T, int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap& tmC, T* __restrict__ C,
                                               uint32_t tmem_base, int acc, int row0, int tn, int bj, int bi, int q, int lane,
-                                              unsigned char* mybuf, uint32_t tempty_addr, const SkEpi sk = SkEpi{}) {
+                                              unsigned char* mybuf, uint32_t tempty_addr, uint64_t* cbar, unsigned& cpar,
+                                              const SkEpi sk = SkEpi{}) {
   const int prow = q * 32 + lane;             // this thread's row inside its CTA's 128 rows (partial-slot index)
   if (sk.kind == kItemContrib) {
     // this CTA's piece of a tile another worker owns: accumulator -> f32 slot (column-major, so a warp's stores of
@@ -327,6 +329,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     // TMEM -> registers -> swizzled shared staging -> TMA store (clips rows/columns past M, N)
     // 128 accumulator columns per trip: four tcgen05.ld in flight, one wait, two 64-column TMA stores
     const bool scale = p.alpha != 1.f;
+    const bool accum = p.beta != 0.f;
     constexpr int TRIPS = (BN + 127) / 128;
 #pragma unroll 1
     for (int c = 0; c < TRIPS; ++c) {
@@ -339,7 +342,17 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         if (hh * 32 < ncols)
           tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 128 + hh * 32), v[hh]);
       // both staging buffers must have been read by the stores of the previous trip
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      if (lane == 0) {
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (accum) {
+          // old C: the same boxes the stores below write, into the same (swizzled) places of the staging buffers;
+          // rows and columns past M, N arrive as zeros and are clipped again by the store
+          const bool two = col0 + 64 < p.N && ncols > 64;
+          mbar_expect_tx(cbar, two ? 8192u : 4096u);
+          tma_load_4d(mybuf, &tmC, cbar, col0, row0, bj, bi);
+          if (two) tma_load_4d(mybuf + 4096, &tmC, cbar, col0 + 64, row0, bj, bi);
+        }
+      }
       tc_ld_wait();
       if (c == TRIPS - 1 || col0 + 128 >= p.N) {         // last trip of this tile: the accumulator is free
         tc_fence_before();
@@ -361,6 +374,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
           }
         }
       }
+      if (accum) {
+        // the warp decides together: a wait that ran out leaves the tile unwritten (device error word set)
+        const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(cbar, cpar, kDevErrGemmTimeout));
+        cpar ^= 1u;
+        if (!ok) return;
+      }
 #pragma unroll
       for (int hb = 0; hb < 2; ++hb) {
         if (hb * 64 >= ncols) break;
@@ -376,7 +395,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
               t8[i] = scale ? p.alpha * a : a;
             }
             const int chunk = hh * 4 + g;       // 16-byte chunk inside the 128-byte row
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pack<T>(t8);
+            uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4));
+            if (accum && (hb == 0 || col0 + 64 < p.N)) {
+              float o8[8];
+              unpack<T>(*slot, o8);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) t8[i] = fmaf(p.beta, o8[i], t8[i]);
+            }
+            *slot = pack<T>(t8);
           }
         }
       }
@@ -471,6 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   SchedSmem* sched = reinterpret_cast<SchedSmem*>(tmem_slot + 4);
+  uint64_t* cbar = reinterpret_cast<uint64_t*>(sched + 1);        // one per epilogue warp: old C boxes have arrived
   // epilogue staging: per epilogue warp two [32 rows][64 cols] buffers in the 128-byte-swizzled layout of a
   // TMA box (4 KB each), 1024-byte aligned
   unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
@@ -481,6 +508,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
     // schedule ring: read by the MMA thread and by the four epilogue warps
     for (int i = 0; i < kSchedDepth; ++i) { mbar_init(sched->full + i, 1); mbar_init(sched->empty + i, 5); mbar_init(sched->empty_peer + i, 5); }
+    for (int w = 0; w < 4; ++w) mbar_init(cbar + w, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -591,6 +619,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- epilogue ----------------
     const int q = warp & 3;                   // TMEM lane quarter this warp may read
     long long local = 0;
+    unsigned cpar = 0;                        // phase of this warp's old-C barrier
     auto epi_tile = [&](long long tile) -> bool {
       int blk, tm, tn;
       decode_tile(tile, tiles_per_block, p, blk, tm, tn);
@@ -602,7 +631,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) return false;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kBM + q * 32, tn, bj, bi, q, lane,
-                           cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc));
+                           cstage + (size_t)(warp - 2) * 8192, smem_u32(tempty + acc), cbar + (warp - 2), cpar);
       ++local;
       return true;
     };
@@ -692,6 +721,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   SchedSmem* sched = reinterpret_cast<SchedSmem*>(tmem_slot + 4);
+  uint64_t* cbar = reinterpret_cast<uint64_t*>(sched + 1);        // one per epilogue warp: old C boxes have arrived
   unsigned char* cstage = tiles + (size_t)STAGES * STAGE_BYTES + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -703,6 +733,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // schedule ring: in the leader read by the MMA thread and four epilogue warps (empty), in the peer by the producer
     // thread and four epilogue warps, which report to the leader's empty_peer
     for (int i = 0; i < kSchedDepth; ++i) { mbar_init(sched->full + i, 1); mbar_init(sched->empty + i, 5); mbar_init(sched->empty_peer + i, 5); }
+    for (int w = 0; w < 4; ++w) mbar_init(cbar + w, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -846,6 +877,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
     const int q = warp & 3;
     long long local = 0;
+    unsigned cpar = 0;                        // phase of this warp's old-C barrier
     auto epi_item = [&](const WorkItem& wi) -> bool {
       int blk, tm, tn;
       decode_tile(wi.tile, tiles_per_block, p, blk, tm, tn);
@@ -869,7 +901,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(tfull + acc, (unsigned)((local >> 1) & 1), kDevErrGemmTimeout))) return false;
       tc_fence_after();
       epilogue_tile<T, BN>(p, tmC, C, tmem_base, acc, tm * kPairBM + (int)rank * kBM + q * 32, tn, bj, bi, q, lane,
-                           cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0), sk);
+                           cstage + (size_t)(warp - 2) * 8192, map_to_rank(smem_u32(tempty + acc), 0), cbar + (warp - 2), cpar, sk);
       ++local;
       return true;
     };
@@ -1108,12 +1140,12 @@ static int gemm_run(uint64_t c, Operand A, Operand B, bool a_mn, bool b_mn, long
             ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
   const uint64_t all = c | (uint64_t)(ldc * 2) | (uint64_t)(nbi > 1 ? csi * 2 : 0) | (uint64_t)(nbo > 1 ? cso * 2 : 0);
   p.c_align = (all & 15) == 0 ? 16 : (all & 7) == 0 ? 8 : (all & 3) == 0 ? 4 : 2;
-  // TMA store of C needs a 16-byte aligned base and strides, and no read-modify-write
+  // TMA store (and, with beta != 0, TMA load) of C needs a 16-byte aligned base and strides
   CUtensorMap tmC = tmA;
   p.c_tma = 0;
   {
     Operand Co{c, M, N, ldc, csi, cso, nbi > 1, nbo > 1};
-    if (beta == 0.f && tma_ok(Co, nbi, nbo) && (nbi == 1 || csi != 0) && (nbo == 1 || cso != 0)) {
+    if (tma_ok(Co, nbi, nbo) && (nbi == 1 || csi != 0) && (nbo == 1 || cso != 0)) {
       rc = encode_operand(&tmC, Co, nbi, nbo, 64, 32, bf16);
       if (rc) return rc;
       p.c_tma = 1;

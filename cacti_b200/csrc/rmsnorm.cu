@@ -37,8 +37,10 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
   const unsigned row_bytes = (unsigned)cols * sizeof(T);
-  const unsigned stage_bytes = row_bytes * ((BWD || ADD) ? 2 : 1);
-  // shared: [groups][nstages] stage buffers (x row, dy row) | mbarriers | reduction slots | dgamma fold [cols]
+  // Accumulate mode of the adjoint (dX += ...): the old dX row rides in the stage behind x and dy
+  const bool acc_dx = BWD && beta_dx != 0;
+  const unsigned stage_bytes = row_bytes * ((BWD || ADD) ? 2 : 1) + (acc_dx ? row_bytes : 0u);
+  // shared: [groups][nstages] stage buffers (x row, dy row[, old dx row]) | mbarriers | reduction slots | dgamma fold [cols]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * stage_bytes);
   float* red = reinterpret_cast<float*>(bars + groups * nstages);
   float* colacc = red + (size_t)2 * groups * kMaxWarpsPerGroup * 2;
@@ -69,6 +71,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
       mbar_expect_tx(bar0 + sl, stage_bytes);
       bulk_g2s(dst, X + r * cols, row_bytes, bar0 + sl);
       if (BWD) bulk_g2s(dst + row_bytes, dY + r * cols, row_bytes, bar0 + sl);
+      if (acc_dx) bulk_g2s(dst + 2 * row_bytes, dX + r * cols, row_bytes, bar0 + sl);
       if (ADD) bulk_g2s(dst + row_bytes, R + r * cols, row_bytes, bar0 + sl);
     }
   };
@@ -92,13 +95,14 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
     unsigned char* ob = outbuf0 + (size_t)(it & 1) * out_bytes;
     ++it;
     if (bulk_out && g.lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-    uint4 xraw[NV], yraw[NV];
+    uint4 xraw[NV], yraw[NV], oraw[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int col0 = (g.lane + k * G) * VEC;
       if (col0 < cols) {
         xraw[k] = *reinterpret_cast<const uint4*>(stage + (size_t)col0 * sizeof(T));
         if (BWD) yraw[k] = *reinterpret_cast<const uint4*>(stage + row_bytes + (size_t)col0 * sizeof(T));
+        if (acc_dx) oraw[k] = *reinterpret_cast<const uint4*>(stage + 2 * row_bytes + (size_t)col0 * sizeof(T));
         if (ADD) {
           float a[VEC], b[VEC];
           unpack<T>(xraw[k], a);
@@ -172,7 +176,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
             d[e] = __fmaf_rn(__fmul_rn(gm[e], gy[e]), rs, -__fmul_rn(x[e], coef));
           }
           T* o = dX + row * cols + col0;
-          if (beta_dx) st_stream(o, pack_accumulate<T>(d, ld_stream(o)));
+          if (beta_dx) st_stream(o, pack_accumulate<T>(d, oraw[k]));
           else if (bulk_out) *reinterpret_cast<uint4*>(ob + (FWD ? row_bytes : 0u) + (size_t)col0 * sizeof(T)) = pack<T>(d);
           else st_stream(o, pack<T>(d));
         }
@@ -315,7 +319,7 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
     if (pl.ok) {
       const int threads = pl.G * pl.groups;
       const int64_t want = (rows + pl.groups - 1) / pl.groups;
-      const size_t stage = (size_t)cols * sizeof(T) * ((BWD || ADD) ? 2 : 1);
+      const size_t stage = (size_t)cols * sizeof(T) * (((BWD || ADD) ? 2 : 1) + ((BWD && beta_dx) ? 1 : 0));
       // measured at [16384, 3200] f16: the forward kernels (four row groups per SM) gain from bulk stores (add + norm
       // 81 -> 75 us); the backward kernels hold two row groups per SM (registers), where the extra barrier per row
       // costs more than the stores (fused forward + backward 90 -> 99-108 us), so they keep per-thread stores
@@ -327,8 +331,10 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
                (want_bulk ? 16 + (size_t)pl.groups * 2 * out_rows * cols * sizeof(T) : 0);
       };
       // ring depth: fill about g_rmsnorm_smem_kb of shared memory per CTA, at most 8 rows per group
+      // (the accumulating adjoint stages three rows per slot and runs one CTA per SM anyway: it may take more)
+      const size_t ring_budget = (size_t)g_rmsnorm_smem_kb * 1024 * ((BWD && beta_dx) ? 3 : 2) / 2;
       int nstages = 8;
-      while (nstages > 1 && smem_for(nstages) > (size_t)g_rmsnorm_smem_kb * 1024) --nstages;
+      while (nstages > 1 && smem_for(nstages) > ring_budget) --nstages;
       const size_t smem = smem_for(nstages);
       const int bulk_out = want_bulk;
       int64_t grid = 0;

@@ -277,16 +277,16 @@ rope_staged_kernel(T* __restrict__ Y, T* __restrict__ dX, const T* __restrict__ 
   if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until read
 }
 
-// Staged form of the head-pitched forward (below), for 16-byte aligned token rows: the x row arrives by a bulk copy and
-// is rotated in place exactly as in rope_staged_kernel; the group then spreads it into an output row of `pitch`
-// elements per head (zeros after head_dim) in a second shared-memory buffer, 8 bytes per thread and step, and the
-// padded row leaves by one bulk store.  Two output buffers per group: a buffer is written again two rows later, after
-// the store that read it has finished reading.  Same bits as the per-thread kernel.
-// ROTATE = false: the copy alone, which is block_pad on rows of whole heads (pad_rows_staged below).
+// Staged form of the head-pitched forward (below), for 16-byte aligned token rows: the x row arrives by a bulk copy;
+// each thread rotates (head, unit) pairs as in rope_staged_kernel but writes them straight to their place in an output
+// row of `pitch` elements per head (the zeros after head_dim are written once, before the first row) in a second
+// shared-memory buffer, and the padded row leaves by one bulk store.  Two output buffers per group: a buffer is written
+// again two rows later, after the store that read it has finished reading.  Same bits as the per-thread kernel.
+// ROTATE = false: the copy alone (8 bytes per thread and step), which is block_pad on rows of whole heads.
 template <typename T, bool ROTATE>
 __global__ void __launch_bounds__(512)
 rope_pitched_staged_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict__ cosT, const T* __restrict__ sinT,
-                           int64_t tokens, int row_len, int hd, int pitch, int items, FastDiv fd_uh, FastDiv fd_po, int G,
+                           int64_t tokens, int row_len, int hd, int pitch, int items, FastDiv fd_uh, FastDiv fd_iu, int G,
                            int nstages, int64_t pos_mod, int64_t pos_off) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int UPV = Unit<T>::UPV;
@@ -320,14 +320,27 @@ rope_pitched_staged_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* 
     for (int sl = 0; sl < nstages; ++sl)
       if (row0 + sl * stride < tokens) issue(row0 + sl * stride, sl);
 
+  // the zeros after head_dim never change: write them once into both output buffers
+  {
+    const int tail_u8 = out_u8 - in_u8;
+    for (int u = lane; u < 2 * heads * tail_u8; u += G) {
+      const int bh = u / tail_u8;                              // buffer * heads + head
+      const int k = u - bh * tail_u8;
+      reinterpret_cast<uint2*>(out0)[(size_t)bh * out_u8 + in_u8 + k] = make_uint2(0u, 0u);
+    }
+  }
+  group_barrier(gc);
+
   int slot = 0;
   unsigned phase = 0, it = 0;
   for (int64_t row = row0; row < tokens; row += stride, ++it) {
     const bool gave_up = !mbar_wait_bounded(bar0 + slot, phase, kDevErrStageTimeout);
-    // the store of two rows back has read the output buffer this row is about to fill
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-    T* sx = reinterpret_cast<T*>(stage0 + (size_t)slot * row_bytes);
+    const T* sx = reinterpret_cast<const T*>(stage0 + (size_t)slot * row_bytes);
+    // this row's output buffer is free: lane 0 saw the store that read it finish before the previous row's barrier
+    unsigned char* ob = out0 + (size_t)(it & 1) * out_bytes;
     if (ROTATE) {
+      // rotated pairs go straight to their pitched place: no pass of their own for the spreading
+      T* so = reinterpret_cast<T*>(ob);
       const T* ct = cosT + pos * hd;
       const T* stb = sinT + pos * hd;
 #pragma unroll 5
@@ -335,30 +348,32 @@ rope_pitched_staged_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* 
         const uint32_t h = fdiv((uint32_t)n, fd_uh);
         const int i = (int)((uint32_t)n - h * fd_uh.d) * UPV;
         const int e = (int)h * hd + i;
+        const int o = (int)h * pitch + i;
         const uint32_t c1 = ldu(ct + i), c2 = ldu(ct + i + half), s1 = ldu(stb + i), s2 = ldu(stb + i + half);
-        uint32_t* p1 = reinterpret_cast<uint32_t*>(sx + e);
-        uint32_t* p2 = reinterpret_cast<uint32_t*>(sx + e + half);
-        const uint32_t x1 = *p1, x2 = *p2;
-        *p1 = rope_unit<T>(x1, x2, c1, s1, true, false);
-        *p2 = rope_unit<T>(x2, x1, c2, s2, false, false);
+        const uint32_t x1 = *reinterpret_cast<const uint32_t*>(sx + e);
+        const uint32_t x2 = *reinterpret_cast<const uint32_t*>(sx + e + half);
+        *reinterpret_cast<uint32_t*>(so + o) = rope_unit<T>(x1, x2, c1, s1, true, false);
+        *reinterpret_cast<uint32_t*>(so + o + half) = rope_unit<T>(x2, x1, c2, s2, false, false);
+      }
+    } else {
+      const uint2* in8 = reinterpret_cast<const uint2*>(sx);
+      uint2* out8 = reinterpret_cast<uint2*>(ob);
+      const int in_units = heads * in_u8;
+#pragma unroll 5
+      for (int u = lane; u < in_units; u += G) {
+        const uint32_t h = fdiv((uint32_t)u, fd_iu);             // 8-byte units per stored head
+        out8[u + (int)h * (out_u8 - in_u8)] = in8[u];
       }
     }
-    // rotation complete (and lane 0 has seen the old store finish); a wait that ran out stops the group here, together
-    if (group_any(gc, gave_up)) break;
-    unsigned char* ob = out0 + (size_t)(it & 1) * out_bytes;
-    const uint2* in8 = reinterpret_cast<const uint2*>(sx);
-    uint2* out8 = reinterpret_cast<uint2*>(ob);
-    for (int u = lane; u < out_units; u += G) {
-      const uint32_t h = fdiv((uint32_t)u, fd_po);
-      const int k = (int)((uint32_t)u - h * fd_po.d);
-      out8[u] = k < in_u8 ? in8[(int)h * in_u8 + k] : make_uint2(0u, 0u);
-    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the bulk store reads what was just written
-    group_barrier(gc);
+    // the store of the previous row has read the other buffer: the next row may fill it right after this barrier
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    // one barrier per row: output row complete, input slot read by every lane, and the vote on a wait that ran out
+    // (the group stops together, nothing is stored)
+    if (group_any(gc, gave_up)) break;
     if (lane == 0) {
       bulk_s2g(Y + row * (int64_t)heads * pitch, ob, out_bytes);
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      // every lane has read the input slot: refill it
       const int64_t next = row + (int64_t)nstages * stride;
       if (next < tokens) issue(next, slot);
     }
@@ -572,7 +587,7 @@ int pitched_rows_staged(bool rotate, uint64_t y, uint64_t x, uint64_t cos, uint6
     if (grid_s > want) grid_s = want;                                                                                         \
     kern<<<(unsigned)grid_s, threads_s, smem, st>>>(reinterpret_cast<T_*>(y), reinterpret_cast<const T_*>(x),                 \
         reinterpret_cast<const T_*>(cos), reinterpret_cast<const T_*>(sin), n_tokens, (int)row_len, (int)head_dim,            \
-        (int)head_pitch, (int)items, make_fastdiv((uint32_t)((head_dim / 2) / 2)), make_fastdiv((uint32_t)(head_pitch / 4)),  \
+        (int)head_pitch, (int)items, make_fastdiv((uint32_t)((head_dim / 2) / 2)), make_fastdiv((uint32_t)(head_dim / 4)),  \
         G, nst, pos_mod, pos_offset);                                                                                         \
   } while (0)
   if (dtype == CACTI_B200_R_16F) { if (rotate) CB_ROPE_PITCHED(__half, true); else CB_ROPE_PITCHED(__half, false); }

@@ -53,6 +53,24 @@ def test_gemm_views_and_bf16(cuda):
     assert_close(host(c), ref, "bfloat16", "bf16 gemm", floor_frac=1.0)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 264, 200), (1000, 3200, 512)])
+def test_gemm_accumulate_epilogues_agree(cuda, m, n, k):
+    """beta = 1 through the two epilogues: old C brought in by TMA (aligned C) and read per thread (C a view whose row
+    pitch is not a multiple of 16 bytes) must give the same bits; both against the oracle."""
+    a, b = _stored(31, m, k, False), _stored(32, k, n, True, 0.1)
+    old = R.normal(33, (m, n), np.float16)
+    c_tma = dev(old)
+    ops.gemm(dev(a), dev(b), False, True, alpha=0.5, beta=1.0, c=c_tma)
+    wide = torch.zeros(m, n + 3, dtype=torch.float16, device="cuda")
+    c_view = wide[:, 1:n + 1]
+    c_view.copy_(dev(old))
+    ops.gemm(dev(a), dev(b), False, True, alpha=0.5, beta=1.0, c=c_view)
+    assert torch.equal(c_tma, c_view.contiguous())
+    assert_close(host(c_tma), R.ref_gemm(a, b, False, True, alpha=0.5, beta=1.0, c=old), "float16", "gemm beta=1 (TMA epilogue)",
+                 floor_frac=1.0)
+    assert float(wide[:, 0].abs().max()) == 0.0 and float(wide[:, n + 1:].abs().max()) == 0.0      # nothing outside the view
+
+
 @pytest.fixture
 def pair_tiles():
     """Force 256-wide tiles, which run as two-SM (cta_group::2) 256 x 256 tiles, for the duration of a test."""
