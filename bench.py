@@ -623,7 +623,8 @@ def run_case(a):
     126 MB L2 so that DRAM counters mean something).  Cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16),
     softmax_full (config 2), nll (2048 x 32000), rmsnorm (16384 x 3200), rope (16384 x 32 x 100), rope_pitched (the same
     rows written 128 wide), block_pad (the same shape), swiglu (4096 x 8640), gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200),
-    qk / pv / attn_fwd / attn_bwd (P and dS for the block matmuls) / attn_bwd_fused (--batch sequences of config 5),
+    qk / pv / ds_k / dst_q (block matmuls of the unfused step and of the attention adjoint) / attn_fwd / attn_bwd (P and dS for
+    the block matmuls) / attn_bwd_fused (--batch sequences of config 5),
     train_step (one config-5 forward+backward over --batch sequences; only for a single-pass launch list)."""
     import torch
     from cacti_b200 import ops
@@ -693,7 +694,7 @@ def run_case(a):
         else:                          # dW = dy^T x
             x, w, c = rnd(m, n), rnd(m, k), empty(n, k)
             fn = lambda: ops.gemm(x, w, True, False, c=c)
-    elif case in ("qk", "pv", "attn_fwd", "attn_bwd", "attn_bwd_fused"):
+    elif case in ("qk", "pv", "ds_k", "dst_q", "attn_fwd", "attn_bwd", "attn_bwd_fused"):
         bsz, sq, h, hd = a.batch, 2048, 32, 100
         if case == "qk":
             q, kk, c = rnd(bsz, sq, h, hd), rnd(bsz, sq, h, hd), empty(bsz, sq, h, sq)
@@ -703,6 +704,14 @@ def run_case(a):
             pr, v, c = rnd(bsz, sq, h, sq, scale=0.02), rnd(bsz, sq, h, hd), empty(bsz, sq, h, hd)
             ws = torch.empty(ops.lib().cacti_b200_gemm_workspace_bytes(sq, hd, sq, bsz, h), dtype=torch.uint8, device="cuda")
             fn = lambda: ops.block_gemm(pr, v, False, False, c=c, workspace=ws)
+        elif case in ("ds_k", "dst_q"):   # dq = dS K and dk = dS^T Q of the attention adjoint: hinted, operand padded to 128
+            from cacti_b200 import capi
+            dsm = torch.tril(rnd(bsz, sq, h, sq, scale=0.02).permute(0, 2, 1, 3)).permute(0, 2, 1, 3).contiguous()
+            kp, c = ops.block_pad(rnd(bsz, sq, h, hd), 128), empty(bsz, sq, h, hd)
+            if case == "ds_k":
+                fn = lambda: ops.block_gemm(dsm, kp, False, False, alpha=0.1, c=c, tri=capi.TRI_A_LOWER, b_valid=hd)
+            else:
+                fn = lambda: ops.block_gemm(dsm, kp, True, False, alpha=0.1, c=c, tri=capi.TRI_A_UPPER, b_valid=hd)
         else:
             alpha = hd ** -0.5
             q, kk, v, do = (ops.block_pad(rnd(bsz, sq, h, hd), 128) for _ in range(4))

@@ -25,6 +25,7 @@ Layout: activations [T, D] = [B, S, H, hd]; scores [B, S, H, S] as in the refere
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -62,10 +63,33 @@ def init_weights(cfg: LlamaShape, device, seed=0, std=0.02, dtype=torch.float16)
     D, F, V = cfg.d_model, cfg.ffn, cfg.vocab
     P = {"embed": w(V, D), "lm_head": w(V, D), "head_norm": torch.ones(D, device=device, dtype=dtype), "layers": []}
     for _ in range(cfg.layers):
-        P["layers"].append({"pre_norm": torch.ones(D, device=device, dtype=dtype), "q": w(D, D), "k": w(D, D),
-                            "v": w(D, D), "o": w(D, D), "post_norm": torch.ones(D, device=device, dtype=dtype),
-                            "up": w(F, D), "gate": w(F, D), "down": w(D, F)})
+        L = {"pre_norm": torch.ones(D, device=device, dtype=dtype), "q": w(D, D), "k": w(D, D),
+             "v": w(D, D), "o": w(D, D), "post_norm": torch.ones(D, device=device, dtype=dtype),
+             "up": w(F, D), "gate": w(F, D), "down": w(D, F)}
+        # one flat buffer per layer, laid out like the gradient buckets of dp.alloc_bucketed_grads: q, k and v are
+        # then adjacent, which lets the step run their three projections as one batched matmul
+        flat = torch.empty(sum((t.numel() + 127) // 128 * 128 for t in L.values()), dtype=dtype, device=device)
+        off = 0
+        for name, t in L.items():
+            L[name] = flat[off:off + t.numel()].view(t.shape).copy_(t)
+            off += (t.numel() + 127) // 128 * 128
+        P["layers"].append(L)
     return P
+
+
+def stacked(*ts):
+    """[n, rows, 1, cols] view over n equal 2-d tensors that lie back to back in memory (None when they do not): the
+    4-d block layout of the batched matmul, one block row per tensor."""
+    t0 = ts[0]
+    if os.environ.get("CACTI_B200_NO_STACK") == "1":         # A/B switch: always the separate launches
+        return None
+    if any(t.shape != t0.shape or t.dtype != t0.dtype or not t.is_contiguous() or
+           t.untyped_storage().data_ptr() != t0.untyped_storage().data_ptr() for t in ts):
+        return None                                          # (neighbours by accident of the allocator do not count)
+    step = t0.numel() * t0.element_size()
+    if any(t.data_ptr() != t0.data_ptr() + i * step for i, t in enumerate(ts)):
+        return None
+    return torch.as_strided(t0, (len(ts), t0.shape[0], 1, t0.shape[1]), (t0.numel(), t0.shape[1], t0.shape[1], 1))
 
 
 def zeros_like_params(P):
@@ -120,9 +144,19 @@ class TrainStep:
         self.launches += 1
         return ops.gemm(a, b, ta, tb, beta=beta, c=c, workspace=self.mm_ws)
 
-    def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0, b_valid=None):
+    def _bmm(self, a, b, ta, tb, alpha=1.0, tri=0, b_valid=None, c=None):
         self.launches += 3 if b_valid is None else 1       # unaligned operands are repacked first; padded ones are not
-        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws, tri=tri, b_valid=b_valid)
+        return ops.block_gemm(a, b, ta, tb, alpha=alpha, workspace=self.gemm_ws, tri=tri, b_valid=b_valid, c=c)
+
+    def _mm_stack(self, a, b, ta, tb, c):
+        """One batched launch for matmuls that share an operand (given as a 2-d tensor, broadcast) and whose other operand
+        and result are `stacked` views.  Same tiles and the same k order as the separate launches, hence the same bits;
+        what changes is the tile count of the launch: 3 x 169 tiles of 256 x 256 fill 74 SM pairs for 6.85 waves, where
+        169 alone fill 2.28 (the third wave a quarter full)."""
+        self.launches += 1
+        a4 = a if a.dim() == 4 else a.view(1, a.shape[0], 1, a.shape[1])
+        b4 = b if b.dim() == 4 else b.view(1, b.shape[0], 1, b.shape[1])
+        return ops.block_gemm(a4, b4, ta, tb, workspace=self.gemm_ws, c=c)
 
     def forward_backward(self, tokens, targets, grads, on_layer_done=None):
         cfg, P, B, T = self.cfg, self.P, self.B, self.T
@@ -142,19 +176,26 @@ class TrainStep:
                 n1 = ops.rmsnorm_fwd(x, Lw["pre_norm"], cfg.eps)
             else:
                 n1, x = ops.add_rmsnorm_fwd(x, branch, Lw["pre_norm"], cfg.eps)
+            w_qkv = stacked(Lw["q"], Lw["k"], Lw["v"])
+            if w_qkv is not None:                         # the three projections of n1 as one batched matmul
+                qkv = torch.empty(3, T, D, dtype=n1.dtype, device=n1.device)
+                self._mm_stack(n1, w_qkv, False, True, qkv.view(3, T, 1, D))
+                q_lin, k_lin, v_lin = qkv[0], qkv[1], qkv[2]
+            else:
+                q_lin, k_lin, v_lin = (self._mm(n1, Lw[name], False, True) for name in ("q", "k", "v"))
             if self.fused:
                 # q, k, v with the head dimension zero-padded to 128 (RoPE writes q and k that way directly); the
                 # padded copies also serve the backward pass
-                q = ops.rope_fwd_pitched(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
-                k = ops.rope_fwd_pitched(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
-                v = ops.block_pad(self._mm(n1, Lw["v"], False, True).view(B, S, H, hd), 128)
+                q = ops.rope_fwd_pitched(q_lin.view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
+                k = ops.rope_fwd_pitched(k_lin.view(T, H, hd), self.cos, self.sin, 128).view(B, S, H, 128)
+                v = ops.block_pad(v_lin.view(B, S, H, hd), 128)
                 ctx, sc = ops.attention_fwd(q, k, v, hd, alpha)               # sc: the row statistics (m, l)
                 ctx = ctx.view(T, D)
                 self.launches += 2
             else:
-                q = ops.rope_fwd(self._mm(n1, Lw["q"], False, True).view(T, H, hd), self.cos, self.sin)
-                k = ops.rope_fwd(self._mm(n1, Lw["k"], False, True).view(T, H, hd), self.cos, self.sin)
-                v = self._mm(n1, Lw["v"], False, True)
+                q = ops.rope_fwd(q_lin.view(T, H, hd), self.cos, self.sin)
+                k = ops.rope_fwd(k_lin.view(T, H, hd), self.cos, self.sin)
+                v = v_lin
                 sc = self._bmm(q.view(B, S, H, hd), k.view(B, S, H, hd), False, True, alpha, TRI_C_LOWER)   # [B,S,H,S]
                 p = ops.softmax_fwd(sc.view(B * S * H, S), mask)
                 ctx = self._bmm(p.view(B, S, H, S), v.view(B, S, H, hd), False, False, tri=TRI_A_LOWER).view(T, D)
@@ -202,10 +243,15 @@ class TrainStep:
             # attention branch: x_mid = x_in + ctx Wo^T
             self._mm(dx, ctx, True, False, c=G["o"])
             dctx = self._mm(dx, Lw["o"], False, False)
+            # dq, dk and dv are written into one [3, T, D] buffer when the q, k, v gradients lie back to back, so that
+            # the three weight-gradient matmuls below can run as one batched launch
+            g_qkv = stacked(G["q"], G["k"], G["v"])
+            dqkv = torch.empty(3, T, D, dtype=dx.dtype, device=dx.device) if g_qkv is not None else None
+            dv_out = dqkv[2].view(B, S, H, hd) if dqkv is not None else None
             if self.fused_bwd:
                 # dq, dk, dv straight from q, k, v (the padded copies), dctx and the row statistics
                 dctx = ops.block_pad(dctx.view(B, S, H, hd), 128)
-                dq, dk, dv = ops.attention_bwd(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha)
+                dq, dk, dv = ops.attention_bwd(q, k, v, dctx, ctx.view(B, S, H, hd), sc, alpha, dv=dv_out)
                 dq, dk, dv = dq.view(T, H, hd), dk.view(T, H, hd), dv.view(T, D)
                 del dctx, sc
                 self.launches += 4
@@ -224,16 +270,21 @@ class TrainStep:
                 dctx, q, k, bv = dctx.view(B, S, H, hd), q.view(B, S, H, hd), k.view(B, S, H, hd), None
             if not self.fused_bwd:
                 del sc
-                dv = self._bmm(p.view(B, S, H, S), dctx, True, False, tri=TRI_A_UPPER, b_valid=bv).view(T, D)      # P^T dctx
+                dv = self._bmm(p.view(B, S, H, S), dctx, True, False, tri=TRI_A_UPPER, b_valid=bv, c=dv_out).view(T, D)   # P^T dctx
                 del p, dctx
                 dq = self._bmm(ds.view(B, S, H, S), k, False, False, alpha, TRI_A_LOWER, b_valid=bv)               # dS K
                 dk = self._bmm(ds.view(B, S, H, S), q, True, False, alpha, TRI_A_UPPER, b_valid=bv)                # dS^T Q
                 del ds
-            dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
-            dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)
-            self._mm(dq, n1, True, False, c=G["q"])
-            self._mm(dk, n1, True, False, c=G["k"])
-            self._mm(dv, n1, True, False, c=G["v"])
+            if dqkv is not None:
+                dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin, dx=dqkv[0].view(T, H, hd)).view(T, D)
+                dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin, dx=dqkv[1].view(T, H, hd)).view(T, D)
+                self._mm_stack(dqkv.view(3, T, 1, D), n1, True, False, g_qkv)
+            else:
+                dq = ops.rope_bwd(dq.view(T, H, hd), self.cos, self.sin).view(T, D)
+                dk = ops.rope_bwd(dk.view(T, H, hd), self.cos, self.sin).view(T, D)
+                self._mm(dq, n1, True, False, c=G["q"])
+                self._mm(dk, n1, True, False, c=G["k"])
+                self._mm(dv, n1, True, False, c=G["v"])
             dn1 = self._mm(dq, Lw["q"], False, False)
             self._mm(dk, Lw["k"], False, False, c=dn1, beta=1.0)
             self._mm(dv, Lw["v"], False, False, c=dn1, beta=1.0)

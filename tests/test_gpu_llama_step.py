@@ -105,3 +105,33 @@ def test_graphed_step_replays_the_eager_step(cuda):
         for (_, g), ref in zip(LS.flat_params(grads), eager[i][1]):
             assert np.array_equal(host(g), ref)
     assert host(step.status)[0] == 0
+
+
+def test_batched_qkv_matmuls_give_the_same_bits(cuda):
+    """q, k and v projections (and their weight gradients) run as one batched matmul when the three weights (gradients)
+    lie back to back in memory, as init_weights and dp.alloc_bucketed_grads lay them out; separately otherwise.  Both
+    ways must give the same loss and gradients, bit for bit."""
+    from cacti_b200 import dp as DP
+    cfg = LS.LlamaShape(layers=2, d_model=256, heads=2, head_dim=128, ffn=128, vocab=160, seq=128)
+    B = 2
+    P = LS.init_weights(cfg, cuda, seed=5, std=0.08)
+    assert LS.stacked(P["layers"][0]["q"], P["layers"][0]["k"], P["layers"][0]["v"]) is not None
+    P_apart = {k: v.clone() for k, v in P.items() if k != "layers"}
+    P_apart["layers"] = [{k: torch.cat([v.reshape(-1), v.new_zeros(8)])[:v.numel()].view(v.shape) for k, v in L.items()}
+                         for L in P["layers"]]
+    assert LS.stacked(P_apart["layers"][0]["q"], P_apart["layers"][0]["k"], P_apart["layers"][0]["v"]) is None
+    tok, tgt = dev(R.uniform_int(3, B * cfg.seq, cfg.vocab)), dev(R.uniform_int(4, B * cfg.seq, cfg.vocab))
+    res = []
+    for params, bucketed in ((P, True), (P_apart, False)):
+        grads = DP.alloc_bucketed_grads(params)[0] if bucketed else LS.zeros_like_params(params)
+        G0 = grads["layers"][0]
+        assert (LS.stacked(G0["q"], G0["k"], G0["v"]) is not None) == bucketed
+        step = LS.TrainStep(cfg, params, B)
+        loss = step.forward_backward(tok, tgt, grads)
+        torch.cuda.synchronize()
+        assert host(step.status)[0] == 0
+        res.append((host(loss).copy(), [host(g).copy() for _, g in LS.flat_params(grads)], step.launches))
+    assert np.array_equal(res[0][0], res[1][0])
+    for a, b in zip(res[0][1], res[1][1]):
+        assert np.array_equal(a, b)
+    assert res[0][2] == res[1][2] - 4 * cfg.layers           # two launches instead of six per layer
