@@ -621,11 +621,12 @@ def run_ours(args, rank, world, local_rank):
 def run_case(a):
     """One small single-kernel workload, a few launches, for a profiler (a few GB at most; inputs larger than the
     126 MB L2 so that DRAM counters mean something).  Cases: softmax (causal fwd+bwd, 8 heads x 2048 x 2048 f16),
-    softmax_full (config 2), nll (2048 x 32000), rmsnorm (16384 x 3200), rope (16384 x 32 x 100), rope_pitched (the same
-    rows written 128 wide), block_pad (the same shape), swiglu (4096 x 8640), gemm_nt / gemm_nn / gemm_tn (4096 x 3200 x 3200),
-    qk / pv / ds_k / dst_q (block matmuls of the unfused step and of the attention adjoint) / attn_fwd / attn_bwd (P and dS for
-    the block matmuls) / attn_bwd_fused (--batch sequences of config 5),
-    train_step (one config-5 forward+backward over --batch sequences; only for a single-pass launch list)."""
+    softmax_full (config 2), nll (2048 x 32000), rmsnorm / rmsnorm_bwd_acc (16384 x 3200), rope (16384 x 32 x 100),
+    rope_pitched (the same rows written 128 wide), block_pad (the same shape), swiglu (4096 x 8640),
+    gemm_nt / gemm_nn / gemm_tn / gemm_nn_acc (4096 x 3200 x 3200), qk / pv / ds_k / dst_q (block matmuls of the
+    unfused step and of the attention adjoint), attn_fwd / attn_bwd (P and dS for the block matmuls) / attn_bwd_fused
+    (--batch sequences of config 5), train_step (one config-5 forward+backward over --batch sequences; only for a
+    single-pass launch list)."""
     import torch
     from cacti_b200 import ops
     for kv in a.tune:
@@ -683,6 +684,15 @@ def run_case(a):
         tok = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
         tgt = torch.randint(0, cfg.vocab, (a.batch * cfg.seq,), device="cuda", dtype=torch.int32, generator=gen)
         fn = lambda: step.forward_backward(tok, tgt, grads)
+    elif case == "rmsnorm_bwd_acc":        # the adjoint in Accumulate mode (dX += ...), as every norm of the step runs it
+        x, dy, g = rnd(16384, 3200), rnd(16384, 3200), rnd(3200)
+        dx, dg = rnd(16384, 3200), empty(3200)
+        ws = ops.rmsnorm_workspace(16384, 3200, x.device)
+        fn = lambda: ops.rmsnorm_bwd(x, g, dy, 1e-6, dx=dx, dgamma=dg, beta_dx=1, workspace=ws)
+    elif case == "gemm_nn_acc":            # dx += dy W (beta = 1): old C comes in by TMA
+        m, n, k = 4096, 3200, 3200
+        x, w, c = rnd(m, n), rnd(n, k, scale=0.02), rnd(m, k)
+        fn = lambda: ops.gemm(x, w, False, False, beta=1.0, c=c)
     elif case in ("gemm_nt", "gemm_nn", "gemm_tn"):
         m, n, k = 4096, 3200, 3200
         if case == "gemm_nt":          # y = x W^T (forward projection)

@@ -561,27 +561,32 @@ attention_bwd_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           if (lane == 0) mbar_arrive(t_empty + sl);
         }
         uint4 pc[4], dc[4];
+        // two bodies, chosen per tile: only the tile on the diagonal carries the compares and selects of the mask
+        auto quarter_math = [&](auto diag_tag) {
+          constexpr bool DIAG = decltype(diag_tag)::value;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t pw[4], dw[4];
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pw[4], dw[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int idx = g * 8 + i * 2;
-            const float2 s2 = rounded_scores<T>(p.alpha, sv[idx], sv[idx + 1]);
-            const float2 g2 = rounded_pair<T>(gv[idx], gv[idx + 1]);
-            float y0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
-            float y1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
-            if (j == qi) {
-              const int c = qt * 32 + idx;
-              if (c > r) y0 = 0.f;
-              if (c + 1 > r) y1 = 0.f;
+            for (int i = 0; i < 4; ++i) {
+              const int idx = g * 8 + i * 2;
+              const float2 s2 = rounded_scores<T>(p.alpha, sv[idx], sv[idx + 1]);
+              const float2 g2 = rounded_pair<T>(gv[idx], gv[idx + 1]);
+              float y0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+              float y1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
+              if (DIAG) {
+                const int c = qt * 32 + idx;
+                if (c > r) y0 = 0.f;
+                if (c + 1 > r) y1 = 0.f;
+              }
+              pw[i] = pack2<T>(y0, y1);
+              dw[i] = pack2<T>(__fmaf_rn(y0, g2.x, -__fmul_rn(cdot, y0)), __fmaf_rn(y1, g2.y, -__fmul_rn(cdot, y1)));
             }
-            pw[i] = pack2<T>(y0, y1);
-            dw[i] = pack2<T>(__fmaf_rn(y0, g2.x, -__fmul_rn(cdot, y0)), __fmaf_rn(y1, g2.y, -__fmul_rn(cdot, y1)));
+            pc[g] = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+            dc[g] = make_uint4(dw[0], dw[1], dw[2], dw[3]);
           }
-          pc[g] = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-          dc[g] = make_uint4(dw[0], dw[1], dw[2], dw[3]);
-        }
+        };
+        if (j == qi) quarter_math(std::true_type{}); else quarter_math(std::false_type{});
         store_quarter(pc, dc, j * kAttnRows + qt * 32);
       }
     }

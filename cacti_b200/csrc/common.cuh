@@ -65,11 +65,15 @@ template <> struct Elem<float> {
 };
 template <> struct Elem<__half> {
   static constexpr int VEC = 8;
+  using Pair = __half2;
+  static __device__ __forceinline__ __half2 pair_neg_inf() { return __half2half2(__ushort_as_half((unsigned short)0xfc00)); }
   static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
 };
 template <> struct Elem<__nv_bfloat16> {
   static constexpr int VEC = 8;
+  using Pair = __nv_bfloat162;
+  static __device__ __forceinline__ __nv_bfloat162 pair_neg_inf() { return __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0xff80)); }
   static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
 };
@@ -303,13 +307,21 @@ template <typename Op> __device__ __forceinline__ float block_reduce(float v, fl
 
 // exp in f32.  16-bit storage: ex2.approx (relative error ~1e-6, far below the storage
 // rounding).  f32 storage: the accurate library exp, so fp32 results stay within 1e-5 relative.
-template <typename T> __device__ __forceinline__ float exp_for(float x) { return __expf(x); }
-template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
-
 __device__ __forceinline__ float exp2f_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+template <typename T> __device__ __forceinline__ float exp_for(float x) { return exp2f_approx(x * 1.4426950408889634f); }
+template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
+
+// exp(a - m) as one FFMA and one MUFU: ex2(a*log2e - m*log2e), neg_m_log2e = -m * log2e formed once per row.  Used for
+// 16-bit storage, where its ~1e-6 relative error is far below the storage rounding; f32 storage uses the accurate
+// expf.  (__expf without flush-to-zero costs a compare and two predicated multiplies around the MUFU for the
+// subnormal range, which a result that is rounded to 16 bits never shows.)
+template <typename T> __device__ __forceinline__ float exp_shifted(float a, float m, float neg_m_log2e) {
+  if constexpr (std::is_same<T, float>::value) return expf(a - m);
+  else return exp2f_approx(__fmaf_rn(a, 1.4426950408889634f, neg_m_log2e));
 }
 
 template <typename F> inline int dispatch_dtype(int dtype, F&& f) {

@@ -112,17 +112,36 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
 
     // pass 1: row maximum
     float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+    if constexpr (std::is_same<T, float>::value) {
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int col0 = (g.lane + k * G) * VEC;
-      if (col0 < cur_active) {
-        float a[VEC];
-        unpack<T>(sraw[k], a);
+      for (int k = 0; k < NV; ++k) {
+        const int col0 = (g.lane + k * G) * VEC;
+        if (col0 < cur_active) {
+          float a[VEC];
+          unpack<T>(sraw[k], a);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[e]);
+          for (int e = 0; e < VEC; ++e) mq[e & 3] = fmaxf(mq[e & 3], a[e]);
+        }
       }
+    } else {
+      // 16-bit storage: the maximum is exact in the storage type, so it is taken on the packed pairs (one
+      // instruction per two elements, no conversion) and widened once
+      using H2 = typename Elem<T>::Pair;
+      H2 hq[2] = {Elem<T>::pair_neg_inf(), Elem<T>::pair_neg_inf()};
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int col0 = (g.lane + k * G) * VEC;
+        if (col0 < cur_active) {
+          const H2* h = reinterpret_cast<const H2*>(&sraw[k]);
+          hq[0] = __hmax2(hq[0], h[0]); hq[1] = __hmax2(hq[1], h[1]);
+          hq[0] = __hmax2(hq[0], h[2]); hq[1] = __hmax2(hq[1], h[3]);
+        }
+      }
+      const H2 hm = __hmax2(hq[0], hq[1]);
+      mq[0] = Elem<T>::to_f32(hm.x); mq[1] = Elem<T>::to_f32(hm.y);
     }
     float m = group_reduce<MaxOp>(g, fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])));
+    const float nml2e = __fmul_rn(-m, 1.4426950408889634f);
     // pass 2: Z = sum exp(a - m); cg = sum exp(a - m) * g  (sum_j y_j g_j = cg / Z)
     float zq[4] = {0.f, 0.f, 0.f, 0.f}, cq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -134,7 +153,7 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
         if (BWD) unpack<T>(graw[k], gv);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float ex = exp_for<T>(a[e] - m);
+          const float ex = exp_shifted<T>(a[e], m, nml2e);
           zq[e & 3] = __fadd_rn(zq[e & 3], ex);
           if (BWD) cq[e & 3] = __fmaf_rn(ex, gv[e], cq[e & 3]);
         }
@@ -162,7 +181,7 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
           if (BWD) unpack<T>(graw[k], gv);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            const float ex = exp_for<T>(a[e] - m);
+            const float ex = exp_shifted<T>(a[e], m, nml2e);
             y[e] = std::is_same<T, float>::value ? __fdiv_rn(ex, z) : __fmul_rn(ex, rz);
             if (BWD) d[e] = __fmaf_rn(y[e], gv[e], -__fmul_rn(c, y[e]));
           }
@@ -200,9 +219,10 @@ softmax_rows_generic_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __re
     float m = -INFINITY;
     for (int64_t j = threadIdx.x; j < active; j += blockDim.x) m = fmaxf(m, Elem<T>::to_f32(srow[j]));
     m = block_reduce<MaxOp>(m, sm);
+    const float nml2e = __fmul_rn(-m, 1.4426950408889634f);
     float z = 0.f, cg = 0.f;
     for (int64_t j = threadIdx.x; j < active; j += blockDim.x) {
-      const float ex = exp_for<T>(Elem<T>::to_f32(srow[j]) - m);
+      const float ex = exp_shifted<T>(Elem<T>::to_f32(srow[j]), m, nml2e);
       z += ex;
       if (BWD) cg = fmaf(ex, Elem<T>::to_f32(dP[row * cols + j]), cg);
     }
@@ -213,7 +233,7 @@ softmax_rows_generic_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __re
     for (int64_t j = threadIdx.x; j < wcols; j += blockDim.x) {
       float y = fill, d = fill;
       if (j < active) {
-        const float ex = exp_for<T>(Elem<T>::to_f32(srow[j]) - m);
+        const float ex = exp_shifted<T>(Elem<T>::to_f32(srow[j]), m, nml2e);
         y = std::is_same<T, float>::value ? ex / z : ex * rz;
         if (BWD) d = y * Elem<T>::to_f32(dP[row * cols + j]) - c * y;
       }

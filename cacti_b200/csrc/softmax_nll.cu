@@ -28,13 +28,6 @@ template <> __device__ __forceinline__ int64_t load_index<uint16_t>(const void* 
   return (int64_t) reinterpret_cast<const uint16_t*>(p)[i];
 }
 
-// exp(a - m) as one FFMA and one MUFU: ex2(a*log2e - m*log2e).  Used for 16-bit storage, where its
-// ~1e-6 relative error is far below the storage rounding; f32 storage uses the accurate expf.
-template <typename T> __device__ __forceinline__ float exp_shifted(float a, float m, float neg_m_log2e) {
-  if constexpr (std::is_same<T, float>::value) return expf(a - m);
-  else return exp2f_approx(__fmaf_rn(a, 1.4426950408889634f, neg_m_log2e));
-}
-
 // exp(d) for the (max, sum) combine: d <= 0 or -inf.
 template <typename T> __device__ __forceinline__ float exp_rescale(float d) {
   if constexpr (std::is_same<T, float>::value) return expf(d);
