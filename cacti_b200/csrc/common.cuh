@@ -65,17 +65,24 @@ template <> struct Elem<float> {
 };
 template <> struct Elem<__half> {
   static constexpr int VEC = 8;
-  using Pair = __half2;
-  static __device__ __forceinline__ __half2 pair_neg_inf() { return __half2half2(__ushort_as_half((unsigned short)0xfc00)); }
   static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
 };
 template <> struct Elem<__nv_bfloat16> {
   static constexpr int VEC = 8;
-  using Pair = __nv_bfloat162;
-  static __device__ __forceinline__ __nv_bfloat162 pair_neg_inf() { return __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0xff80)); }
   static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Packed pair of a 16-bit type (float has none: code that uses it sits behind `if constexpr`).
+template <typename T> struct Pair16 { using type = float2; static __device__ __forceinline__ float2 neg_inf() { return make_float2(0.f, 0.f); } };
+template <> struct Pair16<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ __half2 neg_inf() { return __half2half2(__ushort_as_half((unsigned short)0xfc00)); }
+};
+template <> struct Pair16<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ __nv_bfloat162 neg_inf() { return __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0xff80)); }
 };
 
 // Round an f32 value to T and back: the rounding point of a primitive thunk whose output cell is T.
@@ -312,7 +319,7 @@ __device__ __forceinline__ float exp2f_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-template <typename T> __device__ __forceinline__ float exp_for(float x) { return exp2f_approx(x * 1.4426950408889634f); }
+template <typename T> __device__ __forceinline__ float exp_for(float x) { return __expf(x); }
 template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
 
 // exp(a - m) as one FFMA and one MUFU: ex2(a*log2e - m*log2e), neg_m_log2e = -m * log2e formed once per row.  Used for

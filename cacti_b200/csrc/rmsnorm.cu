@@ -25,20 +25,21 @@ constexpr int kRmsMaxPartials = kNumSMs * 8;
 
 // ADD (forward only): the normalised row is T(X + R), the residual add that precedes every norm of the decoder
 // layer (src/librarium/llama.rs:514,533); the rounded sum is also written to SUM.  The second stage row then holds R.
-template <typename T, int NV, bool FWD, bool BWD, bool ADD = false>
+template <typename T, int NV, bool FWD, bool BWD, bool ADD = false, bool ACC = false>
 __global__ void __launch_bounds__(512)
 rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ partial,
                     const T* __restrict__ X, const T* __restrict__ gamma, const T* __restrict__ dY,
                     float eps, int64_t rows, int cols, int G, int nstages, int beta_dx,
                     const T* __restrict__ R = nullptr, T* __restrict__ SUM = nullptr, int bulk_out_arg = 0) {
   static_assert(!ADD || (FWD && !BWD), "the residual add is fused into the forward norm only");
+  static_assert(!ACC || BWD, "ACC is the Accumulate mode of the adjoint");
   const int bulk_out = BWD ? 0 : bulk_out_arg;      // the backward kernels carry no bulk-store code (see launch_rmsnorm)
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int VEC = Elem<T>::VEC;
   const int groups = blockDim.x / G;
   const unsigned row_bytes = (unsigned)cols * sizeof(T);
   // Accumulate mode of the adjoint (dX += ...): the old dX row rides in the stage behind x and dy
-  const bool acc_dx = BWD && beta_dx != 0;
+  constexpr bool acc_dx = ACC;          // (a kernel of its own: the overwrite forms keep their code and registers)
   const unsigned stage_bytes = row_bytes * ((BWD || ADD) ? 2 : 1) + (acc_dx ? row_bytes : 0u);
   // shared: [groups][nstages] stage buffers (x row, dy row[, old dx row]) | mbarriers | reduction slots | dgamma fold [cols]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)groups * nstages * stage_bytes);
@@ -176,7 +177,7 @@ rmsnorm_rows_kernel(T* __restrict__ Y, T* __restrict__ dX, float* __restrict__ p
             d[e] = __fmaf_rn(__fmul_rn(gm[e], gy[e]), rs, -__fmul_rn(x[e], coef));
           }
           T* o = dX + row * cols + col0;
-          if (beta_dx) st_stream(o, pack_accumulate<T>(d, oraw[k]));
+          if (acc_dx) st_stream(o, pack_accumulate<T>(d, oraw[k]));
           else if (bulk_out) *reinterpret_cast<uint4*>(ob + (FWD ? row_bytes : 0u) + (size_t)col0 * sizeof(T)) = pack<T>(d);
           else st_stream(o, pack<T>(d));
         }
@@ -340,7 +341,8 @@ static int launch_rmsnorm(uint64_t y, uint64_t dx, uint64_t dgamma, uint64_t x, 
       int64_t grid = 0;
 #define CB_LAUNCH(NV_)                                                                                      \
   do {                                                                                                      \
-    auto kern = rmsnorm_rows_kernel<T, NV_, FWD, BWD, ADD>;                                                 \
+    auto kern = (BWD && beta_dx) ? rmsnorm_rows_kernel<T, NV_, FWD, BWD, ADD, BWD>                          \
+                                 : rmsnorm_rows_kernel<T, NV_, FWD, BWD, ADD, false>;                       \
     grid = (int64_t)kNumSMs * resident_ctas(kern, threads, smem);                                           \
     if (grid > max_partials) grid = max_partials;                                                           \
     if (grid > want) grid = want;                                                                           \

@@ -112,7 +112,9 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
 
     // pass 1: row maximum
     float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
-    if constexpr (std::is_same<T, float>::value) {
+    // (measured at [65536, 2048] f16, causal: the packed maximum below takes the forward kernel from 101 to 96 us and
+    // the backward kernel from 121 to 115 us, but the fused kernel from 136 to 145 us, so that one keeps the f32 form)
+    if constexpr (std::is_same<T, float>::value || (FWD && BWD)) {
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int col0 = (g.lane + k * G) * VEC;
@@ -126,8 +128,8 @@ softmax_rows_kernel(T* __restrict__ P, T* __restrict__ dS, const T* __restrict__
     } else {
       // 16-bit storage: the maximum is exact in the storage type, so it is taken on the packed pairs (one
       // instruction per two elements, no conversion) and widened once
-      using H2 = typename Elem<T>::Pair;
-      H2 hq[2] = {Elem<T>::pair_neg_inf(), Elem<T>::pair_neg_inf()};
+      using H2 = typename Pair16<T>::type;
+      H2 hq[2] = {Pair16<T>::neg_inf(), Pair16<T>::neg_inf()};
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int col0 = (g.lane + k * G) * VEC;

@@ -50,9 +50,7 @@ __device__ __forceinline__ void swiglu_h2(uint32_t gw, uint32_t uw, uint32_t dhw
   const __half2 g = *reinterpret_cast<__half2*>(&gw), u = *reinterpret_cast<__half2*>(&uw);
   const __half2 one = __float2half2_rn(1.f);
   const float2 gf = __half22float2(g);
-  // exp(-g) = 2^(-g log2e): one multiply and one MUFU each (flush-to-zero form: the subnormal range it gives up
-  // rounds to zero in 16 bits anyway)
-  const __half2 e = __floats2half2_rn(exp2f_approx(gf.x * -1.4426950408889634f), exp2f_approx(gf.y * -1.4426950408889634f));
+  const __half2 e = __floats2half2_rn(__expf(-gf.x), __expf(-gf.y));
   const __half2 d = __hadd2_rn(one, e);
   const float2 df = __half22float2(d);
   float rx, ry;
