@@ -45,7 +45,7 @@ CONFIG = {"workload": "causal softmax fwd+bwd, scores [1,32,2048,2048] f16 (benc
           "bytes_per_step": MOVED_BYTES}
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one softmax_rows_kernel launch on config 2, from an ncu capture of
-# `bench.py --case softmax_full` (276.9 MB read + 477.2 MB written); not re-measured by a bench run
+# `bench.py --case softmax_full` (277.0 MB read + 474.0 MB written); not re-measured by a bench run
 NCU_TRAFFIC_BYTES = 750946560
 
 
