@@ -372,6 +372,315 @@ done:
   }
 }
 
+// Single-pass form of the forward kernel: S = Q K^T is formed once per key tile.  Each softmax group keeps a running
+// maximum of its own tiles and its own O accumulator in tensor memory (S0, S1, O0, O1: 4 x 128 columns), and the two
+// are merged at the end.  Per tile the group reads S from tensor memory twice (maximum first, then exponentials)
+// instead of having the tensor cores recompute it.  The exponent reference m_used of a group only follows its true
+// running maximum when that has moved by more than 2^8 (probabilities then stay below 256 in 16 bits, relative
+// rounding unchanged); when it moves, the group scales its O rows and its row sum by 2^(old - new) in place, after
+// the P V that last wrote them has completed.  Row statistics written: the true maximum and the sum relative to it,
+// as the two-pass kernel writes them.
+int g_attn_fwd_single = 1;
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_fwd1_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, T* __restrict__ ctx, float* __restrict__ stats,
+                      const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = base;                        // 32 KB
+  unsigned char* sK = sQ + kTileBytes;             // 2 x 32 KB
+  unsigned char* sV = sK + 2 * kTileBytes;         // 2 x 32 KB
+  unsigned char* sP = sV + 2 * kTileBytes;         // 2 x 32 KB (one per softmax group)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kTileBytes);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* k_full = bars + 1;                     // 2
+  uint64_t* k_empty = bars + 3;                    // 2
+  uint64_t* v_full = bars + 5;                     // 2
+  uint64_t* v_empty = bars + 7;                    // 2
+  uint64_t* s_full = bars + 9;                     // 2
+  uint64_t* s_empty = bars + 11;                   // 2
+  uint64_t* p_full = bars + 13;                    // 2
+  uint64_t* p_empty = bars + 15;                   // 2
+  uint64_t* o_full = bars + 17;                    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  float* part = reinterpret_cast<float*>(bars + 20);       // [2 groups][128 rows] exchange area
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // launch order as in attention_fwd_kernel: batch slowest, heaviest query tile first, then head
+  const int nq = p.seq / kAttnRows;
+  const int b = (int)(blockIdx.x / (nq * p.heads));
+  const int rem = (int)(blockIdx.x % (nq * p.heads));
+  const int qi = nq - 1 - rem / p.heads;
+  const int h = rem % p.heads;
+  const int ntiles = qi + 1;                       // key tiles 0 .. qi
+  const int q0 = qi * kAttnRows;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
+      mbar_init(s_full + s, 1); mbar_init(s_empty + s, 4); mbar_init(p_full + s, 4); mbar_init(p_empty + s, 1);
+    }
+    mbar_init(o_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tO = tmem_base + 256u;            // S buffers at columns 0 and 128, O of group g at 256 + 128 g
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    mbar_expect_tx(q_full, kTileBytes);
+    tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+    tma_load_4d(sQ + 16384, &tmQ, q_full, 64, q0, h, b);
+    for (int j = 0; j < ntiles; ++j) {
+      const int sl = j & 1;
+      const unsigned ph = (unsigned)((j >> 1) & 1);
+      if (!mbar_wait_bounded(k_empty + sl, ph ^ 1, kDevErrAttnTimeout)) goto done;
+      unsigned char* dk = sK + (size_t)sl * kTileBytes;
+      mbar_expect_tx(k_full + sl, kTileBytes);
+      tma_load_4d(dk, &tmK, k_full + sl, 0, j * kAttnRows, h, b);
+      tma_load_4d(dk + 16384, &tmK, k_full + sl, 64, j * kAttnRows, h, b);
+      if (!mbar_wait_bounded(v_empty + sl, ph ^ 1, kDevErrAttnTimeout)) goto done;
+      unsigned char* dv = sV + (size_t)sl * kTileBytes;
+      mbar_expect_tx(v_full + sl, kTileBytes);
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+        for (int nh = 0; nh < 2; ++nh)
+          tma_load_4d(dv + kh * 16384 + nh * 8192, &tmV, v_full + sl, nh * 64, j * kAttnRows + kh * 64, h, b);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    if (!mbar_wait_bounded(q_full, 0, kDevErrAttnTimeout)) goto done;
+    const uint32_t aQ = smem_u32(sQ);
+    auto issue_s = [&](int n) -> bool {             // S[n & 1] = Q K_n^T
+      const int ks = n & 1;
+      const unsigned ph = (unsigned)((n >> 1) & 1);
+      if (!mbar_wait_bounded(k_full + ks, ph, kDevErrAttnTimeout)) return false;
+      if (!mbar_wait_bounded(s_empty + ks, ph ^ 1, kDevErrAttnTimeout)) return false;
+      tc_fence_after();
+      const uint32_t aK = smem_u32(sK + (size_t)ks * kTileBytes);
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+        tc_mma_f16(tmem_base + (uint32_t)ks * 128u, kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
+      tc_commit(k_empty + ks);
+      tc_commit(s_full + ks);
+      return true;
+    };
+    int n = 0;
+    for (int j = 0; j < 2 && j < ntiles; ++j, ++n)
+      if (!issue_s(n)) goto done;
+    for (int j = 0; j < ntiles; ++j) {
+      const int vs = j & 1;
+      const unsigned ph = (unsigned)((j >> 1) & 1);
+      if (!mbar_wait_bounded(v_full + vs, ph, kDevErrAttnTimeout)) goto done;
+      if (!mbar_wait_bounded(p_full + vs, ph, kDevErrAttnTimeout)) goto done;
+      tc_fence_after();
+      const uint32_t aV = smem_u32(sV + (size_t)vs * kTileBytes), aP = smem_u32(sP + (size_t)vs * kTileBytes);
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnRows / 16; ++k16)     // O of the tile's group; its first tile overwrites
+        tc_mma_f16(tO + (uint32_t)vs * 128u, kmajor_desc(aP, k16), v_desc(aV, k16), p.idesc_pv, (j >= 2 || k16) ? 1u : 0u);
+      tc_commit(v_empty + vs);
+      tc_commit(p_empty + vs);
+      if (j + 2 < ntiles) { if (!issue_s(n)) goto done; ++n; }
+    }
+    tc_commit(o_full);
+  } else if (warp >= 2) {
+    // ---------------- softmax groups: 2 x 128 threads, thread = query row, group g takes key tiles j = g (mod 2) ------
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;                        // TMEM lane quarter this warp may read
+    const int r = qq * 32 + lane;                   // row inside the tile
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr float kLazy = 8.f;                    // the exponent reference follows the maximum in steps of more than 2^8
+    const bool neg = p.alpha < 0.f;
+    float m_true = -INFINITY;                       // running maximum of the rounded, scaled, unmasked scores of this group's tiles
+    float mb = 0.f;                                 // exponent reference of this group, times log2(e)
+    float l = 0.f;                                  // running row sum relative to that reference
+    bool ok = true;   // a wait that ran out ends this warp's work (all 32 lanes together), but it still meets the barriers
+    unsigned char* myP = sP + (size_t)grp * kTileBytes;
+    const uint32_t tOg = tO + (uint32_t)grp * 128u + lane_off;
+    for (int j = grp; j < ntiles; j += 2) {
+      const int sb = j & 1;                         // == grp
+      const unsigned ph = (unsigned)((j >> 1) & 1);
+      if (!mbar_wait_bounded_warp(s_full + sb, ph, kDevErrAttnTimeout)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tmem_base + (uint32_t)sb * 128u + lane_off;
+      // first reading of the tile: its row maximum (sign-folded raw accumulators; scaling by alpha and rounding to the
+      // storage type are monotone, so they are applied to the extreme value only)
+      float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+        tc_ld_wait();
+        if (j != qi) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float a = __uint_as_float(v[i >> 5][i & 31]);
+            mq[i & 3] = fmaxf(mq[i & 3], neg ? -a : a);
+          }
+        } else {                                    // diagonal tile: columns c <= r are unmasked
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float a = __uint_as_float(v[i >> 5][i & 31]);
+            if (half * 64 + i <= r) mq[i & 3] = fmaxf(mq[i & 3], neg ? -a : a);
+          }
+        }
+      }
+      float tm = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+      tm = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * (neg ? -tm : tm)));       // every row has an unmasked key in every tile
+      m_true = fmaxf(m_true, tm);
+      // move the exponent reference?  (first tile of the group: set it; O and l hold nothing yet)
+      const bool first = j == grp;
+      const float mb_new = m_true * kLog2e;
+      const bool move = first || (mb_new - mb > kLazy);
+      if (__any_sync(0xffffffffu, move && !first)) {
+        // the P V that last wrote this group's O rows must have completed before they are read
+        if (!mbar_wait_bounded_warp(p_empty + grp, ph ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+        tc_fence_after();
+        const float f = move ? exp2f_approx(mb - mb_new) : 1.f;
+        l *= f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kAttnHd; c0 += 32) {
+          uint32_t o[32];
+          tc_ld32(tOg + (uint32_t)c0, o);
+          tc_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tc_st32(tOg + (uint32_t)c0, o);
+        }
+        tc_st_wait();
+      }
+      if (move) mb = mb_new;
+      // second reading: exponentials relative to the reference, row sum, probabilities
+      uint4 pk[16];                                 // this row's 128 probabilities, 8 per 16-byte chunk
+      float lq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+        tc_ld_wait();
+        if (half == 1) {                            // the accumulator is in registers: the next S may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + sb);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int idx = g * 8 + i * 2;
+            const float2 s2 = rounded_scores<T>(p.alpha, v[idx >> 5][idx & 31], v[idx >> 5][(idx & 31) + 1]);
+            float e0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+            float e1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
+            if (j == qi) {
+              const int c = half * 64 + idx;
+              if (c > r) e0 = 0.f;
+              if (c + 1 > r) e1 = 0.f;
+            }
+            lq[i] += e0 + e1;
+            w[i] = pack2<T>(e0, e1);
+          }
+          pk[half * 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l += (lq[0] + lq[1]) + (lq[2] + lq[3]);
+      // the P V two tiles back has read this group's probability buffer
+      if (!mbar_wait_bounded_warp(p_empty + grp, ph ^ 1, kDevErrAttnTimeout)) { ok = false; break; }
+#pragma unroll
+      for (int c = 0; c < 16; ++c)                  // chunk c: keys 8c .. 8c+7; key half c >> 3, chunk c & 7 of the 128-byte row
+        *reinterpret_cast<uint4*>(myP + (size_t)(c >> 3) * 16384 + (size_t)r * 128 + (((c & 7) ^ (r & 7)) << 4)) = pk[c];
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();                            // (orders the in-place scaling of O before the P V that follows)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + grp);
+    }
+    // merge the two groups: common maximum, then each group's factor 2^(mb_g - m log2e) for its sum and its O rows
+    part[grp * kAttnRows + r] = m_true;
+    named_barrier(1, 256);
+    const float m = fmaxf(part[r], part[kAttnRows + r]);
+    named_barrier(1, 256);
+    const bool has = ntiles > grp;                  // (a group without tiles holds nothing: factor 0, its O rows are not read)
+    const float f_own = has ? exp2f_approx(mb - m * kLog2e) : 0.f;
+    part[grp * kAttnRows + r] = l * f_own;
+    named_barrier(1, 256);
+    l = part[r] + part[kAttnRows + r];
+    named_barrier(1, 256);
+    part[grp * kAttnRows + r] = f_own;
+    named_barrier(1, 256);
+    const float f0 = part[r], f1 = part[kAttnRows + r];
+    // context rows = (f0 O0 + f1 O1) / l: group 0 columns 0..63, group 1 the rest, through a packed staging area as in
+    // attention_fwd_kernel
+    const bool fin = ok && mbar_wait_bounded_warp(o_full, 0, kDevErrAttnTimeout);
+    unsigned char* rowbuf = sP;
+    if (fin) {
+      tc_fence_after();
+      const float rl = 1.f / l;
+      const float g0 = f0 * rl, g1 = f1 * rl;
+      if (grp == 0) {
+        float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
+        st[0] = m; st[1] = l;
+      }
+#pragma unroll 1
+      for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
+        uint32_t v0[32], v1[32];
+        tc_ld32(tO + lane_off + (uint32_t)c0, v0);
+        if (ntiles > 1) tc_ld32(tO + 128u + lane_off + (uint32_t)c0, v1);
+        tc_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {               // 4 elements = 8 bytes (head_dim % 4 == 0)
+          const int c = c0 + g * 4;
+          if (c + 4 <= p.head_dim) {
+            float o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              o[i] = __uint_as_float(v0[g * 4 + i]) * g0;
+              if (ntiles > 1) o[i] = __fmaf_rn(__uint_as_float(v1[g * 4 + i]), g1, o[i]);
+            }
+            uint2 w;
+            w.x = pack2<T>(o[0], o[1]);
+            w.y = pack2<T>(o[2], o[3]);
+            *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    named_barrier(1, 256);
+    if (fin) {
+      const int cw = warp - 2;                      // 8 softmax warps, 16 rows each
+      for (int rr = cw * 16; rr < cw * 16 + 16; ++rr) {
+        T* out = ctx + (((long long)b * p.seq + q0 + rr) * p.heads + h) * p.head_dim;
+        if (lane < p.head_dim / 4)
+          reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
+      }
+    }
+    tc_fence_before();
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  Eight lanes per
 // (b, s, h) row, four rows per warp, each lane on 8-byte pieces 8 apart: both tensors stream coalesced and every lane
 // has up to eight loads in flight.
@@ -1158,12 +1467,20 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
                           ((uint32_t)(128 >> 4) << 24);
   p.idesc_s = common;                       // A, B K-major
   p.idesc_pv = common | (1u << 16);         // B (V) MN-major
-  auto kern = attention_fwd_kernel<T>;
-  static bool attr_set[kMaxDevices] = {};
-  ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
-  kern<<<(unsigned)grid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
-                                                           reinterpret_cast<float*>(stats), p);
+  if (g_attn_fwd_single) {
+    auto kern = attention_fwd1_kernel<T>;
+    static bool attr_set[kMaxDevices] = {};
+    ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
+    kern<<<(unsigned)grid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
+                                                             reinterpret_cast<float*>(stats), p);
+  } else {
+    auto kern = attention_fwd_kernel<T>;
+    static bool attr_set[kMaxDevices] = {};
+    ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
+    kern<<<(unsigned)grid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
+                                                             reinterpret_cast<float*>(stats), p);
+  }
   return check_launch();
 }
 

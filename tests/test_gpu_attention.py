@@ -61,6 +61,58 @@ def test_attention_fwd(cuda, bsz, s, h, hd):
                  floor_abs=mag)
 
 
+@pytest.fixture
+def two_pass_forward():
+    """Run attention_fwd on the two-pass kernel (scores formed twice, exact maximum first) for the duration of a test."""
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"attn_fwd_single", 0) == capi.OK
+    yield
+    assert L.cacti_b200_tune(b"attn_fwd_single", 1) == capi.OK
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(2, 256, 3, 100), (1, 640, 2, 64)])
+def test_attention_fwd_two_pass_kernel(cuda, two_pass_forward, bsz, s, h, hd):
+    test_attention_fwd(cuda, bsz, s, h, hd)
+
+
+@pytest.mark.parametrize("sign", [1.0, -1.0])
+@pytest.mark.parametrize("s,hd", [(640, 64), (1024, 100)])
+def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
+    """Scores that grow by about ten per key tile (alternating tiles by twice that), so that in the single-pass kernel
+    each group's exponent reference has to move again and again and its accumulated rows are rescaled in tensor memory;
+    also with a negative alpha (the sign-folded maximum).  Against the oracle, and against the two-pass kernel."""
+    bsz, h = 1, 2
+    alpha = sign / 8.0
+    rng = np.random.default_rng(77)
+    q = (1.0 + 0.1 * rng.standard_normal((bsz, s, h, hd))).astype(np.float16)
+    ramp = (np.arange(s) * (10.0 / 128) * 8.0 / hd).reshape(1, s, 1, 1)           # alpha q.k grows 10 per 128 keys
+    ramp = ramp * np.where((np.arange(s) // 128) % 2 == 1, 1.5, 1.0).reshape(1, s, 1, 1)
+    k = (sign * ramp * (1.0 + 0.05 * rng.standard_normal((bsz, s, h, hd)))).astype(np.float16)
+    v = R.normal(78, (bsz, s, h, hd), np.float16)
+    qp, kp, vp = (ops.block_pad(dev(t), 128) for t in (q, k, v))
+    rctx, rm, rl, mag = ref_attention(q, k, v, alpha)
+    assert (np.diff(rm[0, 0, ::128]) > 5.6).all()              # the maximum does move by more than 2^8 between tiles
+    L = capi.lib()
+    out = {}
+    for single in (1, 0):
+        assert L.cacti_b200_tune(b"attn_fwd_single", single) == capi.OK
+        try:
+            ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
+            torch.cuda.synchronize()
+        finally:
+            L.cacti_b200_tune(b"attn_fwd_single", 1)
+        err = C.c_uint(7)
+        assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+        assert_close(host(ctx), rctx, "float16", f"moving maximum, single={single}", floor_frac=1.0, floor_abs=mag)
+        st = host(stats)
+        assert np.abs(st[..., 0] - rm).max() <= 2.0 ** -9 * np.abs(rm).max()
+        assert np.abs(st[..., 1] / (rl * np.exp(rm - st[..., 0])) - 1).max() < 2e-3
+        out[single] = (host(ctx), st)
+    assert np.array_equal(out[0][1][..., 0], out[1][1][..., 0])          # the same row maxima from both kernels
+    assert_close(out[1][0], out[0][0].astype(np.float64), "float16", "single-pass vs two-pass", rtol=4e-3, floor_frac=1.0,
+                 floor_abs=mag)
+
+
 def test_attention_fwd_bf16_and_errors(cuda):
     bsz, s, h, hd = 1, 256, 2, 100
     q, k, v = (R.bf16_round(R.normal(80 + i, (bsz, s, h, hd))) for i in range(3))
