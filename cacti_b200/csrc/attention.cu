@@ -23,8 +23,11 @@
 //               pass 2 reads S again, forms exp(s - m), sums it, writes the 16-bit probabilities into shared memory
 //               in the 128-byte-swizzled K-major layout the MMA reads; the groups' maxima and sums are combined
 //               through shared memory; at the end each group scales half of O's columns by 1 / sum and stores them
-// Two passes (max first, then exp / sum / P V) instead of an online softmax: no rescaling of O in tensor memory, and
-// the row maximum is the true one as in the reference; the price is computing S twice (K = hd_pad, cheap).
+// That is attention_fwd_kernel: two passes (max first, then exp / sum / P V), no rescaling of O in tensor memory, the
+// price being S computed twice.  attention_fwd1_kernel, which the entry point launches by default, forms S once:
+// a running maximum and an O accumulator per softmax group, rescaled in tensor memory when the maximum has moved far
+// (see the comment at that kernel); measured 560 against 620 us at [8, 2048, 32, 100].  Both write the true row maximum
+// and the sum relative to it.
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
 #include "tc_common.cuh"
 #include <type_traits>
