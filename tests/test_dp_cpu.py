@@ -116,3 +116,31 @@ def test_a_rank_that_leaves_between_steps_ends_the_exchange_with_an_error():
     outs = [p.communicate(timeout=120)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"ok {r}" in o, o
+
+
+def test_stacked_views_need_adjacent_tensors_of_one_storage():
+    """llama_step.stacked: the [n, rows, 1, cols] view behind the batched q / k / v matmuls exists only for equal,
+    contiguous tensors that lie back to back in one storage (as init_weights and alloc_bucketed_grads lay them out)."""
+    import torch
+    from cacti_b200 import dp as DP, llama_step as LS
+    flat = torch.arange(3 * 6 * 4, dtype=torch.float32)
+    a, b, c = (flat[i * 24:(i + 1) * 24].view(6, 4) for i in range(3))
+    v = LS.stacked(a, b, c)
+    assert v is not None and v.shape == (3, 6, 1, 4)
+    assert torch.equal(v[1, :, 0, :], b) and torch.equal(v[2, 5, 0], c[5])
+    assert LS.stacked(a, c, b) is None                                   # wrong order
+    assert LS.stacked(a, b.clone(), c) is None                           # another storage
+    gap = torch.zeros(3 * 24 + 8)
+    g0, g1 = gap[0:24].view(6, 4), gap[32:56].view(6, 4)
+    assert LS.stacked(g0, g1) is None                                    # padding in between
+    assert LS.stacked(a, flat[24:48].view(4, 6)) is None                 # another shape
+    assert LS.stacked(a.t(), b.t()) is None                              # not contiguous
+    # the layouts the step relies on
+    cfg = LS.LlamaShape(layers=1, d_model=256, heads=2, head_dim=128, ffn=128, vocab=64, seq=128)
+    P = LS.init_weights(cfg, torch.device("cpu"), seed=0)
+    L0 = P["layers"][0]
+    assert LS.stacked(L0["q"], L0["k"], L0["v"]) is not None
+    G0 = DP.alloc_bucketed_grads(P)[0]["layers"][0]
+    assert LS.stacked(G0["q"], G0["k"], G0["v"]) is not None
+    G1 = LS.zeros_like_params(P)["layers"][0]
+    assert LS.stacked(G1["q"], G1["k"], G1["v"]) is None
