@@ -684,6 +684,368 @@ done:
   }
 }
 
+// Persistent form of attention_fwd1_kernel: one CTA per SM walks a list of (batch, query tile, head) items instead of
+// ending after one.  Measured on the one-item form with 28 CTAs per SM: 8.1 us per CTA with one key tile, 20.5 us with
+// 8.5 on average, i.e. 1.65 us per tile and 6.5 us per CTA that no tile accounts for (launch, barrier and tensor-memory
+// set-up, the first loads' latency, the context rows' way out, exit), a third of the kernel at config 5.  Here the
+// rings, the barriers and the tensor memory live across items, and the roles run ahead of one another across the item
+// boundary: while the softmax warps merge, scale and store the context rows of an item, the producer has loaded the next
+// Q and K / V tiles and the tensor cores have formed its first scores.
+// Items are dealt in rounds of gridDim.x, every other round in reverse CTA order (the list is sorted heaviest first, so
+// a CTA's long items are paired with short ones); every role derives the same sequence on its own.  Tiles are counted
+// across items (n): key tile n goes through ring slot, S buffer, softmax group and O accumulator n & 1.
+int g_attn_fwd_persistent = 1;
+
+struct AttnItem { int b, qi, h, ntiles; };
+__device__ __forceinline__ bool attn_item(const AttnParams& p, int round, AttnItem& it) {
+  const int nq = p.seq / kAttnRows;
+  const long long total = (long long)p.batch * nq * p.heads;
+  const long long w = (long long)round * gridDim.x + ((round & 1) ? (long long)(gridDim.x - 1 - blockIdx.x) : (long long)blockIdx.x);
+  if (w >= total) return false;
+  it.b = (int)(w / (nq * p.heads));
+  const int rem = (int)(w % (nq * p.heads));
+  it.qi = nq - 1 - rem / p.heads;                  // launch order as in attention_fwd_kernel: heaviest query tile first
+  it.h = rem % p.heads;
+  it.ntiles = it.qi + 1;
+  return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_fwd1p_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, T* __restrict__ ctx, float* __restrict__ stats,
+                       const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = base;                        // 32 KB
+  unsigned char* sK = sQ + kTileBytes;             // 2 x 32 KB
+  unsigned char* sV = sK + 2 * kTileBytes;         // 2 x 32 KB
+  unsigned char* sP = sV + 2 * kTileBytes;         // 2 x 32 KB (one per softmax group)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kTileBytes);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* k_full = bars + 1;                     // 2
+  uint64_t* k_empty = bars + 3;                    // 2
+  uint64_t* v_full = bars + 5;                     // 2
+  uint64_t* v_empty = bars + 7;                    // 2
+  uint64_t* s_full = bars + 9;                     // 2
+  uint64_t* s_empty = bars + 11;                   // 2
+  uint64_t* p_full = bars + 13;                    // 2
+  uint64_t* p_empty = bars + 15;                   // 2
+  uint64_t* o_full = bars + 17;                    // 1
+  uint64_t* q_empty = bars + 18;                   // 1: the item's last S matmul has read Q
+  uint64_t* o_empty = bars + 19;                   // 1: the item's context rows have left the O accumulators
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1); // set by any role whose bounded wait ran out
+  int* group_stop = abort_flag + 1;                        // what the softmax warps agreed on at an item's last barrier
+  float* part = reinterpret_cast<float*>(bars + 22);       // [2 groups][128 rows] exchange area
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = p.seq / kAttnRows;
+  const long long total = (long long)p.batch * nq * p.heads;
+  const int rounds = (int)((total + gridDim.x - 1) / gridDim.x);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
+      mbar_init(s_full + s, 1); mbar_init(s_empty + s, 4); mbar_init(p_full + s, 4); mbar_init(p_empty + s, 1);
+    }
+    mbar_init(o_full, 1); mbar_init(q_empty, 1); mbar_init(o_empty, 8);
+    *abort_flag = 0; *group_stop = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tO = tmem_base + 256u;            // S buffers at columns 0 and 128, O of group g at 256 + 128 g
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    unsigned n = 0, it = 0;                         // key tiles and items so far
+    for (int round = 0; round < rounds; ++round) {
+      AttnItem a;
+      if (!attn_item(p, round, a)) continue;
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      if (it > 0 && !mbar_wait_bounded(q_empty, (it - 1) & 1u, kDevErrAttnTimeout)) break;
+      const int q0 = a.qi * kAttnRows;
+      mbar_expect_tx(q_full, kTileBytes);
+      tma_load_4d(sQ, &tmQ, q_full, 0, q0, a.h, a.b);
+      tma_load_4d(sQ + 16384, &tmQ, q_full, 64, q0, a.h, a.b);
+      bool fail = false;
+      for (int j = 0; j < a.ntiles; ++j, ++n) {
+        const unsigned sl = n & 1u, ph = (n >> 1) & 1u;
+        if (!mbar_wait_bounded(k_empty + sl, ph ^ 1u, kDevErrAttnTimeout)) { fail = true; break; }
+        unsigned char* dk = sK + (size_t)sl * kTileBytes;
+        mbar_expect_tx(k_full + sl, kTileBytes);
+        tma_load_4d(dk, &tmK, k_full + sl, 0, j * kAttnRows, a.h, a.b);
+        tma_load_4d(dk + 16384, &tmK, k_full + sl, 64, j * kAttnRows, a.h, a.b);
+        if (!mbar_wait_bounded(v_empty + sl, ph ^ 1u, kDevErrAttnTimeout)) { fail = true; break; }
+        unsigned char* dv = sV + (size_t)sl * kTileBytes;
+        mbar_expect_tx(v_full + sl, kTileBytes);
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+          for (int nh = 0; nh < 2; ++nh)
+            tma_load_4d(dv + kh * 16384 + nh * 8192, &tmV, v_full + sl, nh * 64, j * kAttnRows + kh * 64, a.h, a.b);
+      }
+      if (fail) { *reinterpret_cast<volatile int*>(abort_flag) = 1; break; }
+      ++it;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t aQ = smem_u32(sQ);
+    auto issue_s = [&](unsigned nn) -> bool {        // S[nn & 1] = Q K_nn^T
+      const unsigned ks = nn & 1u, ph = (nn >> 1) & 1u;
+      if (!mbar_wait_bounded(k_full + ks, ph, kDevErrAttnTimeout)) return false;
+      if (!mbar_wait_bounded(s_empty + ks, ph ^ 1u, kDevErrAttnTimeout)) return false;
+      tc_fence_after();
+      const uint32_t aK = smem_u32(sK + (size_t)ks * kTileBytes);
+#pragma unroll
+      for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+        tc_mma_f16(tmem_base + ks * 128u, kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
+      tc_commit(k_empty + ks);
+      tc_commit(s_full + ks);
+      return true;
+    };
+    unsigned n = 0, it = 0;
+    for (int round = 0; round < rounds; ++round) {
+      AttnItem a;
+      if (!attn_item(p, round, a)) continue;
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      bool fail = !mbar_wait_bounded(q_full, it & 1u, kDevErrAttnTimeout);
+      const unsigned n0 = n;
+      int issued = 0;
+      for (; !fail && issued < 2 && issued < a.ntiles; ++issued) {
+        fail = !issue_s(n0 + issued);
+        if (!fail && issued + 1 == a.ntiles) tc_commit(q_empty);
+      }
+      // the previous item's context rows have been read out of both O accumulators
+      if (!fail && it > 0) fail = !mbar_wait_bounded(o_empty, (it - 1) & 1u, kDevErrAttnTimeout);
+      for (int j = 0; !fail && j < a.ntiles; ++j) {
+        const unsigned nn = n0 + j, vs = nn & 1u, ph = (nn >> 1) & 1u;
+        if (!mbar_wait_bounded(v_full + vs, ph, kDevErrAttnTimeout) || !mbar_wait_bounded(p_full + vs, ph, kDevErrAttnTimeout)) { fail = true; break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + (size_t)vs * kTileBytes), aP = smem_u32(sP + (size_t)vs * kTileBytes);
+#pragma unroll
+        for (int k16 = 0; k16 < kAttnRows / 16; ++k16)   // the group's first tile of the item overwrites its accumulator
+          tc_mma_f16(tO + vs * 128u, kmajor_desc(aP, k16), v_desc(aV, k16), p.idesc_pv, (j >= 2 || k16) ? 1u : 0u);
+        tc_commit(v_empty + vs);
+        tc_commit(p_empty + vs);
+        if (issued < a.ntiles) {
+          fail = !issue_s(n0 + issued);
+          ++issued;
+          if (!fail && issued == a.ntiles) tc_commit(q_empty);
+        }
+      }
+      if (fail) { *reinterpret_cast<volatile int*>(abort_flag) = 1; break; }
+      tc_commit(o_full);
+      n = n0 + a.ntiles;
+      ++it;
+    }
+  } else if (warp >= 2) {
+    // ---------------- softmax groups: 2 x 128 threads, thread = query row, group g takes key tiles n = g (mod 2) ------
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;                        // TMEM lane quarter this warp may read
+    const int r = qq * 32 + lane;                   // row inside the tile
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr float kLazy = 8.f;
+    const bool neg = p.alpha < 0.f;
+    unsigned char* myP = sP + (size_t)grp * kTileBytes;
+    const uint32_t tOg = tO + (uint32_t)grp * 128u + lane_off;
+    unsigned n = 0, it = 0;
+    bool ok = true;   // a wait that ran out: this warp stops working on tiles but meets every barrier of the item; the
+                      // whole group then leaves the item loop together after the item's last barrier
+    for (int round = 0; round < rounds; ++round) {
+      AttnItem a;
+      if (!attn_item(p, round, a)) continue;
+      const int q0 = a.qi * kAttnRows;
+      const unsigned n0 = n;
+      float m_true = -INFINITY, mb = 0.f, l = 0.f;
+      bool first = true;
+      for (int j = 0; ok && j < a.ntiles; ++j) {
+        const unsigned nn = n0 + j;
+        if ((int)(nn & 1u) != grp) continue;
+        const unsigned ph = (nn >> 1) & 1u;
+        if (!mbar_wait_bounded_warp(s_full + grp, ph, kDevErrAttnTimeout)) { ok = false; break; }
+        // The tensor pipe runs its matmuls in issue order and this S was issued after the group's previous P V, so
+        // that one has completed too: the wait below returns at once.  It makes the group's O rows and its
+        // probability buffer safe to touch from here on.
+        if (!mbar_wait_bounded_warp(p_empty + grp, ph ^ 1u, kDevErrAttnTimeout)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ts = tmem_base + (uint32_t)grp * 128u + lane_off;
+        float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[2][32];
+          tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+          tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+          tc_ld_wait();
+          if (j != a.qi) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              const float x = __uint_as_float(v[i >> 5][i & 31]);
+              mq[i & 3] = fmaxf(mq[i & 3], neg ? -x : x);
+            }
+          } else {                                  // diagonal tile: columns c <= r are unmasked
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              const float x = __uint_as_float(v[i >> 5][i & 31]);
+              if (half * 64 + i <= r) mq[i & 3] = fmaxf(mq[i & 3], neg ? -x : x);
+            }
+          }
+        }
+        float tm = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+        tm = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * (neg ? -tm : tm)));
+        m_true = fmaxf(m_true, tm);
+        const float mb_new = m_true * kLog2e;
+        const bool move = first || (mb_new - mb > kLazy);
+        if (__any_sync(0xffffffffu, move && !first)) {
+          const float f = (move && !first) ? exp2f_approx(mb - mb_new) : 1.f;
+          l *= f;
+#pragma unroll 1
+          for (int c0 = 0; c0 < kAttnHd; c0 += 32) {
+            uint32_t o[32];
+            tc_ld32(tOg + (uint32_t)c0, o);
+            tc_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tc_st32(tOg + (uint32_t)c0, o);
+          }
+          tc_st_wait();
+        }
+        if (move) mb = mb_new;
+        first = false;
+        float lq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint4 pk[8];                              // 64 probabilities of this row, 8 per 16-byte chunk
+          uint32_t v[2][32];
+          tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+          tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+          tc_ld_wait();
+          if (half == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + grp);
+          }
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int idx = g * 8 + i * 2;
+              const float2 s2 = rounded_scores<T>(p.alpha, v[idx >> 5][idx & 31], v[idx >> 5][(idx & 31) + 1]);
+              float e0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+              float e1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
+              if (j == a.qi) {
+                const int c = half * 64 + idx;
+                if (c > r) e0 = 0.f;
+                if (c + 1 > r) e1 = 0.f;
+              }
+              lq[i] += e0 + e1;
+              w[i] = pack2<T>(e0, e1);
+            }
+            pk[g] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c)               // chunk c of key half `half`: keys 64 half + 8c .. + 7, 128-byte-swizzled row
+            *reinterpret_cast<uint4*>(myP + (size_t)half * 16384 + (size_t)r * 128 + ((c ^ (r & 7)) << 4)) = pk[c];
+        }
+        l += (lq[0] + lq[1]) + (lq[2] + lq[3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + grp);
+      }
+      n = n0 + (unsigned)a.ntiles;
+      if (!ok && lane == 0) *reinterpret_cast<volatile int*>(abort_flag) = 1;
+      // merge the two groups (a group without a tile in this item holds nothing: factor 0, its O rows are not read)
+      const bool has0 = a.ntiles >= 2 || (n0 & 1u) == 0u, has1 = a.ntiles >= 2 || (n0 & 1u) == 1u;
+      const bool has = grp == 0 ? has0 : has1;
+      part[grp * kAttnRows + r] = has ? m_true : -INFINITY;
+      named_barrier(1, 256);
+      const float m = fmaxf(part[r], part[kAttnRows + r]);
+      named_barrier(1, 256);
+      const float f_own = has ? exp2f_approx(mb - m * kLog2e) : 0.f;
+      part[grp * kAttnRows + r] = has ? l * f_own : 0.f;
+      named_barrier(1, 256);
+      l = part[r] + part[kAttnRows + r];
+      named_barrier(1, 256);
+      part[grp * kAttnRows + r] = f_own;
+      named_barrier(1, 256);
+      const float f0 = part[r], f1 = part[kAttnRows + r];
+      const bool fin = ok && mbar_wait_bounded_warp(o_full, it & 1u, kDevErrAttnTimeout);
+      if (!fin && lane == 0) *reinterpret_cast<volatile int*>(abort_flag) = 1;
+      unsigned char* rowbuf = sP;
+      if (fin) {
+        tc_fence_after();
+        const float rl = 1.f / l;
+        const float g0 = f0 * rl, g1 = f1 * rl;
+        if (grp == 0) {
+          float* st = stats + (((long long)a.b * p.heads + a.h) * p.seq + q0 + r) * 4;
+          st[0] = m; st[1] = l;
+        }
+#pragma unroll 1
+        for (int c0 = grp * 64; c0 < grp * 64 + 64 && c0 < p.head_dim; c0 += 32) {
+          uint32_t v0[32], v1[32];
+          if (has0) tc_ld32(tO + lane_off + (uint32_t)c0, v0);
+          if (has1) tc_ld32(tO + 128u + lane_off + (uint32_t)c0, v1);
+          tc_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int c = c0 + g * 4;
+            if (c + 4 <= p.head_dim) {
+              float o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                o[i] = has0 ? __uint_as_float(v0[g * 4 + i]) * g0 : 0.f;
+                if (has1) o[i] = __fmaf_rn(__uint_as_float(v1[g * 4 + i]), g1, o[i]);
+              }
+              uint2 w;
+              w.x = pack2<T>(o[0], o[1]);
+              w.y = pack2<T>(o[2], o[3]);
+              *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_empty);        // the next item's first P V may overwrite the accumulators
+      }
+      named_barrier(1, 256);
+      if (fin) {
+        const int cw = warp - 2;                    // 8 softmax warps, 16 rows each
+        for (int rr = cw * 16; rr < cw * 16 + 16; ++rr) {
+          T* out = ctx + (((long long)a.b * p.seq + q0 + rr) * p.heads + a.h) * p.head_dim;
+          if (lane < p.head_dim / 4)
+            reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
+        }
+      }
+      // the staging area is the first probability buffer: nobody writes the next item's probabilities into it before
+      // every warp has read its rows.  The same barrier carries the decision to stop: one thread reads the flag and
+      // all eight warps act on that one reading (a named barrier has no time limit, so no warp may leave alone)
+      if (warp == 2 && lane == 0) *group_stop = *reinterpret_cast<volatile int*>(abort_flag);
+      named_barrier(1, 256);
+      ++it;
+      if (*reinterpret_cast<volatile int*>(group_stop)) break;
+    }
+    tc_fence_before();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  Eight lanes per
 // (b, s, h) row, four rows per warp, each lane on 8-byte pieces 8 apart: both tensors stream coalesced and every lane
 // has up to eight loads in flight.
@@ -1471,7 +1833,14 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   p.idesc_s = common;                       // A, B K-major
   p.idesc_pv = common | (1u << 16);         // B (V) MN-major
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
-  if (g_attn_fwd_single) {
+  if (g_attn_fwd_single && g_attn_fwd_persistent) {
+    auto kern = attention_fwd1p_kernel<T>;
+    static bool attr_set[kMaxDevices] = {};
+    ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
+    const unsigned pgrid = (unsigned)(grid < kNumSMs ? grid : kNumSMs);
+    kern<<<pgrid, kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
+                                                    reinterpret_cast<float*>(stats), p);
+  } else if (g_attn_fwd_single) {
     auto kern = attention_fwd1_kernel<T>;
     static bool attr_set[kMaxDevices] = {};
     ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);

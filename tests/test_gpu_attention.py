@@ -75,6 +75,50 @@ def test_attention_fwd_two_pass_kernel(cuda, two_pass_forward, bsz, s, h, hd):
     test_attention_fwd(cuda, bsz, s, h, hd)
 
 
+@pytest.fixture
+def one_item_per_cta():
+    """Run the single-pass forward as one CTA per (batch, query tile, head) instead of the persistent walk."""
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK
+    yield
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 1) == capi.OK
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(2, 256, 3, 100), (1, 640, 2, 64)])
+def test_attention_fwd_one_item_per_cta(cuda, one_item_per_cta, bsz, s, h, hd):
+    test_attention_fwd(cuda, bsz, s, h, hd)
+
+
+def test_attention_fwd_persistent_walk_many_items(cuda):
+    """More items than SMs can hold at once, of every length from 1 to 8 key tiles, so that every CTA of the persistent
+    kernel walks several items (odd and even tile counts: the tile parity that selects ring slot, softmax group and
+    accumulator carries over from item to item), against the oracle and the one-item-per-CTA form (which of the two
+    groups takes a tile may differ between the two forms, hence the rounding: same row maxima, the rest to tolerance)."""
+    bsz, s, h, hd = 3, 1024, 25, 100             # 600 items on at most 148 CTAs
+    q, k, v = (dev(R.normal(60 + i, (bsz, s, h, hd), np.float16)) for i in range(3))
+    alpha = float(1.0 / np.sqrt(hd))
+    qp, kp, vp = (ops.block_pad(t, 128) for t in (q, k, v))
+    L = capi.lib()
+    ctx_p, st_p = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK
+    try:
+        ctx_1, st_1 = ops.attention_fwd(qp, kp, vp, hd, alpha)
+    finally:
+        L.cacti_b200_tune(b"attn_fwd_persistent", 1)
+    torch.cuda.synchronize()
+    err = C.c_uint(7)
+    assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
+    rctx, rm, rl, mag = ref_attention(host(q), host(k), host(v), alpha)
+    for name, ctx_, st_ in (("persistent", ctx_p, st_p), ("one item per CTA", ctx_1, st_1)):
+        assert_close(host(ctx_), rctx, "float16", f"many items, {name}", floor_frac=1.0, floor_abs=mag)
+        st = host(st_)
+        assert np.abs(st[..., 0] - rm).max() <= 2.0 ** -9 * np.abs(rm).max()
+        assert np.abs(st[..., 1] / (rl * np.exp(rm - st[..., 0])) - 1).max() < 2e-3
+    assert torch.equal(st_p[..., 0], st_1[..., 0])
+    assert_close(host(ctx_p), host(ctx_1).astype(np.float64), "float16", "persistent vs one item per CTA", rtol=4e-3,
+                 floor_frac=1.0, floor_abs=mag)
+
+
 @pytest.mark.parametrize("sign", [1.0, -1.0])
 @pytest.mark.parametrize("s,hd", [(640, 64), (1024, 100)])
 def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
@@ -97,13 +141,15 @@ def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
     assert (np.diff(rm[0, 0, ::128]) > 5.6).all()              # the maximum does move by more than 2^8 between tiles
     L = capi.lib()
     out = {}
-    for single in (1, 0):
-        assert L.cacti_b200_tune(b"attn_fwd_single", single) == capi.OK
+    for single in (1, 2, 0):                        # persistent single-pass, one item per CTA, two-pass
+        assert L.cacti_b200_tune(b"attn_fwd_single", 1 if single else 0) == capi.OK
+        assert L.cacti_b200_tune(b"attn_fwd_persistent", 1 if single == 1 else 0) == capi.OK
         try:
             ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
             torch.cuda.synchronize()
         finally:
             L.cacti_b200_tune(b"attn_fwd_single", 1)
+            L.cacti_b200_tune(b"attn_fwd_persistent", 1)
         err = C.c_uint(7)
         assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
         assert_close(host(ctx), rctx, "float16", f"moving maximum, single={single}", floor_frac=1.0, floor_abs=mag)
@@ -112,6 +158,7 @@ def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
         assert np.abs(st[..., 1] / (rl * np.exp(rm - st[..., 0])) - 1).max() < 2e-3
         out[single] = (host(ctx), st)
     assert np.array_equal(out[0][1][..., 0], out[1][1][..., 0])          # the same row maxima from both kernels
+    assert np.array_equal(out[1][1][..., 0], out[2][1][..., 0])          # persistent or not: the same row maxima
     assert_close(out[1][0], out[0][0].astype(np.float64), "float16", "single-pass vs two-pass", rtol=4e-3, floor_frac=1.0,
                  floor_abs=mag)
 
