@@ -24,10 +24,11 @@
 //               in the 128-byte-swizzled K-major layout the MMA reads; the groups' maxima and sums are combined
 //               through shared memory; at the end each group scales half of O's columns by 1 / sum and stores them
 // That is attention_fwd_kernel: two passes (max first, then exp / sum / P V), no rescaling of O in tensor memory, the
-// price being S computed twice.  attention_fwd1_kernel, which the entry point launches by default, forms S once:
-// a running maximum and an O accumulator per softmax group, rescaled in tensor memory when the maximum has moved far
-// (see the comment at that kernel); measured 560 against 620 us at [8, 2048, 32, 100].  Both write the true row maximum
-// and the sum relative to it.
+// price being S computed twice.  attention_fwd1_kernel forms S once: a running maximum and an O accumulator per
+// softmax group, rescaled in tensor memory when the maximum has moved far (see the comment at that kernel); measured
+// 560 against 620 us at [8, 2048, 32, 100].  attention_fwd1p_kernel, which the entry point launches by default, is
+// that kernel with one CTA per SM walking many (batch, query tile, head) items.  All write the true row maximum and the
+// sum relative to it.
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
 #include "tc_common.cuh"
 #include <type_traits>
