@@ -26,9 +26,9 @@
 // That is attention_fwd_kernel: two passes (max first, then exp / sum / P V), no rescaling of O in tensor memory, the
 // price being S computed twice.  attention_fwd1_kernel forms S once: a running maximum and an O accumulator per
 // softmax group, rescaled in tensor memory when the maximum has moved far (see the comment at that kernel); measured
-// 560 against 620 us at [8, 2048, 32, 100].  attention_fwd1p_kernel, which the entry point launches by default, is
-// that kernel with one CTA per SM walking many (batch, query tile, head) items.  All write the true row maximum and the
-// sum relative to it.
+// 560 against 620 us at [8, 2048, 32, 100]; the entry point launches it by default.  attention_fwd1p_kernel is that
+// kernel with one CTA per SM walking many (batch, query tile, head) items, the default for sequences up to 512.  All
+// write the true row maximum and the sum relative to it.
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
 #include "tc_common.cuh"
 #include <type_traits>
@@ -693,7 +693,9 @@ done:
 // boundary: while the softmax warps merge, scale and store the context rows of an item, the producer has loaded the next
 // Q and K / V tiles and the tensor cores have formed its first scores.
 // Items are dealt in rounds of gridDim.x, every other round in reverse CTA order (the list is sorted heaviest first, so
-// a CTA's long items are paired with short ones); every role derives the same sequence on its own.  Tiles are counted
+// a CTA's long items are paired with short ones); every role derives the same sequence on its own.  (Drawing the items
+// from a global counter instead, handed to the roles through a ring in shared memory, balanced better on paper and
+// measured slower everywhere: 578 against 559 us at seq = 2048, 196 against 187 us at seq = 128.)  Tiles are counted
 // across items (n): key tile n goes through ring slot, S buffer, softmax group and O accumulator n & 1.
 int g_attn_fwd_persistent = 1;
 
@@ -1834,7 +1836,11 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   p.idesc_s = common;                       // A, B K-major
   p.idesc_pv = common | (1u << 16);         // B (V) MN-major
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
-  if (g_attn_fwd_single && g_attn_fwd_persistent) {
+  // The persistent walk pays where items are short (measured: 11 to 18 % at seq <= 512, nothing at seq = 2048, where
+  // the hardware's dynamic placement of one-item CTAs balances better than dealing the items out): 1 = short sequences
+  // only, 2 = always, 0 = never.
+  const bool persistent = g_attn_fwd_persistent == 2 || (g_attn_fwd_persistent == 1 && seq / kAttnRows <= 4);
+  if (g_attn_fwd_single && persistent) {
     auto kern = attention_fwd1p_kernel<T>;
     static bool attr_set[kMaxDevices] = {};
     ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);

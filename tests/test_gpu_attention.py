@@ -89,6 +89,19 @@ def test_attention_fwd_one_item_per_cta(cuda, one_item_per_cta, bsz, s, h, hd):
     test_attention_fwd(cuda, bsz, s, h, hd)
 
 
+@pytest.fixture
+def always_persistent():
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 2) == capi.OK
+    yield
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 1) == capi.OK
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(1, 640, 2, 64), (2, 1024, 2, 100)])
+def test_attention_fwd_persistent_long_sequences(cuda, always_persistent, bsz, s, h, hd):
+    test_attention_fwd(cuda, bsz, s, h, hd)
+
+
 def test_attention_fwd_persistent_walk_many_items(cuda):
     """More items than SMs can hold at once, of every length from 1 to 8 key tiles, so that every CTA of the persistent
     kernel walks several items (odd and even tile counts: the tile parity that selects ring slot, softmax group and
@@ -99,9 +112,10 @@ def test_attention_fwd_persistent_walk_many_items(cuda):
     alpha = float(1.0 / np.sqrt(hd))
     qp, kp, vp = (ops.block_pad(t, 128) for t in (q, k, v))
     L = capi.lib()
-    ctx_p, st_p = ops.attention_fwd(qp, kp, vp, hd, alpha)
-    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 2) == capi.OK          # always (the default takes it for seq <= 512 only)
     try:
+        ctx_p, st_p = ops.attention_fwd(qp, kp, vp, hd, alpha)
+        assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK
         ctx_1, st_1 = ops.attention_fwd(qp, kp, vp, hd, alpha)
     finally:
         L.cacti_b200_tune(b"attn_fwd_persistent", 1)
@@ -143,7 +157,7 @@ def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
     out = {}
     for single in (1, 2, 0):                        # persistent single-pass, one item per CTA, two-pass
         assert L.cacti_b200_tune(b"attn_fwd_single", 1 if single else 0) == capi.OK
-        assert L.cacti_b200_tune(b"attn_fwd_persistent", 1 if single == 1 else 0) == capi.OK
+        assert L.cacti_b200_tune(b"attn_fwd_persistent", 2 if single == 1 else 0) == capi.OK
         try:
             ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
             torch.cuda.synchronize()
