@@ -11,7 +11,7 @@ extern int g_nll_gpref, g_nll_stages, g_nll_mode, g_nll_smem_threads;
 extern int g_rope_threads, g_rope_ctas_per_sm, g_rope_staged, g_rope_staged_g, g_rope_staged_groups, g_rope_staged_stages;
 extern int g_swiglu_threads, g_swiglu_ctas_per_sm;
 extern int g_gemm_bn, g_gemm_group_m, g_gemm_sms, g_gemm_pair, g_gemm_split, g_gemm_dynamic;
-extern int g_attn_fwd_single, g_attn_fwd_persistent;
+extern int g_attn_fwd_single, g_attn_fwd_persistent, g_attn_fwd_pair;
 }  // namespace cb
 
 extern "C" {
@@ -105,7 +105,7 @@ int cacti_b200_tune(const char* name, int value) {
       {"rope_staged_groups", &g_rope_staged_groups, 1, 15}, {"rope_staged_stages", &g_rope_staged_stages, 2, 8},
       {"gemm_bn", &g_gemm_bn, 0, 256}, {"gemm_group_m", &g_gemm_group_m, 0, 4096}, {"gemm_sms", &g_gemm_sms, 0, 148}, {"gemm_pair", &g_gemm_pair, 0, 1}, {"gemm_split", &g_gemm_split, 0, 1}, {"gemm_dynamic", &g_gemm_dynamic, 0, 1},
       {"swiglu_threads", &g_swiglu_threads, 32, 256},     {"swiglu_ctas_per_sm", &g_swiglu_ctas_per_sm, 1, 64},
-      {"attn_fwd_single", &g_attn_fwd_single, 0, 1},     {"attn_fwd_persistent", &g_attn_fwd_persistent, 0, 2},
+      {"attn_fwd_single", &g_attn_fwd_single, 0, 1},     {"attn_fwd_persistent", &g_attn_fwd_persistent, 0, 2}, {"attn_fwd_pair", &g_attn_fwd_pair, 0, 1},
   };
   if (!name) return CACTI_B200_ERR_INVALID_VALUE;
   for (const Knob& k : knobs) {

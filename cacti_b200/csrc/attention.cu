@@ -1049,6 +1049,299 @@ attention_fwd1p_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   }
 }
 
+// Two query tiles per CTA, one per softmax group.  In the kernels above the two groups share one query tile and take
+// its key tiles in turn: at the tile's start one group idles until a second key tile exists, at its end one idles while
+// the other finishes, then both wait for the last P V and merge through shared memory: 6.5 us per query tile that no
+// key tile accounts for.  Here group g owns query tile 2 i + g of a (batch, head) outright: its own Q, S buffer, O
+// accumulator, running maximum, probability buffer and context rows, nothing to merge; the two groups read the SAME
+// K / V tiles, loaded once (K through a single slot: both score matmuls of a key tile are issued back to back; V through
+// two).  The tensor-core thread serves whichever group is ready: it looks at the four things it could issue next (a score
+// matmul or a P V for either group) without parking on any of them.  Needs an even number of query tiles.
+int g_attn_fwd_pair = 1;
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, T* __restrict__ ctx, float* __restrict__ stats,
+                      const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = base;                        // 2 x 32 KB (one per group)
+  unsigned char* sK = sQ + 2 * kTileBytes;         // 32 KB
+  unsigned char* sV = sK + kTileBytes;             // 2 x 32 KB
+  unsigned char* sP = sV + 2 * kTileBytes;         // 2 x 32 KB (one per group)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kTileBytes);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* k_full = bars + 1;                     // 1
+  uint64_t* k_empty = bars + 2;                    // 1
+  uint64_t* v_full = bars + 3;                     // 2
+  uint64_t* v_empty = bars + 5;                    // 2
+  uint64_t* s_full = bars + 7;                     // 2 (per group)
+  uint64_t* s_empty = bars + 9;                    // 2
+  uint64_t* p_full = bars + 11;                    // 2
+  uint64_t* p_empty = bars + 13;                   // 2
+  uint64_t* o_full = bars + 15;                    // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // launch order: batch slowest, then the pair of query tiles (heaviest first), then head
+  const int npair = p.seq / (2 * kAttnRows);
+  const int b = (int)(blockIdx.x / (npair * p.heads));
+  const int rem = (int)(blockIdx.x % (npair * p.heads));
+  const int qa = 2 * (npair - 1 - rem / p.heads);  // group 0's query tile; group 1 has qa + 1
+  const int h = rem % p.heads;
+  const int nkv = qa + 2;                          // key tiles 0 .. qa + 1 (the last one for group 1 only)
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
+      mbar_init(s_full + s, 1); mbar_init(s_empty + s, 4); mbar_init(p_full + s, 4); mbar_init(p_empty + s, 1);
+      mbar_init(o_full + s, 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;           // S of group g at 128 g, O of group g at 256 + 128 g
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    mbar_expect_tx(q_full, 2 * kTileBytes);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      tma_load_4d(sQ + (size_t)g * kTileBytes, &tmQ, q_full, 0, (qa + g) * kAttnRows, h, b);
+      tma_load_4d(sQ + (size_t)g * kTileBytes + 16384, &tmQ, q_full, 64, (qa + g) * kAttnRows, h, b);
+    }
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait_bounded(k_empty, (unsigned)(j & 1) ^ 1u, kDevErrAttnTimeout)) goto done;
+      mbar_expect_tx(k_full, kTileBytes);
+      tma_load_4d(sK, &tmK, k_full, 0, j * kAttnRows, h, b);
+      tma_load_4d(sK + 16384, &tmK, k_full, 64, j * kAttnRows, h, b);
+      const int vs = j & 1;
+      if (!mbar_wait_bounded(v_empty + vs, (unsigned)((j >> 1) & 1) ^ 1u, kDevErrAttnTimeout)) goto done;
+      unsigned char* dv = sV + (size_t)vs * kTileBytes;
+      mbar_expect_tx(v_full + vs, kTileBytes);
+#pragma unroll
+      for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+        for (int nh = 0; nh < 2; ++nh)
+          tma_load_4d(dv + kh * 16384 + nh * 8192, &tmV, v_full + vs, nh * 64, j * kAttnRows + kh * 64, h, b);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer: serves whichever group is ready ----------------
+    if (!mbar_wait_bounded(q_full, 0, kDevErrAttnTimeout)) goto done;
+    const int nt[2] = {qa + 1, qa + 2};             // key tiles of each group
+    int sN[2] = {0, 0}, pN[2] = {0, 0};             // score matmuls and P V issued so far, per group
+    int kdone = 0;                                  // key tiles whose slot has been handed back
+    unsigned idle = 0;
+    const uint32_t aK = smem_u32(sK);
+    while (pN[0] < nt[0] || pN[1] < nt[1]) {
+      bool progress = false;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const int j = sN[g];
+        if (j < nt[g] && j == kdone && mbar_test(k_full, (unsigned)(j & 1)) && mbar_test(s_empty + g, (unsigned)(j & 1) ^ 1u)) {
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQ + (size_t)g * kTileBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < kAttnHd / 16; ++k16)
+            tc_mma_f16(tmem_base + (uint32_t)g * 128u, kmajor_desc(aQ, k16), kmajor_desc(aK, k16), p.idesc_s, k16 ? 1u : 0u);
+          tc_commit(s_full + g);
+          sN[g] = j + 1;
+          progress = true;
+          if ((sN[0] > j || j >= nt[0]) && (sN[1] > j || j >= nt[1])) { tc_commit(k_empty); kdone = j + 1; }
+        }
+        const int t = pN[g];
+        if (t < sN[g] && mbar_test(p_full + g, (unsigned)(t & 1)) && mbar_test(v_full + (t & 1), (unsigned)((t >> 1) & 1))) {
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sV + (size_t)(t & 1) * kTileBytes), aP = smem_u32(sP + (size_t)g * kTileBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < kAttnRows / 16; ++k16)
+            tc_mma_f16(tmem_base + 256u + (uint32_t)g * 128u, kmajor_desc(aP, k16), v_desc(aV, k16), p.idesc_pv, (t | k16) ? 1u : 0u);
+          tc_commit(p_empty + g);
+          pN[g] = t + 1;
+          progress = true;
+          if ((pN[0] > t || t >= nt[0]) && (pN[1] > t || t >= nt[1])) tc_commit(v_empty + (t & 1));
+          if (pN[g] == nt[g]) tc_commit(o_full + g);
+        }
+      }
+      if (progress) {
+        idle = 0;
+      } else if (++idle > (1u << 24)) {             // nothing became ready for far longer than any healthy wait
+        atomicMax(&g_dev_error, kDevErrAttnTimeout);
+        goto done;
+      }
+    }
+  } else if (warp >= 2) {
+    // ---------------- softmax groups: group g = query tile qa + g, thread = query row ----------------
+    const int grp = (warp - 2) >> 2;
+    const int qq = warp & 3;                        // TMEM lane quarter this warp may read
+    const int r = qq * 32 + lane;                   // row inside the tile
+    const uint32_t lane_off = (uint32_t)(qq * 32) << 16;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr float kLazy = 8.f;
+    const bool neg = p.alpha < 0.f;
+    const int qi = qa + grp, ntiles = qi + 1, q0 = qi * kAttnRows;
+    unsigned char* myP = sP + (size_t)grp * kTileBytes;
+    const uint32_t ts = tmem_base + (uint32_t)grp * 128u + lane_off;
+    const uint32_t tOg = tmem_base + 256u + (uint32_t)grp * 128u + lane_off;
+    float m_true = -INFINITY, mb = 0.f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      const unsigned ph = (unsigned)(j & 1);
+      if (!mbar_wait_bounded_warp(s_full + grp, ph, kDevErrAttnTimeout)) { ok = false; break; }
+      tc_fence_after();
+      float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+        tc_ld_wait();
+        if (j != qi) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float x = __uint_as_float(v[i >> 5][i & 31]);
+            mq[i & 3] = fmaxf(mq[i & 3], neg ? -x : x);
+          }
+        } else {                                    // diagonal tile: columns c <= r are unmasked
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float x = __uint_as_float(v[i >> 5][i & 31]);
+            if (half * 64 + i <= r) mq[i & 3] = fmaxf(mq[i & 3], neg ? -x : x);
+          }
+        }
+      }
+      float tm = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+      tm = Elem<T>::to_f32(Elem<T>::from_f32(p.alpha * (neg ? -tm : tm)));
+      m_true = fmaxf(m_true, tm);
+      const bool first = j == 0;
+      const float mb_new = m_true * kLog2e;
+      const bool move = first || (mb_new - mb > kLazy);
+      // the group's previous P V must have completed before its O rows are scaled and before its probability buffer
+      // is written again (a score matmul may overtake the P V before it, so s_full does not imply it)
+      bool waited = false;
+      if (__any_sync(0xffffffffu, move && !first)) {
+        if (!mbar_wait_bounded_warp(p_empty + grp, ph ^ 1u, kDevErrAttnTimeout)) { ok = false; break; }
+        waited = true;
+        tc_fence_after();
+        const float f = (move && !first) ? exp2f_approx(mb - mb_new) : 1.f;
+        l *= f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kAttnHd; c0 += 32) {
+          uint32_t o[32];
+          tc_ld32(tOg + (uint32_t)c0, o);
+          tc_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tc_st32(tOg + (uint32_t)c0, o);
+        }
+        tc_st_wait();
+      }
+      if (move) mb = mb_new;
+      float lq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint4 pk[8];
+        uint32_t v[2][32];
+        tc_ld32(ts + (uint32_t)(half * 64), v[0]);
+        tc_ld32(ts + (uint32_t)(half * 64 + 32), v[1]);
+        tc_ld_wait();
+        if (half == 1) {                            // the accumulator is in registers: the next S may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + grp);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int idx = g * 8 + i * 2;
+            const float2 s2 = rounded_scores<T>(p.alpha, v[idx >> 5][idx & 31], v[idx >> 5][(idx & 31) + 1]);
+            float e0 = exp2f_approx(__fmaf_rn(s2.x, kLog2e, -mb));
+            float e1 = exp2f_approx(__fmaf_rn(s2.y, kLog2e, -mb));
+            if (j == qi) {
+              const int c = half * 64 + idx;
+              if (c > r) e0 = 0.f;
+              if (c + 1 > r) e1 = 0.f;
+            }
+            lq[i] += e0 + e1;
+            w[i] = pack2<T>(e0, e1);
+          }
+          pk[g] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (!waited) {
+          if (!mbar_wait_bounded_warp(p_empty + grp, ph ^ 1u, kDevErrAttnTimeout)) { ok = false; break; }
+          waited = true;
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)                 // chunk c of key half `half`, 128-byte-swizzled row
+          *reinterpret_cast<uint4*>(myP + (size_t)half * 16384 + (size_t)r * 128 + ((c ^ (r & 7)) << 4)) = pk[c];
+      }
+      if (!ok) break;
+      l += (lq[0] + lq[1]) + (lq[2] + lq[3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + grp);
+    }
+    // context rows = O / l, through the group's own probability buffer (free once its last P V has completed) so that
+    // whole rows leave with consecutive lanes on consecutive 8-byte pieces
+    const bool fin = ok && mbar_wait_bounded_warp(o_full + grp, 0, kDevErrAttnTimeout);
+    unsigned char* rowbuf = myP;
+    if (fin) {
+      tc_fence_after();
+      const float rl = 1.f / l;
+      float* st = stats + (((long long)b * p.heads + h) * p.seq + q0 + r) * 4;
+      st[0] = m_true;
+      st[1] = l * exp2f_approx(mb - m_true * kLog2e);       // the sum relative to the true maximum
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.head_dim; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(tOg + (uint32_t)c0, v);
+        tc_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {               // 4 elements = 8 bytes (head_dim % 4 == 0)
+          const int c = c0 + g * 4;
+          if (c + 4 <= p.head_dim) {
+            uint2 w;
+            w.x = pack2<T>(__uint_as_float(v[g * 4]) * rl, __uint_as_float(v[g * 4 + 1]) * rl);
+            w.y = pack2<T>(__uint_as_float(v[g * 4 + 2]) * rl, __uint_as_float(v[g * 4 + 3]) * rl);
+            *reinterpret_cast<uint2*>(rowbuf + ((size_t)r * p.head_dim + c) * sizeof(T)) = w;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    named_barrier(1 + grp, 128);
+    if (fin) {
+      const int cw = (warp - 2) & 3;                // the group's 4 warps, 32 rows each
+      for (int rr = cw * 32; rr < cw * 32 + 32; ++rr) {
+        T* out = ctx + (((long long)b * p.seq + q0 + rr) * p.heads + h) * p.head_dim;
+        if (lane < p.head_dim / 4)
+          reinterpret_cast<uint2*>(out)[lane] = *reinterpret_cast<const uint2*>(rowbuf + ((size_t)rr * p.head_dim + lane * 4) * sizeof(T));
+      }
+    }
+    tc_fence_before();
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // c[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d] in f32, written to word 2 of the row's statistics.  Eight lanes per
 // (b, s, h) row, four rows per warp, each lane on 8-byte pieces 8 apart: both tensors stream coalesced and every lane
 // has up to eight loads in flight.
@@ -1840,7 +2133,13 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   // the hardware's dynamic placement of one-item CTAs balances better than dealing the items out): 1 = short sequences
   // only, 2 = always, 0 = never.
   const bool persistent = g_attn_fwd_persistent == 2 || (g_attn_fwd_persistent == 1 && seq / kAttnRows <= 4);
-  if (g_attn_fwd_single && persistent) {
+  if (g_attn_fwd_single && g_attn_fwd_pair && !persistent && (seq / kAttnRows) % 2 == 0) {
+    auto kern = attention_fwd2_kernel<T>;
+    static bool attr_set[kMaxDevices] = {};
+    ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);
+    kern<<<(unsigned)(grid / 2), kAttnThreads, kAttnFwdSmem, st>>>(tmQ, tmK, tmV, reinterpret_cast<T*>(ctx),
+                                                                   reinterpret_cast<float*>(stats), p);
+  } else if (g_attn_fwd_single && persistent) {
     auto kern = attention_fwd1p_kernel<T>;
     static bool attr_set[kMaxDevices] = {};
     ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);

@@ -271,6 +271,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(g_mbar_suspend_ns) : "memory");
   return ok != 0;
 }
+// One look, no parking: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Returns false after `polls` failed polls (default 2^20: at most about 4 s, every poll parked for the full hint; at
 // least a few tens of milliseconds, polls that return at once; far beyond any wait of a healthy kernel).  The answer
 // is per thread: a caller that shares barriers or warp-wide instructions with other threads must agree on it with

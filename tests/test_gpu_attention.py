@@ -79,13 +79,41 @@ def test_attention_fwd_two_pass_kernel(cuda, two_pass_forward, bsz, s, h, hd):
 def one_item_per_cta():
     """Run the single-pass forward as one CTA per (batch, query tile, head) instead of the persistent walk."""
     L = capi.lib()
-    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK and L.cacti_b200_tune(b"attn_fwd_pair", 0) == capi.OK
     yield
-    assert L.cacti_b200_tune(b"attn_fwd_persistent", 1) == capi.OK
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 1) == capi.OK and L.cacti_b200_tune(b"attn_fwd_pair", 1) == capi.OK
 
 
 @pytest.mark.parametrize("bsz,s,h,hd", [(2, 256, 3, 100), (1, 640, 2, 64)])
 def test_attention_fwd_one_item_per_cta(cuda, one_item_per_cta, bsz, s, h, hd):
+    test_attention_fwd(cuda, bsz, s, h, hd)
+
+
+@pytest.fixture
+def pair_forward():
+    """Two query tiles per CTA, one per softmax group (taken by default for sequences longer than 512 with an even number
+    of query tiles): here also for short ones."""
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK and L.cacti_b200_tune(b"attn_fwd_pair", 1) == capi.OK
+    yield
+    assert L.cacti_b200_tune(b"attn_fwd_persistent", 1) == capi.OK
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(1, 256, 1, 128), (2, 256, 3, 100), (1, 512, 2, 64), (2, 1024, 2, 100), (1, 2048, 3, 100)])
+def test_attention_fwd_pair_kernel(cuda, pair_forward, bsz, s, h, hd):
+    test_attention_fwd(cuda, bsz, s, h, hd)
+
+
+@pytest.fixture
+def no_pair_forward():
+    L = capi.lib()
+    assert L.cacti_b200_tune(b"attn_fwd_pair", 0) == capi.OK
+    yield
+    assert L.cacti_b200_tune(b"attn_fwd_pair", 1) == capi.OK
+
+
+@pytest.mark.parametrize("bsz,s,h,hd", [(2, 1024, 2, 100)])
+def test_attention_fwd_one_tile_per_cta_long(cuda, no_pair_forward, bsz, s, h, hd):
     test_attention_fwd(cuda, bsz, s, h, hd)
 
 
@@ -155,15 +183,17 @@ def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
     assert (np.diff(rm[0, 0, ::128]) > 5.6).all()              # the maximum does move by more than 2^8 between tiles
     L = capi.lib()
     out = {}
-    for single in (1, 2, 0):                        # persistent single-pass, one item per CTA, two-pass
+    for single in (1, 2, 0, 3):                     # persistent single-pass, one item per CTA, two-pass, two tiles per CTA
         assert L.cacti_b200_tune(b"attn_fwd_single", 1 if single else 0) == capi.OK
         assert L.cacti_b200_tune(b"attn_fwd_persistent", 2 if single == 1 else 0) == capi.OK
+        assert L.cacti_b200_tune(b"attn_fwd_pair", 1 if single == 3 else 0) == capi.OK
         try:
             ctx, stats = ops.attention_fwd(qp, kp, vp, hd, alpha)
             torch.cuda.synchronize()
         finally:
             L.cacti_b200_tune(b"attn_fwd_single", 1)
             L.cacti_b200_tune(b"attn_fwd_persistent", 1)
+            L.cacti_b200_tune(b"attn_fwd_pair", 1)
         err = C.c_uint(7)
         assert L.cacti_b200_device_error(C.byref(err)) == capi.OK and err.value == 0
         assert_close(host(ctx), rctx, "float16", f"moving maximum, single={single}", floor_frac=1.0, floor_abs=mag)
@@ -173,6 +203,10 @@ def test_attention_fwd_moving_maximum(cuda, s, hd, sign):
         out[single] = (host(ctx), st)
     assert np.array_equal(out[0][1][..., 0], out[1][1][..., 0])          # the same row maxima from both kernels
     assert np.array_equal(out[1][1][..., 0], out[2][1][..., 0])          # persistent or not: the same row maxima
+    if s % 256 == 0:                                 # (an odd number of query tiles falls back to one tile per CTA)
+        assert np.array_equal(out[3][1][..., 0], out[2][1][..., 0])
+        assert_close(out[3][0], out[0][0].astype(np.float64), "float16", "two tiles per CTA vs two-pass", rtol=4e-3, floor_frac=1.0,
+                     floor_abs=mag)
     assert_close(out[1][0], out[0][0].astype(np.float64), "float16", "single-pass vs two-pass", rtol=4e-3, floor_frac=1.0,
                  floor_abs=mag)
 
