@@ -26,9 +26,10 @@
 // That is attention_fwd_kernel: two passes (max first, then exp / sum / P V), no rescaling of O in tensor memory, the
 // price being S computed twice.  attention_fwd1_kernel forms S once: a running maximum and an O accumulator per
 // softmax group, rescaled in tensor memory when the maximum has moved far (see the comment at that kernel); measured
-// 560 against 620 us at [8, 2048, 32, 100]; the entry point launches it by default.  attention_fwd1p_kernel is that
-// kernel with one CTA per SM walking many (batch, query tile, head) items, the default for sequences up to 512.  All
-// write the true row maximum and the sum relative to it.
+// 560 against 620 us at [8, 2048, 32, 100].  attention_fwd1p_kernel is that kernel with one CTA per SM walking many
+// (batch, query tile, head) items, the default for sequences up to 512.  attention_fwd2_kernel, the default beyond
+// that, gives each softmax group a query tile of its own (455 us).  All write the true row maximum and the sum relative
+// to it.
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
 #include "tc_common.cuh"
 #include <type_traits>
