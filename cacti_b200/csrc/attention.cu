@@ -27,8 +27,8 @@
 // price being S computed twice.  attention_fwd1_kernel forms S once: a running maximum and an O accumulator per
 // softmax group, rescaled in tensor memory when the maximum has moved far (see the comment at that kernel); measured
 // 560 against 620 us at [8, 2048, 32, 100].  attention_fwd1p_kernel is that kernel with one CTA per SM walking many
-// (batch, query tile, head) items, the default for sequences up to 512.  attention_fwd2_kernel, the default beyond
-// that, gives each softmax group a query tile of its own (455 us).  All write the true row maximum and the sum relative
+// (batch, query tile, head) items (short sequences with an odd number of query tiles).  attention_fwd2_kernel, the
+// default wherever the number of query tiles is even, gives each softmax group a query tile of its own (455 us).  All write the true row maximum and the sum relative
 // to it.
 // Every wait is bounded (kDevErrAttnTimeout); no load uses cluster multicast.
 #include "tc_common.cuh"
@@ -2130,11 +2130,15 @@ static int attention_fwd_run(uint64_t ctx, uint64_t stats, uint64_t q, uint64_t 
   p.idesc_s = common;                       // A, B K-major
   p.idesc_pv = common | (1u << 16);         // B (V) MN-major
   const long long grid = (long long)batch * heads * (seq / kAttnRows);
-  // The persistent walk pays where items are short (measured: 11 to 18 % at seq <= 512, nothing at seq = 2048, where
-  // the hardware's dynamic placement of one-item CTAs balances better than dealing the items out): 1 = short sequences
-  // only, 2 = always, 0 = never.
+  // The persistent walk pays where items are short (measured against one tile per CTA: 11 to 18 % at seq <= 512, nothing
+  // at seq = 2048, where the hardware's dynamic placement of one-item CTAs balances better than dealing the items out):
+  // 1 = short sequences only, 2 = always, 0 = never.
+  // Two query tiles per CTA wherever their number is even (measured fastest at every length: 185 / 227 / 313 / 464 us at
+  // seq = 256 / 512 / 1024 / 2048 against 196 / 257 / 356 / 562 us persistent and 233 / 289 / 389 / 568 us one tile per
+  // CTA, 28 one-tile CTAs per SM each); otherwise the persistent walk for short sequences, one tile per CTA for long.
+  const bool pair = g_attn_fwd_pair && (seq / kAttnRows) % 2 == 0 && g_attn_fwd_persistent != 2;
   const bool persistent = g_attn_fwd_persistent == 2 || (g_attn_fwd_persistent == 1 && seq / kAttnRows <= 4);
-  if (g_attn_fwd_single && g_attn_fwd_pair && !persistent && (seq / kAttnRows) % 2 == 0) {
+  if (g_attn_fwd_single && pair) {
     auto kern = attention_fwd2_kernel<T>;
     static bool attr_set[kMaxDevices] = {};
     ensure_dynamic_smem(kern, kAttnFwdSmem, attr_set);

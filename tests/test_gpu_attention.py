@@ -91,8 +91,7 @@ def test_attention_fwd_one_item_per_cta(cuda, one_item_per_cta, bsz, s, h, hd):
 
 @pytest.fixture
 def pair_forward():
-    """Two query tiles per CTA, one per softmax group (taken by default for sequences longer than 512 with an even number
-    of query tiles): here also for short ones."""
+    """Two query tiles per CTA, one per softmax group (the default wherever the number of query tiles is even)."""
     L = capi.lib()
     assert L.cacti_b200_tune(b"attn_fwd_persistent", 0) == capi.OK and L.cacti_b200_tune(b"attn_fwd_pair", 1) == capi.OK
     yield
